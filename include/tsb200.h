@@ -1,0 +1,145 @@
+/*
+ * tsb200 - C ABI of the B200 (sm_100a) kernel library behind the torch_scatter operator set.
+ *
+ * Everything here is plain C: device pointers, 64-bit sizes, enums as int, a CUDA stream handle.
+ * No torch types cross this boundary.  Every entry point
+ *   - returns 0 (TSB_OK) or a tsb_status error code, never throws,
+ *   - launches on the stream it is given and returns without synchronising,
+ *   - allocates no memory: scratch comes from the caller (query the *_workspace_bytes twin first),
+ *   - is re-entrant; the only global state is read-only per-device attributes cached on first use.
+ *
+ * Canonical flattened shapes (the same B/E/K/N flattening the upstream launchers use,
+ * csrc/cuda/scatter_cuda.cu:103-110, segment_csr_cuda.cu:144-146, segment_coo_cuda.cu:207-211):
+ *   src  [B, E, K]   B = product of the dims before the reduced dim, E = length of the reduced dim,
+ *   out  [B, N, K]   K = product of the trailing (feature) dims, N = output length of the reduced dim.
+ * All data tensors are dense row-major in that flattened shape.  Index / indptr tensors are int64.
+ *
+ * Robustness rule: an index outside [0, N) or an indptr outside [0, E] never faults the GPU; such
+ * entries are skipped / clamped (the upstream kernels leave this undefined, scatter_cuda.cu:25-30).
+ */
+#ifndef TSB200_H
+#define TSB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cudaStream_t without pulling in cuda_runtime.h */
+typedef struct CUstream_st *tsb_stream_t;
+
+/* element types of src/out (the six types the upstream test-suite exercises, torch_scatter/testing.py:7-10) */
+enum tsb_dtype { TSB_F32 = 0, TSB_F64 = 1, TSB_F16 = 2, TSB_BF16 = 3, TSB_I32 = 4, TSB_I64 = 5 };
+
+/* reductions (csrc/cuda/reducer.cuh:8-13; "div" is unreachable upstream and is not provided) */
+enum tsb_reduce { TSB_SUM = 0, TSB_MEAN = 1, TSB_MIN = 2, TSB_MAX = 3, TSB_MUL = 4 };
+
+enum tsb_status {
+  TSB_OK = 0,
+  TSB_ERR_DTYPE = 1,       /* unknown dtype enum */
+  TSB_ERR_REDUCE = 2,      /* unknown / unsupported reduction for this entry point */
+  TSB_ERR_ARG = 3,         /* null pointer or negative size where one is required */
+  TSB_ERR_WORKSPACE = 4,   /* workspace pointer null or smaller than *_workspace_bytes() */
+  TSB_ERR_LAUNCH = 5,      /* cudaGetLastError() reported a launch failure */
+  TSB_ERR_TOO_LARGE = 6    /* a size exceeds a documented limit of the entry point */
+};
+
+/* Human-readable text for a tsb_status value (static storage). */
+const char *tsb_status_string(int status);
+
+/* CUDA toolkit version the library was compiled with, e.g. 12090.
+ * Replaces scatter::cuda_version(), csrc/version.cpp:27-42. */
+int64_t tsb_cuda_version(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * segment_csr: out[b,n,:] = reduce over e in [indptr[b,n], indptr[b,n+1]) of src[b,e,:]
+ * Replaces segment_csr_cuda + segment_csr_kernel / segment_csr_broadcast_kernel,
+ * csrc/cuda/segment_csr_cuda.cu:97-168, :15-60, :62-95 (CPU twin csrc/cpu/segment_csr_cpu.cpp:8-92).
+ *   indptr               [*, N+1] int64; row b starts at indptr + b*indptr_batch_stride (0 = one shared row)
+ *   out                  [B,N,K]; always overwritten (never accumulated into)
+ *   arg_out              [B,N,K] int64, required for MIN/MAX, ignored otherwise; empty rows get E
+ *   reduce               SUM, MEAN, MIN or MAX.  MEAN divides by max(count,1); empty rows give 0.
+ * Deterministic: the summation order depends only on the shapes.  Needs no workspace. */
+int tsb_segment_csr(const void *src, const int64_t *indptr, void *out, int64_t *arg_out,
+                    int64_t B, int64_t E, int64_t K, int64_t N, int64_t indptr_batch_stride,
+                    int dtype, int reduce, tsb_stream_t stream);
+
+/* gather_csr: out[b,e,:] = src[b,n,:] for e in [indptr[b,n], indptr[b,n+1]); positions no row covers
+ * are left untouched.  Replaces gather_csr_cuda + kernels, csrc/cuda/segment_csr_cuda.cu:219-281,
+ * :170-217.  Here src is [B,N,K] and out is [B,E,K].
+ *   divide_by_count != 0 fuses the backward of segment_mean_csr (csrc/segment_csr.cpp:94-111):
+ *   each row's value is divided by its length before it is broadcast (floating dtypes only). */
+int tsb_gather_csr(const void *src, const int64_t *indptr, void *out,
+                   int64_t B, int64_t E, int64_t K, int64_t N, int64_t indptr_batch_stride,
+                   int dtype, int divide_by_count, tsb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * segment_coo: the same reduction keyed by a SORTED index [*, E] (row b at index + b*index_batch_stride).
+ * Replaces segment_coo_cuda + its five kernels, csrc/cuda/segment_coo_cuda.cu:152-283, :14-150
+ * (CPU twin csrc/cpu/segment_coo_cpu.cpp:8-141).
+ *   out_seeded == 0      out is write-only: rows no index names become 0; MIN/MAX results equal to
+ *                        the reduction's identity are replaced by 0 (segment_coo_cpu.cpp:131-132)
+ *   out_seeded != 0      accumulate into the caller's out (the `out=` argument): each named row
+ *                        starts from its current value; unnamed rows are untouched
+ *   arg_out              [B,N,K] int64 for MIN/MAX (always fully written; E where no element won)
+ *   count_out            [B,N] of dtype, for MEAN: run length clamped to >= 1 (segment_coo_cpu.cpp:134-136)
+ *   workspace            tsb_segment_coo_workspace_bytes(B,N) bytes, holds the row pointers rebuilt
+ *                        from the sorted index.
+ * Deterministic (no atomics). */
+size_t tsb_segment_coo_workspace_bytes(int64_t B, int64_t N);
+int tsb_segment_coo(const void *src, const int64_t *index, void *out, int64_t *arg_out, void *count_out,
+                    int64_t B, int64_t E, int64_t K, int64_t N, int64_t index_batch_stride,
+                    int dtype, int reduce, int out_seeded,
+                    void *workspace, size_t workspace_bytes, tsb_stream_t stream);
+
+/* gather_coo: out[b,e,:] = src[b,index[b,e],:].  src [B,N,K], out [B,E,K].
+ * Replaces gather_coo_cuda + kernels, csrc/cuda/segment_coo_cuda.cu:327-382, :285-325.
+ *   count (may be null)  [B,N] of dtype: when given, each value is divided by count[b,index[b,e]];
+ *                        fuses the backward of segment_mean_coo (csrc/segment_coo.cpp:99-112). */
+int tsb_gather_coo(const void *src, const int64_t *index, void *out, const void *count,
+                   int64_t B, int64_t E, int64_t K, int64_t N, int64_t index_batch_stride,
+                   int dtype, tsb_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * scatter: out[b, index(b,e,k), k] (+)= src[b,e,k] for an UNSORTED index.
+ * Replaces scatter_cuda + scatter_kernel + scatter_arg_kernel, csrc/cuda/scatter_cuda.cu:58-138,
+ * :13-56 (CPU twin csrc/cpu/scatter_cpu.cpp:7-87), and for SUM/MEAN the ATen route of
+ * torch_scatter/scatter.py:8-25,44-66.
+ *   index                int64 view of logical shape [B,E,K] addressed as
+ *                        index[b*idx_stride_b + e*idx_stride_e + k*idx_stride_k]; a broadcast 1-D
+ *                        index is (0,1,0) and is then read once per row, not once per element
+ *   reduce               SUM, MEAN, MIN, MAX or MUL
+ *   out_seeded           0: out is write-only (SUM/MEAN/MUL start from the identity; MIN/MAX results
+ *                        equal to the identity become 0, scatter_cpu.cpp:80-81); !=0: accumulate into out
+ *   arg_out              [B,N,K] int64 for MIN/MAX: smallest e whose value equals the result, else E
+ *   count_out            MEAN only: int32 [Bc,N,Kc] with Bc = idx_stride_b ? B : 1 and
+ *                        Kc = idx_stride_k ? K : 1; receives the per-target element count
+ *   workspace            tsb_scatter_workspace_bytes(...) bytes (fp32 accumulators for 16-bit dtypes)
+ * Float SUM/MEAN/MUL use atomics: the summation order is not fixed.  MIN/MAX and arg are exact. */
+size_t tsb_scatter_workspace_bytes(int64_t B, int64_t N, int64_t K, int dtype, int reduce);
+int tsb_scatter(const void *src, const int64_t *index, void *out, int64_t *arg_out, int32_t *count_out,
+                int64_t B, int64_t E, int64_t K, int64_t N,
+                int64_t idx_stride_b, int64_t idx_stride_e, int64_t idx_stride_k,
+                int dtype, int reduce, int out_seeded,
+                void *workspace, size_t workspace_bytes, tsb_stream_t stream);
+
+/* Backward of scatter SUM / MEAN: grad_in[b,e,k] = grad_out[b, index(b,e,k), k] (/ max(count,1)).
+ * Replaces the torch::gather calls in ScatterSum/ScatterMean::backward, csrc/scatter.cpp:72-80,149-160.
+ * count may be null (SUM); otherwise the int32 tensor tsb_scatter filled for MEAN. */
+int tsb_scatter_backward(const void *grad_out, const int64_t *index, void *grad_in, const int32_t *count,
+                         int64_t B, int64_t E, int64_t K, int64_t N,
+                         int64_t idx_stride_b, int64_t idx_stride_e, int64_t idx_stride_k,
+                         int dtype, tsb_stream_t stream);
+
+/* Backward of every MIN/MAX op: grad_in [B,E,K] is zeroed, then grad_in[b, arg[b,n,k], k] = grad_out[b,n,k]
+ * wherever arg < E.  Replaces the zeros + scatter_ + narrow sequence of csrc/scatter.cpp:184-196,
+ * csrc/segment_coo.cpp:132-144 and csrc/segment_csr.cpp:130-142. */
+int tsb_arg_backward(const void *grad_out, const int64_t *arg, void *grad_in,
+                     int64_t B, int64_t E, int64_t K, int64_t N, int dtype, tsb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TSB200_H */

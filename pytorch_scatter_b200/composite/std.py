@@ -1,0 +1,39 @@
+"""Grouped standard deviation over an unsorted index.
+
+Same signature and two-pass arithmetic as ``torch_scatter/composite/std.py:8-39`` upstream: group
+means first, then the sum of squared deviations, divided by ``max(count - 1, 1) + 1e-6`` when
+``unbiased``.
+"""
+from typing import Optional
+
+import torch
+
+from ..scatter import scatter_sum
+from ..utils import broadcast
+
+
+def scatter_std(src: torch.Tensor, index: torch.Tensor, dim: int = -1,
+                out: Optional[torch.Tensor] = None,
+                dim_size: Optional[int] = None,
+                unbiased: bool = True) -> torch.Tensor:
+    if out is not None:
+        dim_size = out.size(dim)
+    if dim < 0:
+        dim = src.dim() + dim
+
+    # group sizes, counted over the index as given (before broadcasting)
+    index_dim = dim if index.dim() > dim else index.dim() - 1
+    ones = torch.ones(index.size(), dtype=src.dtype, device=src.device)
+    count = scatter_sum(ones, index, index_dim, dim_size=dim_size)
+
+    index = broadcast(index, src, dim)
+    total = scatter_sum(src, index, dim, dim_size=dim_size)
+    count = broadcast(count, total, dim).clamp(1)
+    mean = total.div(count)
+
+    deviation = src - mean.gather(dim, index)
+    out = scatter_sum(deviation * deviation, index, dim, out, dim_size)
+
+    if unbiased:
+        count = count.sub(1).clamp_(1)
+    return out.div(count + 1e-6).sqrt()

@@ -1,0 +1,28 @@
+// Internal interface of the row-pointer segmented reduction shared by segment_csr and segment_coo.
+#pragma once
+
+#include "common.cuh"
+
+namespace tsb {
+
+// How results are written (the three behaviours of the upstream CPU loops):
+//   kCsr        out overwritten; empty row -> 0, arg E          (csrc/cpu/segment_csr_cpu.cpp:69-87)
+//   kCooFresh   out write-only; absent row -> 0; MIN/MAX equal to the identity -> 0
+//                                                              (csrc/cpu/segment_coo_cpu.cpp:84-85,131-132)
+//   kCooSeeded  accumulate into out; absent rows untouched     (csrc/cpu/segment_coo_cpu.cpp:91-92,120)
+enum CsrMode { kCsr = 0, kCooFresh = 1, kCooSeeded = 2 };
+
+struct CsrParams {
+  const void *src;        // [B,E,K]
+  const int64_t *indptr;  // row b at indptr + b*bstride, N+1 entries
+  void *out;              // [B,N,K]
+  int64_t *arg_out;       // [B,N,K] or null
+  void *count_out;        // [B,N] of dtype or null (COO mean)
+  int64_t B, E, K, N, bstride;
+  int mode;
+};
+
+// Picks the vector width / lane geometry from the shapes and launches.  Returns a tsb_status.
+int launch_csr_reduce(const CsrParams &p, int dtype, int reduce, cudaStream_t stream);
+
+}  // namespace tsb

@@ -1,0 +1,280 @@
+// torch_scatter::scatter_{sum,mul,mean,min,max}: schemas and autograd behaviour of the upstream
+// registry (csrc/scatter.cpp:54-277) on top of the tsb200 C ABI.  Unlike upstream, the Python
+// scatter_sum / scatter_mean wrappers route here too instead of to ATen's scatter_add_.
+#include "ops_common.h"
+
+namespace tsb_ops {
+namespace {
+
+// index broadcast to src's shape (csrc/scatter.cpp:25-33)
+torch::Tensor broadcast(torch::Tensor src, torch::Tensor other, int64_t dim) {
+  if (src.dim() == 1)
+    for (int64_t i = 0; i < dim; i++) src = src.unsqueeze(0);
+  for (int64_t i = src.dim(); i < other.dim(); i++) src = src.unsqueeze(-1);
+  src = src.expand(other.sizes().vec());
+  return src;
+}
+
+// Stride of the dims [lo,hi) of `t` seen as one flattened dim, if such a single stride exists.
+bool collapse_stride(const torch::Tensor &t, int64_t lo, int64_t hi, int64_t *stride) {
+  int64_t s = 0;      // stride of the innermost non-trivial dim seen so far
+  int64_t span = 1;   // number of elements that dim block covers
+  bool any = false;
+  for (int64_t i = hi - 1; i >= lo; i--) {
+    if (t.size(i) == 1) continue;
+    if (!any) {
+      s = t.stride(i);
+      span = t.size(i);
+      any = true;
+    } else {
+      if (t.stride(i) != s * span) return false;
+      span *= t.size(i);
+    }
+  }
+  *stride = any ? s : 0;
+  return true;
+}
+
+// The broadcast index as (tensor kept alive, strides over the flattened [B,E,K] view).
+struct FlatIndex {
+  torch::Tensor holder;
+  int64_t sb, se, sk;
+};
+
+FlatIndex flatten_index(const torch::Tensor &index, int64_t dim) {
+  FlatIndex f;
+  f.holder = index;
+  const int64_t nd = index.dim();
+  if (collapse_stride(index, 0, dim, &f.sb) && collapse_stride(index, dim + 1, nd, &f.sk)) {
+    f.se = index.size(dim) == 1 ? 0 : index.stride(dim);
+    return f;
+  }
+  f.holder = index.contiguous();
+  int64_t K = 1;
+  for (int64_t i = dim + 1; i < nd; i++) K *= index.size(i);
+  f.sk = K == 1 ? 0 : 1;
+  f.se = K;
+  f.sb = K * index.size(dim);
+  return f;
+}
+
+struct ScatterResult {
+  torch::Tensor out;
+  std::optional<torch::Tensor> arg_out;
+  std::optional<torch::Tensor> count;  // int32, MEAN only
+};
+
+// index must already be broadcast to src's shape.
+ScatterResult scatter_fw(torch::Tensor src, torch::Tensor index, int64_t dim,
+                         std::optional<torch::Tensor> optional_out, std::optional<int64_t> dim_size,
+                         const std::string &reduce) {
+  TSB_CHECK_CUDA(src);
+  TSB_CHECK_CUDA(index);
+  if (optional_out.has_value()) TSB_CHECK_CUDA(optional_out.value());
+  check_index_dtype(index, "index");
+  c10::cuda::CUDAGuard guard(src.device());
+
+  TSB_CHECK_INPUT(src.dim() == index.dim());
+  TSB_CHECK_INPUT(dim >= 0 && dim < src.dim());
+  for (int64_t i = 0; i < index.dim(); i++) TSB_CHECK_INPUT(src.size(i) == index.size(i));
+
+  src = src.contiguous();
+  const int red = reduce_enum(reduce);
+
+  ScatterResult r;
+  bool copy_back = false;
+  if (optional_out.has_value()) {
+    copy_back = !optional_out.value().is_contiguous();
+    r.out = optional_out.value().contiguous();
+    TSB_CHECK_INPUT(r.out.dim() == src.dim());
+    TSB_CHECK_INPUT(r.out.scalar_type() == src.scalar_type());
+    for (int64_t i = 0; i < r.out.dim(); i++)
+      if (i != dim) TSB_CHECK_INPUT(src.size(i) == r.out.size(i));
+  } else {
+    auto sizes = src.sizes().vec();
+    if (dim_size.has_value())
+      sizes[dim] = dim_size.value();
+    else if (index.numel() == 0)
+      sizes[dim] = 0;
+    else
+      sizes[dim] = 1 + index.max().item<int64_t>();  // host sync, as upstream (scatter_cuda.cu:87)
+    r.out = torch::empty(sizes, src.options());
+  }
+
+  const bool minmax = red == TSB_MIN || red == TSB_MAX;
+  int64_t B = 1;
+  for (int64_t i = 0; i < dim; i++) B *= src.size(i);
+  const int64_t E = src.size(dim);
+  int64_t K = 1;
+  for (int64_t i = dim + 1; i < src.dim(); i++) K *= src.size(i);
+  const int64_t N = r.out.size(dim);
+
+  if (src.numel() == 0) {
+    if (minmax) r.arg_out = torch::full_like(r.out, src.size(dim), index.options());
+    if (red == TSB_MEAN) r.count = torch::ones({1}, index.options().dtype(torch::kInt32));
+    if (!optional_out.has_value()) r.out.fill_(0);
+    return r;
+  }
+
+  FlatIndex fi = flatten_index(index, dim);
+  if (minmax) r.arg_out = torch::empty(r.out.sizes(), index.options());
+  if (red == TSB_MEAN) {
+    // element counts over the dims the index really varies in (torch_scatter/scatter.py:52-61)
+    r.count = torch::empty({fi.sb ? B : 1, N, fi.sk ? K : 1}, index.options().dtype(torch::kInt32));
+  }
+  if (r.out.numel() > 0) {
+    const size_t ws_bytes = tsb_scatter_workspace_bytes(B, N, K, dtype_enum(src), red);
+    torch::Tensor workspace;
+    if (ws_bytes > 0) workspace = torch::empty({(int64_t)ws_bytes}, src.options().dtype(torch::kUInt8));
+    check_status(tsb_scatter(src.data_ptr(), fi.holder.data_ptr<int64_t>(), r.out.data_ptr(),
+                             minmax ? r.arg_out.value().data_ptr<int64_t>() : nullptr,
+                             red == TSB_MEAN ? r.count.value().data_ptr<int32_t>() : nullptr, B, E, K, N, fi.sb,
+                             fi.se, fi.sk, dtype_enum(src), red, optional_out.has_value() ? 1 : 0,
+                             ws_bytes > 0 ? workspace.data_ptr() : nullptr, ws_bytes, current_stream()),
+                 "tsb_scatter");
+  }
+  if (copy_back) {
+    optional_out.value().copy_(r.out);
+    r.out = optional_out.value();
+  }
+  return r;
+}
+
+// grad_in[b,e,k] = grad_out[b, index(b,e,k), k] (/ count): the gather behind SUM / MEAN / MUL backward.
+torch::Tensor scatter_bw(const torch::Tensor &grad_out_, const torch::Tensor &index, int64_t dim,
+                         const std::vector<int64_t> &src_shape, std::optional<torch::Tensor> count) {
+  c10::cuda::CUDAGuard guard(grad_out_.device());
+  auto grad_out = grad_out_.contiguous();
+  auto grad_in = torch::empty(src_shape, grad_out.options());
+  if (grad_in.numel() == 0) return grad_in;
+  int64_t B = 1, K = 1;
+  for (int64_t i = 0; i < dim; i++) B *= src_shape[i];
+  for (size_t i = dim + 1; i < src_shape.size(); i++) K *= src_shape[i];
+  const int64_t E = src_shape[dim];
+  const int64_t N = grad_out.size(dim);
+  FlatIndex fi = flatten_index(index, dim);
+  check_status(tsb_scatter_backward(grad_out.data_ptr(), fi.holder.data_ptr<int64_t>(), grad_in.data_ptr(),
+                                    count.has_value() ? count.value().data_ptr<int32_t>() : nullptr, B, E, K, N,
+                                    fi.sb, fi.se, fi.sk, dtype_enum(grad_out), current_stream()),
+               "tsb_scatter_backward");
+  return grad_in;
+}
+
+using torch::autograd::AutogradContext;
+using torch::autograd::Variable;
+using torch::autograd::variable_list;
+
+// SUM (csrc/scatter.cpp:54-81) and MEAN (csrc/scatter.cpp:115-161; the count and the divide are
+// fused into the forward kernels, the gathered-count divide into the backward kernel).
+template <bool MEAN> class ScatterSumMean : public torch::autograd::Function<ScatterSumMean<MEAN>> {
+public:
+  static variable_list forward(AutogradContext *ctx, Variable src, Variable index, int64_t dim,
+                               std::optional<Variable> optional_out, std::optional<int64_t> dim_size) {
+    dim = dim < 0 ? src.dim() + dim : dim;
+    ctx->saved_data["dim"] = dim;
+    ctx->saved_data["src_shape"] = src.sizes();
+    index = broadcast(index, src, dim);
+    auto result = scatter_fw(src, index, dim, optional_out, dim_size, MEAN ? "mean" : "sum");
+    if (MEAN) ctx->save_for_backward({index, result.count.value()});
+    else ctx->save_for_backward({index});
+    if (optional_out.has_value()) ctx->mark_dirty({optional_out.value()});
+    return {result.out};
+  }
+  static variable_list backward(AutogradContext *ctx, variable_list grad_outs) {
+    auto saved = ctx->get_saved_variables();
+    auto dim = ctx->saved_data["dim"].toInt();
+    auto src_shape = list2vec(ctx->saved_data["src_shape"].toIntList());
+    std::optional<torch::Tensor> count = std::nullopt;
+    if (MEAN) count = saved[1];
+    auto grad_in = scatter_bw(grad_outs[0], saved[0], dim, src_shape, count);
+    return {grad_in, Variable(), Variable(), Variable(), Variable()};
+  }
+};
+
+// MUL (csrc/scatter.cpp:83-113)
+class ScatterMul : public torch::autograd::Function<ScatterMul> {
+public:
+  static variable_list forward(AutogradContext *ctx, Variable src, Variable index, int64_t dim,
+                               std::optional<Variable> optional_out, std::optional<int64_t> dim_size) {
+    dim = dim < 0 ? src.dim() + dim : dim;
+    ctx->saved_data["dim"] = dim;
+    ctx->saved_data["src_shape"] = src.sizes();
+    index = broadcast(index, src, dim);
+    auto result = scatter_fw(src, index, dim, optional_out, dim_size, "mul");
+    ctx->save_for_backward({src, index, result.out});
+    if (optional_out.has_value()) ctx->mark_dirty({optional_out.value()});
+    return {result.out};
+  }
+  static variable_list backward(AutogradContext *ctx, variable_list grad_outs) {
+    auto saved = ctx->get_saved_variables();
+    auto src = saved[0];
+    auto index = saved[1];
+    auto out = saved[2];
+    auto dim = ctx->saved_data["dim"].toInt();
+    auto src_shape = list2vec(ctx->saved_data["src_shape"].toIntList());
+    auto grad_in = scatter_bw(grad_outs[0] * out, index, dim, src_shape, std::nullopt).div_(src);
+    grad_in.masked_fill_(grad_in.isnan(), 0);
+    return {grad_in, Variable(), Variable(), Variable(), Variable()};
+  }
+};
+
+// MIN / MAX (csrc/scatter.cpp:163-233)
+template <bool MAX> class ScatterMinMax : public torch::autograd::Function<ScatterMinMax<MAX>> {
+public:
+  static variable_list forward(AutogradContext *ctx, Variable src, Variable index, int64_t dim,
+                               std::optional<Variable> optional_out, std::optional<int64_t> dim_size) {
+    dim = dim < 0 ? src.dim() + dim : dim;
+    ctx->saved_data["dim"] = dim;
+    ctx->saved_data["src_shape"] = src.sizes();
+    index = broadcast(index, src, dim);
+    auto result = scatter_fw(src, index, dim, optional_out, dim_size, MAX ? "max" : "min");
+    auto arg_out = result.arg_out.value();
+    ctx->save_for_backward({index, arg_out});
+    ctx->mark_non_differentiable({arg_out});
+    if (optional_out.has_value()) ctx->mark_dirty({optional_out.value()});
+    return {result.out, arg_out};
+  }
+  static variable_list backward(AutogradContext *ctx, variable_list grad_outs) {
+    auto saved = ctx->get_saved_variables();
+    auto dim = ctx->saved_data["dim"].toInt();
+    auto src_shape = list2vec(ctx->saved_data["src_shape"].toIntList());
+    auto grad_in = arg_backward(grad_outs[0], saved[1], src_shape, dim);
+    return {grad_in, Variable(), Variable(), Variable(), Variable()};
+  }
+};
+
+torch::Tensor scatter_sum(torch::Tensor src, torch::Tensor index, int64_t dim,
+                          std::optional<torch::Tensor> optional_out, std::optional<int64_t> dim_size) {
+  return ScatterSumMean<false>::apply(src, index, dim, optional_out, dim_size)[0];
+}
+torch::Tensor scatter_mul(torch::Tensor src, torch::Tensor index, int64_t dim,
+                          std::optional<torch::Tensor> optional_out, std::optional<int64_t> dim_size) {
+  return ScatterMul::apply(src, index, dim, optional_out, dim_size)[0];
+}
+torch::Tensor scatter_mean(torch::Tensor src, torch::Tensor index, int64_t dim,
+                           std::optional<torch::Tensor> optional_out, std::optional<int64_t> dim_size) {
+  return ScatterSumMean<true>::apply(src, index, dim, optional_out, dim_size)[0];
+}
+std::tuple<torch::Tensor, torch::Tensor> scatter_min(torch::Tensor src, torch::Tensor index, int64_t dim,
+                                                     std::optional<torch::Tensor> optional_out,
+                                                     std::optional<int64_t> dim_size) {
+  auto result = ScatterMinMax<false>::apply(src, index, dim, optional_out, dim_size);
+  return std::make_tuple(result[0], result[1]);
+}
+std::tuple<torch::Tensor, torch::Tensor> scatter_max(torch::Tensor src, torch::Tensor index, int64_t dim,
+                                                     std::optional<torch::Tensor> optional_out,
+                                                     std::optional<int64_t> dim_size) {
+  auto result = ScatterMinMax<true>::apply(src, index, dim, optional_out, dim_size);
+  return std::make_tuple(result[0], result[1]);
+}
+
+}  // namespace
+}  // namespace tsb_ops
+
+TORCH_LIBRARY_FRAGMENT(torch_scatter, m) {
+  m.def("scatter_sum", &tsb_ops::scatter_sum);
+  m.def("scatter_mul", &tsb_ops::scatter_mul);
+  m.def("scatter_mean", &tsb_ops::scatter_mean);
+  m.def("scatter_min", &tsb_ops::scatter_min);
+  m.def("scatter_max", &tsb_ops::scatter_max);
+}
