@@ -1,0 +1,352 @@
+#!/usr/bin/env python
+"""Benchmark of the reduction hot path: segment_csr(sum) and unsorted scatter(sum), fp32, F=64, on the
+synthetic power-law CSR workload (1,048,576 rows, ~16.8M entries, log-normal row lengths).
+
+One step = one segment_csr(sum) over the sorted rows + one scatter(sum) of the same source rows
+through a shuffled (unsorted) copy of the row index.  The metric is effective HBM bandwidth:
+algorithmic bytes (each of src, index/indptr and out counted once) divided by device time.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]        this library, N GPUs (torchrun for N>1)
+    python bench.py --impl reference [...]                     the upstream CPU implementation on the
+                                                               host cores, on a bounded sample
+
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import os.path as osp
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = osp.dirname(osp.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS = 1 << 20
+FEAT = 64
+SEED = 20240602
+METRIC = 'segment_csr+scatter sum effective HBM bandwidth (F=64, fp32, power-law CSR)'
+UNIT = 'GB/s'
+# Per-launch DRAM traffic of csr_reduce_kernel on the full workload, from the ncu capture summarised
+# in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists.
+CSR_KERNEL_DRAM_TRAFFIC_BYTES = None
+
+
+def row_lengths(rows, seed, force_long=8):
+    """Log-normal row lengths with mean ~16, clipped to 20,000, ~13% empty rows; `force_long` seeded
+    rows are set to 20,000 so that the long-row path is always exercised."""
+    g = torch.Generator().manual_seed(seed)
+    sigma = 1.5
+    mu = torch.log(torch.tensor(16.5, dtype=torch.float64)) - sigma * sigma / 2
+    z = torch.randn(rows, generator=g, dtype=torch.float64)
+    lens = torch.exp(mu + sigma * z).floor().clamp_(0, 20000).long()
+    if force_long:
+        where = torch.randperm(rows, generator=g)[:force_long]
+        lens[where] = 20000
+    return lens
+
+
+def make_workload(rows, seed, feat=FEAT):
+    """CPU tensors: indptr [rows+1], sorted index [nnz], shuffled index [nnz], src [nnz, feat]."""
+    lens = row_lengths(rows, seed, force_long=max(1, 8 * rows // ROWS))
+    indptr = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)])
+    nnz = int(indptr[-1])
+    g = torch.Generator().manual_seed(seed + 1)
+    sorted_index = torch.repeat_interleave(torch.arange(rows), lens)
+    shuffled_index = sorted_index[torch.randperm(nnz, generator=g)]
+    src = torch.randn(nnz, feat, generator=g, dtype=torch.float32)
+    return indptr, sorted_index, shuffled_index, src
+
+
+def algorithmic_bytes(rows, nnz, feat=FEAT, s=4):
+    csr = nnz * feat * s + (rows + 1) * 8 + rows * feat * s
+    scatter = nnz * feat * s + nnz * 8 + rows * feat * s
+    return csr, scatter
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,'
+         'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+         'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index):
+        self.gpu_index, self.proc = gpu_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits',
+                                          '-lms', '100', '-i', str(self.gpu_index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(',')]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith('active'):
+                    reasons.add(name)
+        return {'sm_mhz': statistics.median(sm) if sm else None, 'sm_max_mhz': max(mx) if mx else None,
+                'reasons': sorted(reasons), 'samples': len(sm)}
+
+
+# -------------------------------------------------------------------------------------------------
+def run_reference(args):
+    """Upstream CPU implementation (oracle/_ref when built, else the C port) on a bounded sample."""
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    rows = ROWS // args.ref_fraction
+    indptr, _, shuffled, src = make_workload(rows, SEED)
+    nnz = src.size(0)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    ref_dir = osp.join(ROOT, 'oracle', '_ref')
+    libs = sorted(f for f in os.listdir(ref_dir) if f.endswith('_cpu.so')) if osp.isdir(ref_dir) else []
+    if len(libs) >= 3:
+        kind = 'reference'
+        for f in libs:
+            torch.ops.load_library(osp.join(ref_dir, f))
+
+        def step():
+            out1 = torch.ops.torch_scatter.segment_sum_csr(src, indptr, None)
+            # upstream's Python scatter_sum: zeros + ATen scatter_add_ (torch_scatter/scatter.py:8-25)
+            idx = shuffled.view(-1, 1).expand(-1, src.size(1))
+            out2 = torch.zeros(rows, src.size(1)).scatter_add_(0, idx, src)
+            return out1, out2
+    else:
+        kind = 'port'
+        cores = 1
+        from oracle import oracle
+
+        def step():
+            out1 = oracle.segment_csr(src.view(1, nnz, -1), indptr.view(1, -1), 'sum')[0]
+            out2 = oracle.scatter(src.view(1, nnz, -1), shuffled.view(1, -1, 1), rows, 'sum')[0]
+            return out1, out2
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    b_csr, b_sc = algorithmic_bytes(rows, nnz)
+    value = (b_csr + b_sc) / dt / 1e9
+    sample = f'{rows} rows / {nnz} entries (1/{args.ref_fraction} of the workload), F={FEAT}, fp32'
+    line = {
+        'impl': 'reference', 'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': args.gpus,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dt * 1e3, 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': f'power-law CSR {ROWS} rows, F={FEAT}, fp32; reference arm timed on: {sample}',
+                   'threads': torch.get_num_threads()},
+        'cpu_baseline': {'value': value, 'unit': UNIT, 'cores': cores, 'kind': kind, 'sample': sample},
+        'e2e': {'value': value, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# -------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch.distributed as dist
+    import pytorch_scatter_b200 as ts
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    assert torch.cuda.is_available(), 'bench.py needs a CUDA device (no CPU fallback exists)'
+    torch.cuda.set_device(local_rank)
+    dev = torch.device('cuda', local_rank)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+
+    # weak scaling: every rank holds its own workload-sized shard (its own seed)
+    indptr_h, _, shuffled_h, src_h = make_workload(ROWS, SEED + 17 * rank)
+    nnz = src_h.size(0)
+    src_p, indptr_p, shuffled_p = src_h.pin_memory(), indptr_h.pin_memory(), shuffled_h.pin_memory()
+    src, indptr, shuffled = src_p.to(dev), indptr_p.to(dev), shuffled_p.to(dev)
+    out_csr = torch.empty(ROWS, FEAT, device=dev)
+    out_sc = torch.empty(ROWS, FEAT, device=dev)
+    rs_out = torch.empty(ROWS // world, FEAT, device=dev) if world > 1 else None
+
+    def step():
+        # CSR rows are independent: each rank reduces its own row range, no collective.
+        ts.segment_csr(src, indptr, out=out_csr, reduce='sum')
+        # Unsorted scatter shards the edge dimension: every rank reduces its edges into a full-length
+        # partial, then a reduce-scatter leaves each rank with its block of target rows.
+        out_sc.zero_()
+        ts.scatter(src, shuffled, dim=0, out=out_sc, reduce='sum')
+        if world > 1:
+            dist.reduce_scatter_tensor(rs_out, out_sc, op=dist.ReduceOp.SUM)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    sync_all()
+
+    sampler = ClockSampler(torch.cuda.current_device() if 'CUDA_VISIBLE_DEVICES' not in os.environ else
+                           int(os.environ['CUDA_VISIBLE_DEVICES'].split(',')[local_rank]))
+    if rank == 0:
+        sampler.start()
+    stream = torch.cuda.current_stream()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3 * args.steps + 1)]
+    ev[0].record(stream)
+    for i in range(args.steps):
+        ts.segment_csr(src, indptr, out=out_csr, reduce='sum')
+        ev[3 * i + 1].record(stream)
+        out_sc.zero_()
+        ts.scatter(src, shuffled, dim=0, out=out_sc, reduce='sum')
+        ev[3 * i + 2].record(stream)
+        if world > 1:
+            dist.reduce_scatter_tensor(rs_out, out_sc, op=dist.ReduceOp.SUM)
+        ev[3 * i + 3].record(stream)
+    sync_all()
+    clocks = sampler.stop() if rank == 0 else None
+
+    total_ms = ev[0].elapsed_time(ev[-1])
+    csr_ms = sum(ev[3 * i].elapsed_time(ev[3 * i + 1]) for i in range(args.steps)) / args.steps
+    sc_ms = sum(ev[3 * i + 1].elapsed_time(ev[3 * i + 2]) for i in range(args.steps)) / args.steps
+    coll_ms = sum(ev[3 * i + 2].elapsed_time(ev[3 * i + 3]) for i in range(args.steps)) / args.steps
+
+    # ---- end to end through the public API with host buffers: H2D of the step's inputs from pinned
+    # memory, both operators, D2H of both results, all inside the timed region
+    e2e_steps = max(1, min(args.steps, 5))
+    out_csr_h = torch.empty(ROWS, FEAT).pin_memory()
+    out_sc_h = torch.empty(ROWS, FEAT).pin_memory()
+
+    def e2e_step():
+        s = src_p.to(dev, non_blocking=True)
+        ip = indptr_p.to(dev, non_blocking=True)
+        ix = shuffled_p.to(dev, non_blocking=True)
+        o1 = ts.segment_csr(s, ip, reduce='sum')
+        o2 = ts.scatter(s, ix, dim=0, dim_size=ROWS, reduce='sum')
+        if world > 1:
+            dist.reduce_scatter_tensor(rs_out, o2, op=dist.ReduceOp.SUM)
+            out_sc_h[:ROWS // world].copy_(rs_out, non_blocking=True)
+        else:
+            out_sc_h.copy_(o2, non_blocking=True)
+        out_csr_h.copy_(o1, non_blocking=True)
+
+    e2e_step()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    sync_all()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    # ---- max over ranks
+    times = torch.tensor([total_ms, csr_ms, sc_ms, coll_ms, e2e_ms, float(nnz)], device=dev, dtype=torch.float64)
+    if world > 1:
+        gathered = [torch.empty_like(times) for _ in range(world)]
+        dist.all_gather(gathered, times)
+        allt = torch.stack(gathered)
+    else:
+        allt = times.unsqueeze(0)
+    total_ms, csr_ms, sc_ms, coll_ms, e2e_ms = [float(allt[:, i].max()) for i in range(5)]
+    nnz_all = [int(x) for x in allt[:, 5].tolist()]
+
+    if rank == 0:
+        b = [algorithmic_bytes(ROWS, n) for n in nnz_all]
+        b_csr, b_sc = sum(x[0] for x in b), sum(x[1] for x in b)
+        ms_per_step = total_ms / args.steps
+        value = (b_csr + b_sc) / (ms_per_step * 1e-3) / 1e9
+        peaks_path = osp.join(ROOT, 'MEASURED_PEAKS.json')
+        if osp.exists(peaks_path):
+            peak, peak_src = float(json.load(open(peaks_path))['hbm_gbs']), 'measured (MEASURED_PEAKS.json hbm_gbs)'
+        else:
+            peak, peak_src = 6650.0, 'fallback'
+        csr_gbs = b[0][0] / (csr_ms * 1e-3) / 1e9          # rank-0-sized launch over the slowest rank's time
+        sc_gbs = b[0][1] / (sc_ms * 1e-3) / 1e9
+        h2d = src_h.numel() * 4 + indptr_h.numel() * 8 + shuffled_h.numel() * 8
+        d2h = ROWS * FEAT * 4 + (ROWS // world) * FEAT * 4
+        line = {
+            'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
+            'warmup': args.warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+            'config': {'workload': f'power-law CSR: {ROWS} rows, {nnz_all[0]} entries per GPU (log-normal row '
+                                   f'lengths, mean 16, clip 20000, 8 rows forced to 20000), src fp32 [nnz x {FEAT}], '
+                                   'int64 indptr/index; step = segment_csr(sum) + scatter(sum, shuffled index)'
+                                   + (' + NCCL reduce-scatter of the scatter partial' if world > 1 else ''),
+                       'l2': 'inputs (4.3 GB) larger than L2, no flush needed',
+                       'parallelism': f'{world} x independent row shards (csr); edge shards + reduce-scatter (scatter)'},
+            'ops': {'segment_csr_sum': {'ms': csr_ms, 'GB/s': csr_gbs, 'frac_of_peak': csr_gbs / peak},
+                    'scatter_sum': {'ms': sc_ms, 'GB/s': sc_gbs, 'frac_of_peak': sc_gbs / peak},
+                    'reduce_scatter_ms': coll_ms},
+            'roofline': {'bound': 'hbm', 'kernel': 'csr_reduce_kernel<float,sum,4>', 'achieved': csr_gbs, 'peak': peak,
+                         'unit': 'GB/s', 'frac': csr_gbs / peak, 'traffic': CSR_KERNEL_DRAM_TRAFFIC_BYTES,
+                         'peak_source': peak_src, 'algorithmic_bytes_per_launch': b[0][0]},
+            'e2e': {'value': (b_csr + b_sc) / (e2e_ms * 1e-3) / 1e9, 'unit': UNIT, 'ms_per_step': e2e_ms,
+                    'steps': e2e_steps, 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h},
+            'gpu_launches': 2 * args.steps,
+            'clocks': clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line['cpu_baseline'] = cpu_baseline(args)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(args):
+    """Times the upstream CPU path in a child process (it registers the same operator names)."""
+    try:
+        p = subprocess.run([sys.executable, osp.abspath(__file__), '--impl', 'reference', '--steps', '3', '--warmup', '1',
+                            '--ref-fraction', str(args.ref_fraction)],
+                           stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900,
+                           env={k: v for k, v in os.environ.items() if k not in ('RANK', 'WORLD_SIZE', 'LOCAL_RANK')})
+        for ln in reversed(p.stdout.strip().splitlines()):
+            if ln.startswith('{'):
+                return json.loads(ln)['cpu_baseline']
+        return {'value': None, 'unit': UNIT, 'cores': None, 'kind': None, 'sample': 'failed: ' + p.stderr[-200:]}
+    except Exception as e:  # noqa: BLE001
+        return {'value': None, 'unit': UNIT, 'cores': None, 'kind': None, 'sample': f'failed: {e}'}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--ref-fraction', type=int, default=4, help='reference arm runs on 1/this of the rows')
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == 'ours':
+        args.warmup = 3
+    if args.impl == 'reference':
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == '__main__':
+    main()
