@@ -164,7 +164,8 @@ __global__ void __launch_bounds__(kThreads) scatter_rows_kernel(ScatterParams p)
   const T *srow = src + entry * p.K;
   U *trow = target + (b * p.N + idx) * p.K;
   for (int64_t c = col; c < Kv; c += L) apply_pack<OP, T, VEC>(trow + c * VEC, ld_stream<T, VEC>(srow + c * VEC));
-  if (p.count != nullptr && col == 0) atomicAdd(p.count + (p.sb ? b : 0) * p.N + idx, 1);
+  // one count per row of the index itself: a batch-broadcast index is counted for b == 0 only
+  if (p.count != nullptr && col == 0 && (p.sb != 0 || b == 0)) atomicAdd(p.count + (p.sb ? b : 0) * p.N + idx, 1);
 }
 
 template <typename T, int OP>
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(kThreads) scatter_elems_kernel(ScatterParams p
   const int64_t idx = p.index[b * p.sb + e * p.se + k * p.sk];
   if (idx < 0 || idx >= p.N) return;
   apply_one<OP, U>(target + (b * p.N + idx) * p.K + k, to_acc<T>(src[i]));
-  if (p.count != nullptr) atomicAdd(p.count + ((p.sb ? b : 0) * p.N + idx) * p.K + k, 1);
+  if (p.count != nullptr && (p.sb != 0 || b == 0)) atomicAdd(p.count + ((p.sb ? b : 0) * p.N + idx) * p.K + k, 1);
 }
 
 // ---- init / finalize ---------------------------------------------------------------------------
