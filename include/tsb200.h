@@ -61,10 +61,13 @@ int64_t tsb_cuda_version(void);
  *   out                  [B,N,K]; always overwritten (never accumulated into)
  *   arg_out              [B,N,K] int64, required for MIN/MAX, ignored otherwise; empty rows get E
  *   reduce               SUM, MEAN, MIN or MAX.  MEAN divides by max(count,1); empty rows give 0.
- * Deterministic: the summation order depends only on the shapes.  Needs no workspace. */
+ *   workspace            tsb_segment_csr_workspace_bytes(...) bytes, 256-byte aligned: partial rows at
+ *                        the borders of the entry chunks the reduction is balanced over
+ * Deterministic: the summation order depends only on the shapes. */
+size_t tsb_segment_csr_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce);
 int tsb_segment_csr(const void *src, const int64_t *indptr, void *out, int64_t *arg_out,
                     int64_t B, int64_t E, int64_t K, int64_t N, int64_t indptr_batch_stride,
-                    int dtype, int reduce, tsb_stream_t stream);
+                    int dtype, int reduce, void *workspace, size_t workspace_bytes, tsb_stream_t stream);
 
 /* gather_csr: out[b,e,:] = src[b,n,:] for e in [indptr[b,n], indptr[b,n+1]); positions no row covers
  * are left untouched.  Replaces gather_csr_cuda + kernels, csrc/cuda/segment_csr_cuda.cu:219-281,
@@ -85,10 +88,10 @@ int tsb_gather_csr(const void *src, const int64_t *indptr, void *out,
  *                        starts from its current value; unnamed rows are untouched
  *   arg_out              [B,N,K] int64 for MIN/MAX (always fully written; E where no element won)
  *   count_out            [B,N] of dtype, for MEAN: run length clamped to >= 1 (segment_coo_cpu.cpp:134-136)
- *   workspace            tsb_segment_coo_workspace_bytes(B,N) bytes, holds the row pointers rebuilt
- *                        from the sorted index.
+ *   workspace            tsb_segment_coo_workspace_bytes(...) bytes, 256-byte aligned: the row pointers
+ *                        rebuilt from the sorted index, then the scratch of the row-pointer reduction
  * Deterministic (no atomics). */
-size_t tsb_segment_coo_workspace_bytes(int64_t B, int64_t N);
+size_t tsb_segment_coo_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce);
 int tsb_segment_coo(const void *src, const int64_t *index, void *out, int64_t *arg_out, void *count_out,
                     int64_t B, int64_t E, int64_t K, int64_t N, int64_t index_batch_stride,
                     int dtype, int reduce, int out_seeded,

@@ -20,7 +20,12 @@ struct CsrParams {
   void *count_out;        // [B,N] of dtype or null (COO mean)
   int64_t B, E, K, N, bstride;
   int mode;
+  void *workspace;        // csr_reduce_workspace_bytes(...) bytes, 256-byte aligned
+  size_t workspace_bytes;
 };
+
+// Scratch for the partial rows at chunk borders (see segment_csr.cu).
+size_t csr_reduce_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce);
 
 // Picks the vector width / lane geometry from the shapes and launches.  Returns a tsb_status.
 int launch_csr_reduce(const CsrParams &p, int dtype, int reduce, cudaStream_t stream);

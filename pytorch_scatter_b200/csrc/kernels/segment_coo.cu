@@ -40,9 +40,15 @@ coo_rowptr_kernel(const int64_t *__restrict__ index, int64_t *__restrict__ rowpt
 }  // namespace
 }  // namespace tsb
 
-extern "C" size_t tsb_segment_coo_workspace_bytes(int64_t B, int64_t N) {
-  if (B < 0 || N < 0) return 0;
-  return (size_t)B * (size_t)(N + 1) * sizeof(int64_t);
+namespace {
+size_t rowptr_bytes(int64_t B, int64_t N) {
+  return (((size_t)B * (size_t)(N + 1) * sizeof(int64_t)) + 255) & ~(size_t)255;
+}
+}  // namespace
+
+extern "C" size_t tsb_segment_coo_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce) {
+  if (B < 0 || N < 0 || E < 0 || K < 0) return 0;
+  return rowptr_bytes(B, N) + tsb::csr_reduce_workspace_bytes(B, E, K, N, dtype, reduce);
 }
 
 extern "C" int tsb_segment_coo(const void *src, const int64_t *index, void *out, int64_t *arg_out,
@@ -53,11 +59,12 @@ extern "C" int tsb_segment_coo(const void *src, const int64_t *index, void *out,
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (B < 0 || E < 0 || K < 0 || N < 0) return TSB_ERR_ARG;
   if (B * N == 0) return TSB_OK;
-  if (workspace == nullptr || workspace_bytes < tsb_segment_coo_workspace_bytes(B, N)) return TSB_ERR_WORKSPACE;
+  if (workspace == nullptr || workspace_bytes < tsb_segment_coo_workspace_bytes(B, E, K, N, dtype, reduce)) return TSB_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return TSB_ERR_WORKSPACE;
   if (E > 0 && index == nullptr) return TSB_ERR_ARG;
   int64_t *rowptr = static_cast<int64_t *>(workspace);
   if (E == 0) {
-    if (cudaMemsetAsync(rowptr, 0, tsb_segment_coo_workspace_bytes(B, N), stream) != cudaSuccess) return TSB_ERR_LAUNCH;
+    if (cudaMemsetAsync(rowptr, 0, rowptr_bytes(B, N), stream) != cudaSuccess) return TSB_ERR_LAUNCH;
   } else {
     const int64_t blocks = (B * E + kThreads - 1) / kThreads;
     if (blocks > 2147483647LL) return TSB_ERR_TOO_LARGE;
@@ -73,5 +80,7 @@ extern "C" int tsb_segment_coo(const void *src, const int64_t *index, void *out,
   p.B = B; p.E = E; p.K = K; p.N = N;
   p.bstride = N + 1;
   p.mode = out_seeded ? kCooSeeded : kCooFresh;
+  p.workspace = static_cast<unsigned char *>(workspace) + rowptr_bytes(B, N);
+  p.workspace_bytes = workspace_bytes - rowptr_bytes(B, N);
   return launch_csr_reduce(p, dtype, reduce, stream);
 }

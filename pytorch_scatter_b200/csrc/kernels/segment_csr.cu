@@ -1,20 +1,23 @@
 // segment_csr for sm_100a: row-pointer segmented reduction of src [B,E,K] into out [B,N,K].
 //
-// The rows of a CSR matrix are contiguous in src, so a run of consecutive rows is one contiguous
-// byte stream.  Each warp owns a chunk of up to 31 consecutive rows and STREAMS their entries in
-// order, independent of where the row boundaries fall:
-//   * an entry (K contiguous elements) is covered by L lanes holding one 16-byte pack each, so a warp
-//     consumes 32/L entries (512 contiguous bytes for 16-byte packs) per step;
-//   * loads run D steps ahead of consumption through a register ring, so every warp keeps D*512
-//     bytes in flight no matter how short its rows are;
-//   * the row boundaries of the chunk live in registers (lane j holds indptr[first_row + j]); all
-//     control flow that depends on them is warp-uniform.  When one or more rows end inside a step,
-//     the lanes whose entry belongs to the closing row contribute to a shuffle butterfly and the
-//     row is written; the remaining lanes start the next row.
-// Rows of at least `long_len` entries (128 KiB of source) are cut out of the stream and reduced by a
-// second kernel whose 1024-thread CTAs scan the row pointers for them and put all 32 warps on one
-// row at a time, partials combined through shared memory in a fixed order.
-// Nothing is atomic: results depend only on the shapes, never on scheduling.
+// Merge-path style, balanced over ENTRIES rather than rows.  The rows of a CSR matrix are contiguous
+// in src, so the whole reduced dimension is one byte stream; it is cut into fixed chunks of C entries
+// (about 128 KiB) and every chunk is streamed by one warp (one single-warp CTA, so the hardware
+// scheduler balances them and a finished warp frees its slot at once):
+//   * the warp finds the first row that ends inside its chunk with a cooperative 32-ary search over
+//     the row pointers (4 rounds for a million rows);
+//   * an entry (K contiguous elements) is covered by L lanes holding one 16-byte pack each, so the
+//     warp consumes 32/L entries (512 contiguous bytes for 16-byte packs) per step; loads run D steps
+//     ahead of consumption through a register ring, so D*512 bytes stay in flight per warp no matter
+//     how short the rows are;
+//   * row boundaries live in registers, 31 rows at a time (lane j holds row pointer j of the window);
+//     all control flow that depends on them is warp-uniform.  When rows end inside a step, the lanes
+//     whose entry belongs to the closing row feed a shuffle butterfly and the row is written;
+//   * a row that straddles chunk borders is never written by the stream: the chunk where it ends
+//     stores a HEAD partial, every chunk it runs out of stores a TAIL partial (workspace), and a
+//     small fix-up kernel folds TAIL[c1..c2-1] and HEAD[c2] in a fixed order and writes the row.
+// A 20,000-entry row is thus spread over 40 warps, a million-entry row over 2,000.  Nothing is
+// atomic: results depend only on the shapes, never on scheduling.
 //
 // Replaces segment_csr_kernel / segment_csr_broadcast_kernel of the upstream project
 // (csrc/cuda/segment_csr_cuda.cu:15-95), which walk each row with a single thread per feature.
@@ -26,13 +29,39 @@ namespace tsb {
 
 namespace {
 
-constexpr int kMaxRowsPerWarp = 31;  // lane j holds boundary j, so rows+1 <= 32
+// Resident single-warp CTAs per SM the streaming kernel is compiled for (caps its registers).
+#ifndef TSB_CSR_MIN_BLOCKS
+#define TSB_CSR_MIN_BLOCKS 16
+#endif
+#ifndef TSB_CSR_DEPTH
+#define TSB_CSR_DEPTH 8
+#endif
+constexpr int kWindowRows = 31;          // lane j holds row pointer j of the window, so rows+1 <= 32
+constexpr int kRelInf = 0x3fffffff;      // "never ends inside this chunk"
+constexpr int64_t kChunkBytes = 128 * 1024;
 
 struct CsrGeom {
-  int l_log2;         // lanes per entry
-  int rows_per_warp;  // consecutive rows streamed by one warp (<= 31)
-  int64_t long_len;   // rows at least this long are reduced by the whole CTA
+  int l_log2;            // lanes per entry
+  int chunk_entries;     // C: entries per chunk (a power of two >= 32)
+  int64_t chunks;        // chunks per batch = max(1, ceil(E / C))
+  // workspace: per chunk two partial rows (HEAD, TAIL) of K accumulators, the same of int64 arg
+  // indices for MIN/MAX, and the id of the row whose HEAD partial the chunk stored (-1: none)
+  void *carry_val;
+  int64_t *carry_arg;
+  int64_t *head_row;
 };
+
+// Chunk length: a power of two holding about kChunkBytes of source, at least one full warp step.
+inline int chunk_entries_for(int64_t K, size_t elem) {
+  int64_t c = kChunkBytes / (K * (int64_t)elem);
+  if (const char *forced = std::getenv("TSB_CSR_CHUNK_ENTRIES")) {  // test hook: force short chunks
+    const long long v = std::atoll(forced);
+    if (v >= 32) c = v;
+  }
+  int64_t pow2 = 32;
+  while (pow2 * 2 <= c && pow2 < (1 << 20)) pow2 *= 2;
+  return (int)pow2;
+}
 
 template <typename T, int REDUCE, int VEC> struct RowAcc {
   using A = acc_t<T>;
@@ -142,11 +171,9 @@ __device__ __forceinline__ void write_row(const RowAcc<T, REDUCE, VEC> &acc, T *
   st_pack<T, VEC>(out_p, o);
 }
 
-// Kernel A: one warp per CTA streams a chunk of consecutive rows (long rows are skipped here).
-// Single-warp CTAs let the hardware scheduler balance chunks of very different sizes: a warp that
-// finishes early frees its slot at once instead of idling until its CTA's slowest warp is done.
+// Streaming kernel: blockIdx.x = (batch, chunk); one warp.
 template <typename T, int REDUCE, int VEC, int D>
-__global__ void __launch_bounds__(32) csr_stream_kernel(CsrParams p, CsrGeom g) {
+__global__ void __launch_bounds__(32, TSB_CSR_MIN_BLOCKS) csr_stream_kernel(CsrParams p, CsrGeom g) {
   using A = acc_t<T>;
   using Acc = RowAcc<T, REDUCE, VEC>;
   constexpr bool kArg = Acc::kArg;
@@ -161,277 +188,297 @@ __global__ void __launch_bounds__(32) csr_stream_kernel(CsrParams p, CsrGeom g) 
   const int eps = 32 >> g.l_log2;
   const int64_t Kv = p.K / VEC;
 
-  const int RW = g.rows_per_warp;
-  const int64_t chunks_per_batch = (p.N + RW - 1) / RW;
-  const int64_t chunk = blockIdx.x;
-  const int64_t b = chunk / chunks_per_batch;
-  const int64_t n0 = (chunk - b * chunks_per_batch) * RW;
-  const int nrows = (int)((p.N - n0) < RW ? (p.N - n0) : RW);
-  const int64_t *ip = p.indptr + b * p.bstride + n0;
+  const int64_t chunk_id = blockIdx.x;
+  const int64_t b = chunk_id / g.chunks;
+  const int64_t w = chunk_id - b * g.chunks;
+  const int64_t cs = w * g.chunk_entries;
+  const int64_t ce = (cs + g.chunk_entries < p.E) ? cs + g.chunk_entries : p.E;
+  const int t = (int)(ce - cs);
+  const int64_t *ip = p.indptr + b * p.bstride;
 
-  // lane j holds boundary j of the chunk (clamped and made monotone, so that bad row pointers can
-  // never take a load or a store out of bounds); lanes past nrows repeat the last boundary
-  int64_t bnd = (lane <= nrows) ? clamp64(ip[lane], 0, p.E) : 0;
-#pragma unroll
-  for (int off = 1; off < 32; off <<= 1) {
-    const int64_t o = (int64_t)__shfl_up_sync(kFullMask, (long long)bnd, off);
-    if (lane >= off && o > bnd) bnd = o;
+  // ---- first row that ends after cs: 32-ary search over ends[r] = indptr[r + 1] -----------------
+  int64_t r_first = 0;
+  if (w > 0) {
+    int64_t lo = 0, hi = p.N;  // answer in [lo, hi]; hi == N means "no such row"
+    while (hi - lo > 32) {
+      const int64_t step = (hi - lo + 31) / 32;
+      int64_t probe = lo + (lane + 1) * step - 1;
+      if (probe > hi - 1) probe = hi - 1;
+      const unsigned gt = __ballot_sync(kFullMask, ip[probe + 1] > cs);
+      if (gt == 0) { lo = hi; break; }
+      const int f = __ffs((int)gt) - 1;
+      const int64_t new_hi = lo + (int64_t)(f + 1) * step - 1;
+      lo = lo + (int64_t)f * step;
+      hi = new_hi < hi - 1 ? new_hi : hi - 1;  // ends[hi] > cs is known: the answer is <= hi
+      if (hi < lo) hi = lo;
+    }
+    if (lo < p.N) {
+      const bool in = lo + lane <= hi && lo + lane < p.N;
+      const unsigned gt = __ballot_sync(kFullMask, in && ip[lo + lane + 1] > cs);
+      r_first = gt ? lo + (__ffs((int)gt) - 1) : hi;  // ends[hi] > cs is known (or hi == N: no such row)
+    } else {
+      r_first = p.N;
+    }
   }
-  const int64_t next_bnd = (int64_t)__shfl_down_sync(kFullMask, (long long)bnd, 1);
-  const unsigned long_mask = __ballot_sync(kFullMask, lane < nrows && (next_bnd - bnd) >= g.long_len);
 
   const T *bsrc = src + (b * p.E) * p.K;
-  const int64_t row0 = b * p.N + n0;
   const int64_t step_stride = (int64_t)eps * p.K;  // elements between consecutive steps of a lane
 
   Pack<T, VEC> fill;  // what a lane without an entry holds: the identity, so that it never matters
 #pragma unroll
   for (int i = 0; i < VEC; ++i) fill.v[i] = from_acc<T>(reduce_identity<T, REDUCE>());
 
+  A *carry = static_cast<A *>(g.carry_val) + chunk_id * 2 * p.K;
+  int64_t *carry_arg = kArg ? g.carry_arg + chunk_id * 2 * p.K : nullptr;
+
   for (int64_t cb = 0; cb < Kv; cb += L) {
     const int64_t c = cb + col;
     const bool col_ok = c < Kv;
-    T *obase = out + row0 * p.K + c * VEC;
-    int64_t *abase = kArg ? p.arg_out + row0 * p.K + c * VEC : nullptr;
 
-    int ra = 0;
-    while (ra < nrows) {  // one iteration per maximal run of non-long rows
-      const unsigned rest = long_mask >> ra;
-      if (rest & 1u) { ++ra; continue; }
-      const int rb = rest ? ra + (__ffs((int)rest) - 1) : nrows;
-      const int64_t s = (int64_t)__shfl_sync(kFullMask, (long long)bnd, ra);
-      // boundaries of this run relative to its first entry: < 31 * long_len, fits 32 bits
-      const int64_t rel64 = bnd - s;
-      const int rel = rel64 < 0 ? 0 : (rel64 > 0x3fffffff ? 0x3fffffff : (int)rel64);
-      const int t = __shfl_sync(kFullMask, rel, rb);
+    // ---- window of row pointers: lane j holds pointer j of rows [r_win, r_win + 31) -------------
+    int64_t r_win = r_first;
+    int rel = 0;            // this lane's pointer relative to cs, clamped to [0, kRelInf]
+    bool head_pending = false;
+    auto load_window = [&]() {
+      const int64_t r = r_win + lane;
+      int64_t v = (r <= p.N) ? ip[r] : (int64_t)1 << 62;
+      if (lane == 0 && r_win == r_first) head_pending = (w > 0) && (r < p.N) && (v < cs);
+      v -= cs;
+      rel = v < 0 ? 0 : (v > kRelInf ? kRelInf : (int)v);
+      if (r > p.N) rel = kRelInf;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {  // monotone, so that bad pointers stay harmless
+        const int o = __shfl_up_sync(kFullMask, rel, off);
+        if (lane >= off && o > rel) rel = o;
+      }
+    };
+    load_window();
+    head_pending = __shfl_sync(kFullMask, (int)head_pending, 0) != 0;
 
-      int cur = ra;
-      int cur_start = 0;
-      int cur_end = __shfl_sync(kFullMask, rel, ra + 1);
-      Acc acc;
-      acc.init(p.E);
+    int cur = 0;  // row r_win + cur is open: entries [cur_start, cur_end) relative to cs
+    int cur_start = __shfl_sync(kFullMask, rel, 0);
+    int cur_end = __shfl_sync(kFullMask, rel, 1);
+    if (r_win >= p.N) { cur_start = kRelInf; cur_end = kRelInf; }
+    Acc acc;
+    acc.init(p.E);
 
-      // Closes every row that ends at or before `step_end`; `v` is this lane's entry `e` of the step.
-      auto close_rows = [&](const Pack<T, VEC> &v, int e, int step_end) {
-        while (cur < rb && cur_end <= step_end) {
-          Acc tot = acc;
-          if (e >= cur_start && e < cur_end) tot.update(v, s + e);
-          tot.butterfly(L, 32);
+    // Closes every row that ends at or before `step_end`; `v` is this lane's entry `e` of the step.
+    auto close_rows = [&](const Pack<T, VEC> &v, int e, int step_end) {
+      while (cur_end <= step_end) {
+        Acc tot = acc;
+        if (e >= cur_start && e < cur_end) tot.update(v, cs + e);
+        tot.butterfly(L, 32);
+        const int64_t row = r_win + cur;
+        if (head_pending) {
+          // the row started in an earlier chunk: leave its last piece for the fix-up kernel
           if (sub == 0 && col_ok) {
-            write_row<T, REDUCE, VEC>(tot, obase + (int64_t)cur * p.K, kArg ? abase + (int64_t)cur * p.K : nullptr,
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+              carry[c * VEC + i] = tot.val[i];
+              if (kArg) carry_arg[c * VEC + i] = tot.arg[i];
+            }
+          }
+          if (lane == 0 && cb == 0) g.head_row[chunk_id] = row;
+          head_pending = false;
+        } else {
+          const int64_t grow = b * p.N + row;
+          if (sub == 0 && col_ok) {
+            write_row<T, REDUCE, VEC>(tot, out + grow * p.K + c * VEC, kArg ? p.arg_out + grow * p.K + c * VEC : nullptr,
                                       (int64_t)(cur_end - cur_start), p.mode, p.E);
           }
           if (lane == 0 && cb == 0 && p.count_out != nullptr) {
             const int len = cur_end - cur_start;
-            static_cast<T *>(p.count_out)[row0 + cur] = from_acc<T>((A)(len > 0 ? len : 1));
+            static_cast<T *>(p.count_out)[grow] = from_acc<T>((A)(len > 0 ? len : 1));
           }
-          acc.init(p.E);
-          ++cur;
-          cur_start = cur_end;
-          cur_end = __shfl_sync(kFullMask, rel, cur + 1 <= nrows ? cur + 1 : nrows);
         }
-      };
+        acc.init(p.E);
+        ++cur;
+        if (cur == kWindowRows) {
+          r_win += kWindowRows;
+          cur = 0;
+          load_window();
+        }
+        cur_start = cur_end;
+        cur_end = __shfl_sync(kFullMask, rel, cur + 1);
+        if (r_win + cur >= p.N) cur_end = kRelInf;  // past the last row: nothing more closes
+      }
+    };
 
-      const T *next_ptr = bsrc + (s + sub) * p.K + c * VEC;
-      int next_rel = sub;
-      Pack<T, VEC> ring[D];
+    if (lane == 0 && cb == 0) g.head_row[chunk_id] = -1;
+
+    const T *next_ptr = bsrc + (cs + sub) * p.K + c * VEC;
+    int next_rel = sub;
+    Pack<T, VEC> ring[D];
+#pragma unroll
+    for (int j = 0; j < D; ++j) {
+      ring[j] = (col_ok && next_rel < t) ? ld_stream<T, VEC>(next_ptr) : fill;
+      next_ptr += step_stride;
+      next_rel += eps;
+    }
+    for (int pos0 = 0; pos0 < t; pos0 += D * eps) {
 #pragma unroll
       for (int j = 0; j < D; ++j) {
-        ring[j] = (col_ok && next_rel < t) ? ld_stream<T, VEC>(next_ptr) : fill;
-        next_ptr += step_stride;
-        next_rel += eps;
-      }
-      for (int pos0 = 0; pos0 < t; pos0 += D * eps) {
-#pragma unroll
-        for (int j = 0; j < D; ++j) {
-          const int pos = pos0 + j * eps;
-          if (pos < t) {  // warp-uniform
-            const Pack<T, VEC> v = ring[j];
-            ring[j] = (col_ok && next_rel < t) ? ld_stream<T, VEC>(next_ptr) : fill;
-            next_ptr += step_stride;
-            next_rel += eps;
-            const int e = pos + sub;
-            const int step_end = (pos + eps < t) ? pos + eps : t;
-            if (cur_end <= step_end) {
-              close_rows(v, e, step_end);
-              if (e >= cur_start) acc.update(v, s + e);  // the row still open after this step
-            } else {
-              acc.update(v, s + e);
-            }
-          }
+        const int pos = pos0 + j * eps;
+        if (pos < t) {  // warp-uniform
+          const Pack<T, VEC> v = ring[j];
+          ring[j] = (col_ok && next_rel < t) ? ld_stream<T, VEC>(next_ptr) : fill;
+          next_ptr += step_stride;
+          next_rel += eps;
+          const int e = pos + sub;
+          const int step_end = (pos + eps < t) ? pos + eps : t;
+          if (cur_end <= step_end) close_rows(v, e, step_end);
+          if (e >= cur_start) acc.update(v, cs + e);  // the row still open after this step
         }
       }
-      // rows without any entry at the end of the run (or a run with no entries at all)
-      close_rows(fill, t, t);
-      ra = rb;
+    }
+    // rows that end exactly at the chunk's end, including rows without entries there
+    close_rows(fill, t, t);
+
+    // the row still open runs on into the next chunk: store what this chunk holds of it
+    if (r_win + cur < p.N && cur_start < t) {
+      acc.butterfly(L, 32);
+      if (sub == 0 && col_ok) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          carry[p.K + c * VEC + i] = acc.val[i];
+          if (kArg) carry_arg[p.K + c * VEC + i] = acc.arg[i];
+        }
+      }
     }
   }
 }
 
-// Kernel B: rows of at least long_len entries, skipped by kernel A.  Every CTA scans a block of rows
-// for long ones (the row pointers are L2-resident after kernel A) and reduces each with all its
-// warps striding over the row; per-warp partials are folded through shared memory in warp order.
-constexpr int kLongThreads = 1024;
-constexpr int kLongWarps = kLongThreads / 32;
-
-template <typename T, int REDUCE, int VEC, int U>
-__global__ void __launch_bounds__(kLongThreads) csr_long_rows_kernel(CsrParams p, CsrGeom g) {
+// Fix-up kernel: one warp per chunk.  If the chunk closed a row that began in an earlier chunk,
+// fold the TAIL partials of the chunks the row ran through and this chunk's HEAD partial, in a
+// fixed order, and write the row.
+template <typename T, int REDUCE, int VEC>
+__global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeom g) {
   using A = acc_t<T>;
   using Acc = RowAcc<T, REDUCE, VEC>;
   constexpr bool kArg = Acc::kArg;
-
-  const T *__restrict__ src = static_cast<const T *>(p.src);
   T *__restrict__ out = static_cast<T *>(p.out);
-
   const int L = 1 << g.l_log2;
-  const int tid = threadIdx.x;
-  const int warp = tid >> 5, lane = tid & 31;
+  const int lane = threadIdx.x & 31;
   const int col = lane & (L - 1);
   const int sub = lane >> g.l_log2;
   const int eps = 32 >> g.l_log2;
   const int64_t Kv = p.K / VEC;
-  const int64_t total_rows = p.B * p.N;
-
-  __shared__ int64_t s_long[kLongThreads];
-  __shared__ int s_nlong;
-  extern __shared__ __align__(16) unsigned char s_dyn[];
-  A *s_val = reinterpret_cast<A *>(s_dyn);                                                  // [kLongWarps][32*VEC]
-  int64_t *s_arg = reinterpret_cast<int64_t *>(s_dyn + sizeof(A) * kLongWarps * 32 * VEC);  // same shape, kArg only
-
-  if (tid == 0) s_nlong = 0;
-  __syncthreads();
-  const int64_t row = (int64_t)blockIdx.x * kLongThreads + tid;
-  if (row < total_rows) {
-    const int64_t b = row / p.N;
-    const int64_t *ip = p.indptr + b * p.bstride + (row - b * p.N);
-    const int64_t rs = clamp64(ip[0], 0, p.E);
-    const int64_t re = clamp64(ip[1], rs, p.E);
-    if (re - rs >= g.long_len) s_long[atomicAdd(&s_nlong, 1)] = row;
+  const int64_t chunk_id = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  if (chunk_id >= p.B * g.chunks) return;
+  const int64_t row = g.head_row[chunk_id];
+  if (row < 0 || row >= p.N) return;
+  const int64_t b = chunk_id / g.chunks;
+  const int64_t w = chunk_id - b * g.chunks;
+  const int64_t *ip = p.indptr + b * p.bstride + row;
+  const int64_t rs = clamp64(ip[0], 0, p.E);
+  const int64_t re = clamp64(ip[1], rs, p.E);
+  int64_t c1 = rs / g.chunk_entries;
+  if (c1 > w) c1 = w;
+  const A *carry = static_cast<const A *>(g.carry_val);
+  const int64_t grow = b * p.N + row;
+  for (int64_t cb = 0; cb < Kv; cb += L) {
+    const int64_t c = cb + col;
+    const bool col_ok = c < Kv;
+    Acc acc;
+    acc.init(p.E);
+    if (col_ok) {
+      for (int64_t cc = c1 + sub; cc < w; cc += eps) {  // TAIL partials of the chunks run through
+        const int64_t at = ((b * g.chunks + cc) * 2 + 1) * p.K + c * VEC;
+        A oval[VEC];
+        int64_t oarg[kArg ? VEC : 1];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          oval[i] = carry[at + i];
+          if (kArg) oarg[i] = g.carry_arg[at + i];
+        }
+        acc.merge(oval, oarg);
+      }
+    }
+    acc.butterfly(L, 32);
+    if (sub == 0 && col_ok) {
+      const int64_t at = (chunk_id * 2) * p.K + c * VEC;  // this chunk's HEAD partial
+      A oval[VEC];
+      int64_t oarg[kArg ? VEC : 1];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        oval[i] = carry[at + i];
+        if (kArg) oarg[i] = g.carry_arg[at + i];
+      }
+      acc.merge(oval, oarg);
+      write_row<T, REDUCE, VEC>(acc, out + grow * p.K + c * VEC, kArg ? p.arg_out + grow * p.K + c * VEC : nullptr,
+                                re - rs, p.mode, p.E);
+    }
   }
-  __syncthreads();
-  const int nlong = s_nlong;
-  if (nlong == 0) return;
-
-  const int64_t stride = (int64_t)kLongWarps * eps;
-  for (int i = 0; i < nlong; ++i) {
-    const int64_t lrow = s_long[i];
-    const int64_t lb = lrow / p.N;
-    const int64_t *ip = p.indptr + lb * p.bstride + (lrow - lb * p.N);
-    const int64_t lrs = clamp64(ip[0], 0, p.E);
-    const int64_t lre = clamp64(ip[1], lrs, p.E);
-    const int64_t llen = lre - lrs;
-    for (int64_t cb = 0; cb < Kv; cb += L) {
-      const int64_t c = cb + col;
-      const bool col_ok = c < Kv;
-      Acc acc;
-      acc.init(p.E);
-      const T *base = src + (lb * p.E) * p.K + c * VEC;
-      if (col_ok) {
-        int64_t e = lrs + (int64_t)warp * eps + sub;
-        for (; e + (U - 1) * stride < lre; e += U * stride) {
-          Pack<T, VEC> v[U];
-#pragma unroll
-          for (int u = 0; u < U; ++u) v[u] = ld_stream<T, VEC>(base + (e + u * stride) * p.K);
-#pragma unroll
-          for (int u = 0; u < U; ++u) acc.update(v[u], e + u * stride);
-        }
-        for (; e < lre; e += stride) acc.update(ld_stream<T, VEC>(base + e * p.K), e);
-      }
-      acc.butterfly(L, 32);
-      if (sub == 0) {
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) {
-          s_val[warp * 32 * VEC + col * VEC + k] = acc.val[k];
-          if (kArg) s_arg[warp * 32 * VEC + col * VEC + k] = acc.arg[k];
-        }
-      }
-      __syncthreads();
-      if (warp == 0 && sub == 0) {
-        // warp 0 already holds its own partial in acc; fold in the other warps in order
-        for (int w = 1; w < kLongWarps; ++w) {
-          A oval[VEC];
-          int64_t oarg[kArg ? VEC : 1];
-#pragma unroll
-          for (int k = 0; k < VEC; ++k) {
-            oval[k] = s_val[w * 32 * VEC + col * VEC + k];
-            if (kArg) oarg[k] = s_arg[w * 32 * VEC + col * VEC + k];
-          }
-          acc.merge(oval, oarg);
-        }
-        if (col_ok) {
-          write_row<T, REDUCE, VEC>(acc, out + lrow * p.K + c * VEC,
-                                    kArg ? p.arg_out + lrow * p.K + c * VEC : nullptr, llen, p.mode, p.E);
-        }
-      }
-      __syncthreads();
-    }
-    if (tid == 0 && p.count_out != nullptr) {
-      static_cast<T *>(p.count_out)[lrow] = from_acc<T>((A)(llen > 0 ? llen : 1));
-    }
+  if (lane == 0 && p.count_out != nullptr) {
+    static_cast<T *>(p.count_out)[grow] = from_acc<T>((A)(re - rs > 0 ? re - rs : 1));
   }
 }
 
-int64_t env_int(const char *name, int64_t fallback) {
-  const char *s = std::getenv(name);
-  if (s == nullptr || *s == '\0') return fallback;
-  char *end = nullptr;
-  const long long v = std::strtoll(s, &end, 10);
-  return (end != nullptr && *end == '\0') ? (int64_t)v : fallback;
+size_t carry_bytes(int64_t total_chunks, int64_t K, size_t acc_size, bool with_arg, size_t *arg_off, size_t *row_off) {
+  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  size_t off = up((size_t)total_chunks * 2 * (size_t)K * acc_size);
+  *arg_off = off;
+  if (with_arg) off += up((size_t)total_chunks * 2 * (size_t)K * sizeof(int64_t));
+  *row_off = off;
+  off += up((size_t)total_chunks * sizeof(int64_t));
+  return off;
 }
 
 template <typename T, int REDUCE, int VEC>
-int launch_vec(const CsrParams &p, cudaStream_t stream) {
-  using A = acc_t<T>;
+int launch_vec(const CsrParams &p, CsrGeom g, cudaStream_t stream) {
   constexpr bool kArg = (REDUCE == kMin || REDUCE == kMax);
-  constexpr int kDepth = kArg ? 4 : 8;   // load ring depth: 8 steps (4 KiB per warp) in flight for sums
-  constexpr int kUnroll = kArg ? 2 : 4;  // loads in flight per thread in the long-row kernel
+  constexpr int kDepth = kArg ? 4 : TSB_CSR_DEPTH;  // load ring depth: 8 steps (4 KiB per warp) in flight for sums
   const int64_t Kv = p.K / VEC;
-
-  CsrGeom g;
   g.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
-  // Chunk size: rows holding about 128 KiB of source on average, between 4 and 31 rows.
-  const int64_t avg = p.N > 0 ? (p.E + p.N - 1) / p.N : 1;
-  const int64_t row_bytes = (avg > 0 ? avg : 1) * p.K * (int64_t)sizeof(T);
-  int64_t rw = (128 * 1024) / row_bytes;
-  if (rw < 4) rw = 4;
-  rw = env_int("TSB_CSR_ROWS_PER_WARP", rw);  // test hook
-  if (rw < 1) rw = 1;
-  if (rw > kMaxRowsPerWarp) rw = kMaxRowsPerWarp;
-  g.rows_per_warp = (int)rw;
-  // A row leaves the stream for the whole-CTA kernel once it holds 128 KiB of source data.
-  const int64_t long_bytes = env_int("TSB_CSR_LONG_BYTES", 128 * 1024);  // test hook
-  const int64_t long_len = long_bytes / (p.K * (int64_t)sizeof(T));
-  g.long_len = long_len < 1 ? 1 : long_len;
-
-  const int64_t chunks = p.B * ((p.N + g.rows_per_warp - 1) / g.rows_per_warp);
-  if (chunks > 2147483647LL) return TSB_ERR_TOO_LARGE;
-  csr_stream_kernel<T, REDUCE, VEC, kDepth><<<(unsigned)chunks, 32, 0, stream>>>(p, g);
-
-  // no row can reach long_len when the whole reduced dimension is shorter
-  if (p.E >= g.long_len) {
-    const size_t dyn = (size_t)kLongWarps * 32 * VEC * (sizeof(A) + (kArg ? sizeof(int64_t) : 0));
-    static bool attr_set = false;  // per instantiation; the value never changes
-    if (dyn > 48 * 1024 && !attr_set) {
-      if (cudaFuncSetAttribute(csr_long_rows_kernel<T, REDUCE, VEC, kUnroll>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn) != cudaSuccess)
-        return TSB_ERR_LAUNCH;
-      attr_set = true;
-    }
-    const int64_t blocks = (p.B * p.N + kLongThreads - 1) / kLongThreads;
-    csr_long_rows_kernel<T, REDUCE, VEC, kUnroll><<<(unsigned)blocks, kLongThreads, dyn, stream>>>(p, g);
+  const int64_t total_chunks = p.B * g.chunks;
+  if (total_chunks > 2147483647LL) return TSB_ERR_TOO_LARGE;
+  csr_stream_kernel<T, REDUCE, VEC, kDepth><<<(unsigned)total_chunks, 32, 0, stream>>>(p, g);
+  if (g.chunks > 1) {  // a single chunk per batch cannot split a row
+    const int64_t blocks = (total_chunks + (kThreads / 32) - 1) / (kThreads / 32);
+    csr_fixup_kernel<T, REDUCE, VEC><<<(unsigned)blocks, kThreads, 0, stream>>>(p, g);
   }
   return launch_status();
 }
 
 template <typename T, int REDUCE>
 int launch_typed(const CsrParams &p, cudaStream_t stream) {
+  using A = acc_t<T>;
   constexpr int kFull = full_vec<T>();
+  constexpr bool kArg = (REDUCE == kMin || REDUCE == kMax);
   if (p.B * p.N == 0) return TSB_OK;
+  CsrGeom g;
+  g.l_log2 = 0;
+  g.chunk_entries = chunk_entries_for(p.K, sizeof(T));
+  g.chunks = (p.E + g.chunk_entries - 1) / g.chunk_entries;
+  if (g.chunks < 1) g.chunks = 1;
+  size_t arg_off = 0, row_off = 0;
+  const size_t need = carry_bytes(p.B * g.chunks, p.K, sizeof(A), kArg, &arg_off, &row_off);
+  if (p.workspace == nullptr || p.workspace_bytes < need || (reinterpret_cast<uintptr_t>(p.workspace) & 255u)) return TSB_ERR_WORKSPACE;
+  unsigned char *ws = static_cast<unsigned char *>(p.workspace);
+  g.carry_val = ws;
+  g.carry_arg = reinterpret_cast<int64_t *>(ws + arg_off);
+  g.head_row = reinterpret_cast<int64_t *>(ws + row_off);
   const bool vec_ok = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.out);
-  return vec_ok ? launch_vec<T, REDUCE, kFull>(p, stream) : launch_vec<T, REDUCE, 1>(p, stream);
+  return vec_ok ? launch_vec<T, REDUCE, kFull>(p, g, stream) : launch_vec<T, REDUCE, 1>(p, g, stream);
 }
 
 }  // namespace
+
+size_t csr_reduce_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce) {
+  (void)N;
+  if (B <= 0 || K <= 0 || E < 0) return 256;
+  size_t elem = 4, acc = 4;
+  switch (dtype) {
+    case TSB_F64: case TSB_I64: elem = 8; acc = 8; break;
+    case TSB_F16: case TSB_BF16: elem = 2; acc = 4; break;
+    default: break;
+  }
+  const int c = chunk_entries_for(K, elem);
+  int64_t chunks = (E + c - 1) / c;
+  if (chunks < 1) chunks = 1;
+  size_t a = 0, r = 0;
+  return carry_bytes(B * chunks, K, acc, reduce == TSB_MIN || reduce == TSB_MAX, &a, &r);
+}
 
 int launch_csr_reduce(const CsrParams &p, int dtype, int reduce, cudaStream_t stream) {
   if (p.B < 0 || p.E < 0 || p.K < 0 || p.N < 0) return TSB_ERR_ARG;
@@ -452,9 +499,14 @@ int launch_csr_reduce(const CsrParams &p, int dtype, int reduce, cudaStream_t st
 
 }  // namespace tsb
 
+extern "C" size_t tsb_segment_csr_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce) {
+  return tsb::csr_reduce_workspace_bytes(B, E, K, N, dtype, reduce);
+}
+
 extern "C" int tsb_segment_csr(const void *src, const int64_t *indptr, void *out, int64_t *arg_out,
                                int64_t B, int64_t E, int64_t K, int64_t N, int64_t indptr_batch_stride,
-                               int dtype, int reduce, tsb_stream_t stream) {
+                               int dtype, int reduce, void *workspace, size_t workspace_bytes,
+                               tsb_stream_t stream) {
   tsb::CsrParams p;
   p.src = src;
   p.indptr = indptr;
@@ -464,5 +516,7 @@ extern "C" int tsb_segment_csr(const void *src, const int64_t *indptr, void *out
   p.B = B; p.E = E; p.K = K; p.N = N;
   p.bstride = indptr_batch_stride;
   p.mode = tsb::kCsr;
+  p.workspace = workspace;
+  p.workspace_bytes = workspace_bytes;
   return tsb::launch_csr_reduce(p, dtype, reduce, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -69,7 +69,7 @@ segment_coo_fw(torch::Tensor src, torch::Tensor index, std::optional<torch::Tens
   const int64_t N = out.size(dim);
   if (out.numel() > 0) {
     BatchedRows rows = batched_rows(index);
-    const size_t ws_bytes = tsb_segment_coo_workspace_bytes(B, N);
+    const size_t ws_bytes = tsb_segment_coo_workspace_bytes(B, E, K, N, dtype_enum(src), red);
     auto workspace = torch::empty({(int64_t)ws_bytes}, src.options().dtype(torch::kUInt8));
     check_status(tsb_segment_coo(src.data_ptr(), rows.ptr(), out.data_ptr(),
                                  minmax ? arg_out.value().data_ptr<int64_t>() : nullptr,

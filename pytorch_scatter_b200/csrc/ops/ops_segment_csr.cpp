@@ -55,9 +55,12 @@ segment_csr_fw(torch::Tensor src, torch::Tensor indptr, std::optional<torch::Ten
   const int64_t E = src.size(dim);
   const int64_t K = (B * N) > 0 ? out.numel() / (B * N) : 0;
   BatchedRows rows = batched_rows(indptr);
+  const size_t ws_bytes = tsb_segment_csr_workspace_bytes(B, E, K, N, dtype_enum(src), red);
+  auto workspace = torch::empty({(int64_t)ws_bytes}, src.options().dtype(torch::kUInt8));
   check_status(tsb_segment_csr(src.data_ptr(), rows.ptr(), out.data_ptr(),
                                minmax ? arg_out.value().data_ptr<int64_t>() : nullptr, B, E, K, N,
-                               rows.batch_stride, dtype_enum(src), red, current_stream()),
+                               rows.batch_stride, dtype_enum(src), red, workspace.data_ptr(), ws_bytes,
+                               current_stream()),
                "tsb_segment_csr");
   if (copy_back) {
     optional_out.value().copy_(out);

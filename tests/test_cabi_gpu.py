@@ -1,0 +1,229 @@
+"""GPU parity proper: the C ABI of libtsb200.so against the C oracle on seeded inputs.
+
+Integers, MIN/MAX values and arg indices must be bit-exact; float SUM/MEAN within rtol 1e-5 (fp32) /
+1e-2 (fp16, bf16), atol as in helpers.TOL.  Sizes are chosen so that the oracle finishes in seconds
+while every kernel variant runs: short chunks are forced so that rows straddle many chunk borders.
+"""
+import itertools
+import os
+
+import pytest
+import torch
+
+import cabi
+from helpers import assert_close
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.float64, torch.float16, torch.bfloat16, torch.int32, torch.int64]
+
+
+def rand_src(gen, shape, dtype):
+    if dtype.is_floating_point:
+        return torch.randn(shape, generator=gen, dtype=torch.float32).to(dtype)
+    return torch.randint(-9, 10, shape, generator=gen).to(dtype)
+
+
+def row_lengths(gen, rows, kind):
+    if kind == 'lognormal':  # the benchmark's shape: many empty rows, a heavy tail
+        lens = torch.exp(1.7 + 1.5 * torch.randn(rows, generator=gen)).floor().clamp_(0, 3000).long()
+    elif kind == 'uniform':
+        lens = torch.randint(0, 9, (rows,), generator=gen)
+    elif kind == 'giant':    # one row holds nearly everything, the rest are empty or tiny
+        lens = torch.randint(0, 2, (rows,), generator=gen)
+        lens[rows // 3] = 5000
+    elif kind == 'empty_ends':
+        lens = torch.randint(1, 40, (rows,), generator=gen)
+        lens[:40] = 0
+        lens[-70:] = 0
+    else:
+        raise ValueError(kind)
+    return lens
+
+
+@pytest.fixture(params=[None, 32, 64], ids=['chunk-default', 'chunk-32', 'chunk-64'])
+def chunk(request):
+    old = os.environ.get('TSB_CSR_CHUNK_ENTRIES')
+    if request.param is None:
+        os.environ.pop('TSB_CSR_CHUNK_ENTRIES', None)
+    else:
+        os.environ['TSB_CSR_CHUNK_ENTRIES'] = str(request.param)
+    yield request.param
+    if old is None:
+        os.environ.pop('TSB_CSR_CHUNK_ENTRIES', None)
+    else:
+        os.environ['TSB_CSR_CHUNK_ENTRIES'] = old
+
+
+@pytest.mark.parametrize('kind', ['lognormal', 'uniform', 'giant', 'empty_ends'])
+@pytest.mark.parametrize('K', [1, 2, 3, 4, 16, 33, 64, 130])
+def test_segment_csr_and_coo(chunk, kind, K):
+    gen = torch.Generator().manual_seed(1000 + K)
+    rows = 300
+    lens = row_lengths(gen, rows, kind)
+    indptr = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)]).view(1, -1)
+    E = int(indptr[0, -1])
+    index = torch.repeat_interleave(torch.arange(rows), lens).view(1, -1)
+    dtypes = DTYPES if K in (1, 4, 64) else [torch.float32, torch.int64, torch.bfloat16]
+    for dtype in dtypes:
+        src = rand_src(gen, (1, E, K), dtype)
+        for reduce in ('sum', 'mean', 'min', 'max'):
+            want, want_arg = oracle.segment_csr(src, indptr, reduce)
+            got, got_arg = cabi.segment_csr(src.cuda(), indptr.cuda(), reduce)
+            what = f'segment_csr {reduce} {dtype} K={K} {kind}'
+            assert_close(got, want, what=what)
+            if want_arg is not None:
+                assert torch.equal(got_arg.cpu(), want_arg), what + ' arg'
+            want, want_extra = oracle.segment_coo(src, index, rows, reduce)
+            got, got_extra = cabi.segment_coo(src.cuda(), index.cuda(), rows, reduce)
+            what = f'segment_coo {reduce} {dtype} K={K} {kind}'
+            assert_close(got, want, what=what)
+            if reduce in ('min', 'max'):
+                assert torch.equal(got_extra.cpu(), want_extra), what + ' arg'
+            elif reduce == 'mean':
+                assert_close(got_extra, want_extra, what=what + ' count')
+
+
+def test_segment_csr_batched(chunk):
+    """Per-batch row pointers and a row pointer shared by all batches."""
+    gen = torch.Generator().manual_seed(5)
+    B, rows, K = 3, 50, 8
+    lens = torch.stack([row_lengths(gen, rows, 'uniform') for _ in range(B)])
+    E = int(lens.sum(1).max())
+    lens[:, -1] += E - lens.sum(1)  # same total per batch
+    indptr = torch.cat([torch.zeros(B, 1, dtype=torch.long), lens.cumsum(1)], 1)
+    for dtype in (torch.float32, torch.int64):
+        src = rand_src(gen, (B, E, K), dtype)
+        for reduce in ('sum', 'mean', 'min', 'max'):
+            for ip in (indptr, indptr[:1]):
+                want, want_arg = oracle.segment_csr(src, ip, reduce)
+                got, got_arg = cabi.segment_csr(src.cuda(), ip.contiguous().cuda(), reduce)
+                assert_close(got, want, what=f'batched csr {reduce} {dtype}')
+                if want_arg is not None:
+                    assert torch.equal(got_arg.cpu(), want_arg)
+
+
+def test_segment_csr_deterministic(chunk):
+    gen = torch.Generator().manual_seed(11)
+    lens = row_lengths(gen, 2000, 'lognormal')
+    indptr = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)]).view(1, -1).cuda()
+    src = torch.randn(1, int(indptr[0, -1]), 64, generator=gen).cuda()
+    a, _ = cabi.segment_csr(src, indptr, 'sum')
+    b, _ = cabi.segment_csr(src, indptr, 'sum')
+    assert torch.equal(a, b)
+
+
+def test_segment_csr_bad_pointers_do_not_fault():
+    """Row pointers outside [0, E] or not ascending are clamped: garbage in, garbage out, no fault."""
+    src = torch.randn(1, 100, 4).cuda()
+    indptr = torch.tensor([[0, 50, 20, 1000, -5, 100]]).cuda()
+    out, _ = cabi.segment_csr(src, indptr, 'sum')
+    torch.cuda.synchronize()
+    assert out.shape == (1, 5, 4)
+
+
+@pytest.mark.parametrize('K', [1, 4, 16, 33, 64])
+def test_gathers(K):
+    gen = torch.Generator().manual_seed(77 + K)
+    rows = 400
+    for kind in ('lognormal', 'giant', 'empty_ends'):
+        lens = row_lengths(gen, rows, kind)
+        indptr = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)]).view(1, -1)
+        E = int(indptr[0, -1])
+        index = torch.repeat_interleave(torch.arange(rows), lens).view(1, -1)
+        for dtype in DTYPES:
+            table = rand_src(gen, (1, rows, K), dtype)
+            want = oracle.gather_csr(table, indptr, E)
+            assert_close(cabi.gather_csr(table.cuda(), indptr.cuda(), E), want, exact=True, what=f'gather_csr {dtype} K={K}')
+            want = oracle.gather_coo(table, index)
+            assert_close(cabi.gather_coo(table.cuda(), index.cuda()), want, exact=True, what=f'gather_coo {dtype} K={K}')
+        # fused mean backward: value / row length
+        table = rand_src(gen, (1, rows, K), torch.float32)
+        want = oracle.gather_csr(table / lens.clamp(min=1).view(1, -1, 1).float(), indptr, E)
+        assert_close(cabi.gather_csr(table.cuda(), indptr.cuda(), E, divide=True), want, what='gather_csr divide')
+        count = lens.clamp(min=1).view(1, -1).float()
+        assert_close(cabi.gather_coo(table.cuda(), index.cuda(), count.cuda()), want, what='gather_coo divide')
+
+
+@pytest.mark.parametrize('K', [1, 3, 4, 16, 33, 64])
+def test_scatter_rows(K):
+    """Index constant along the features (a broadcast 1-D index): the vectorised row kernels."""
+    gen = torch.Generator().manual_seed(300 + K)
+    B, E, N = 2, 3000, 97
+    index = torch.randint(0, N, (1, E, 1), generator=gen)
+    index[0, :200, 0] = 5  # a hot target
+    for dtype in DTYPES:
+        src = rand_src(gen, (B, E, K), dtype)
+        for reduce in ('sum', 'mean', 'min', 'max'):
+            want, want_arg = oracle.scatter(src, index, N, reduce)
+            got, got_arg, _ = cabi.scatter(src.cuda(), index.cuda(), N, reduce, (0, 1, 0))
+            what = f'scatter {reduce} {dtype} K={K}'
+            assert_close(got, want, what=what)
+            if want_arg is not None:
+                assert torch.equal(got_arg.cpu(), want_arg), what + ' arg'
+
+
+def test_scatter_elements_and_ties():
+    """A full-shaped index (one target per element) and quantised values with many exact ties."""
+    gen = torch.Generator().manual_seed(9)
+    B, E, K, N = 2, 2000, 5, 31
+    index = torch.randint(0, N, (B, E, K), generator=gen)
+    for dtype in DTYPES:
+        src = rand_src(gen, (B, E, K), dtype)
+        if dtype.is_floating_point:
+            src = (src.float() * 4).round().div(4).to(dtype)
+        for reduce in ('sum', 'mean', 'min', 'max', 'mul'):
+            s = src
+            if reduce == 'mul':
+                if dtype in (torch.float16, torch.bfloat16):
+                    continue
+                s = torch.where(torch.rand(src.shape, generator=gen) < 0.02, src.double().clamp(-2, 2).to(dtype),
+                                torch.ones_like(src))
+            want, want_arg = oracle.scatter(s, index, N, reduce)
+            got, got_arg, _ = cabi.scatter(s.cuda(), index.cuda(), N, reduce, (E * K, K, 1))
+            what = f'scatter elems {reduce} {dtype}'
+            assert_close(got, want, what=what)
+            if want_arg is not None:
+                assert torch.equal(got_arg.cpu(), want_arg), what + ' arg'
+
+
+def test_scatter_seeded_and_out_of_range():
+    gen = torch.Generator().manual_seed(21)
+    E, K, N = 500, 8, 20
+    index = torch.randint(0, N, (1, E, 1), generator=gen)
+    src = torch.randn(1, E, K, generator=gen)
+    base = torch.randn(1, N, K, generator=gen)
+    for reduce in ('sum', 'min', 'max'):
+        want, _ = oracle.scatter(src, index, N, reduce, base)
+        got, _, _ = cabi.scatter(src.cuda(), index.cuda(), N, reduce, (0, 1, 0), out=base.clone().cuda())
+        assert_close(got, want, what=f'scatter seeded {reduce}')
+    # targets outside [0, N) are skipped, never written
+    bad = index.clone()
+    bad[0, ::7, 0] = N + 3
+    bad[0, 1::11, 0] = -1
+    keep = ((bad >= 0) & (bad < N)).view(-1)
+    want, _ = oracle.scatter(src[:, keep], bad[:, keep], N, 'sum')
+    got, _, _ = cabi.scatter(src.cuda(), bad.cuda(), N, 'sum', (0, 1, 0))
+    assert_close(got, want, what='scatter out-of-range skipped')
+
+
+def test_backward_kernels():
+    gen = torch.Generator().manual_seed(33)
+    B, E, K, N = 2, 700, 16, 40
+    index = torch.randint(0, N, (1, E, 1), generator=gen)
+    grad_out = torch.randn(B, N, K, generator=gen)
+    want = grad_out[:, index.view(-1)]
+    got = cabi.scatter_backward(grad_out.cuda(), index.cuda(), E, (0, 1, 0))
+    assert_close(got, want, exact=True, what='scatter_backward')
+    count = torch.bincount(index.view(-1), minlength=N).int()
+    want = grad_out[:, index.view(-1)] / count.clamp(min=1)[index.view(-1)].view(1, -1, 1)
+    got = cabi.scatter_backward(grad_out.cuda(), index.cuda(), E, (0, 1, 0), count.cuda())
+    assert_close(got, want, what='scatter_backward mean')
+    arg = torch.randint(0, E + 1, (B, N, K), generator=gen)  # E marks "no element"
+    want = torch.zeros(B, E + 1, K).scatter_(1, arg, grad_out)[:, :E]
+    # several outputs may name the same element: use distinct args per (b,k) column for a defined result
+    arg = torch.stack([torch.stack([torch.randperm(E + 1, generator=gen)[:N] for _ in range(K)], 1) for _ in range(B)])
+    want = torch.zeros(B, E + 1, K).scatter_(1, arg, grad_out)[:, :E]
+    got = cabi.arg_backward(grad_out.cuda(), arg.cuda(), E)
+    assert_close(got, want, exact=True, what='arg_backward')
