@@ -40,6 +40,20 @@ def assert_close(got, want, exact=False, what=''):
         assert ok, f'{what}: max abs diff {(got.double() - want.double()).abs().max()} (tol {tol})'
 
 
+def assert_sum_close(got, want64, mass64, what=''):
+    """Float SUM/MEAN check that is fair to any summation order: the error against the float64 result
+    must stay within rtol * (sum of |terms| behind that output), rtol = 1e-5 for fp32 and 1e-2 for
+    fp16/bf16 (for 16-bit the final rounding of the result is allowed on top)."""
+    got = got.cpu()
+    rtol = TOL[got.dtype]['rtol']
+    err = (got.double() - want64).abs()
+    bound = rtol * mass64 + 1e-30
+    if got.dtype in (torch.float16, torch.bfloat16):
+        bound = bound + rtol * want64.abs()
+    bad = err > bound
+    assert not bool(bad.any()), f'{what}: {int(bad.sum())} outputs off; worst err {float(err.max())} vs bound {float(bound[err.argmax()] if bound.dim() == 0 else bound.flatten()[err.argmax()])}'
+
+
 def load_golden(name):
     return torch.load(osp.join(GOLDEN, name), weights_only=False)
 
