@@ -31,7 +31,7 @@ FEAT = 64
 SEED = 20240602
 METRIC = 'segment_csr+scatter sum effective HBM bandwidth (F=64, fp32, power-law CSR)'
 UNIT = 'GB/s'
-# Per-launch DRAM traffic of csr_reduce_kernel on the full workload, from the ncu capture summarised
+# Per-launch DRAM traffic of csr_stream_kernel on the full workload, from the ncu capture summarised
 # in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists.
 CSR_KERNEL_DRAM_TRAFFIC_BYTES = None
 
@@ -69,47 +69,57 @@ def algorithmic_bytes(rows, nnz, feat=FEAT, s=4):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    Q = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,'
-         'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
-         'clocks_event_reasons.sw_power_cap')
+    """Samples SM clock, power and throttle reasons through NVML (read-only) in a background thread
+    while the timed region runs; falls back to one `nvidia-smi` query when NVML is not importable."""
+    REASONS = {0x4: 'sw_power_cap', 0x8: 'hw_slowdown', 0x20: 'sw_thermal_slowdown', 0x40: 'hw_thermal_slowdown'}
 
-    def __init__(self, gpu_index):
-        self.gpu_index, self.proc = gpu_index, None
+    def __init__(self, device):
+        import threading
+        self.device, self.samples, self.reasons, self.max_mhz = device, [], set(), None
+        self.stop_flag, self.thread, self.handle, self.nvml = threading.Event(), None, None, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device).uuid)
+            uuid = uuid if uuid.startswith('GPU-') else 'GPU-' + uuid
+            self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            self.nvml = pynvml
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._run, daemon=True)
+        except Exception:  # noqa: BLE001
+            self.nvml = None
+
+    def _run(self):
+        n = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
+                bits = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                for bit, name in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.005)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits',
-                                          '-lms', '100', '-i', str(self.gpu_index)],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+        if self.thread is not None:
+            self.thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
-        self.proc.terminate()
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            return {'sm_mhz': statistics.median(self.samples) if self.samples else None, 'sm_max_mhz': self.max_mhz,
+                    'reasons': sorted(self.reasons), 'samples': len(self.samples), 'source': 'nvml'}
         try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
-        for line in out.strip().splitlines():
-            f = [x.strip() for x in line.split(',')]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, v in zip(names, f[5:9]):
-                if v.lower().startswith('active'):
-                    reasons.add(name)
-        return {'sm_mhz': statistics.median(sm) if sm else None, 'sm_max_mhz': max(mx) if mx else None,
-                'reasons': sorted(reasons), 'samples': len(sm)}
+            q = 'clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.sw_power_cap'
+            out = subprocess.run(['nvidia-smi', f'--query-gpu={q}', '--format=csv,noheader,nounits'],
+                                 stdout=subprocess.PIPE, text=True, timeout=10).stdout.strip().splitlines()[0].split(',')
+            return {'sm_mhz': float(out[0]), 'sm_max_mhz': float(out[1]), 'reasons': [], 'samples': 1,
+                    'source': 'nvidia-smi after the timed region'}
+        except Exception:  # noqa: BLE001
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['clock query unavailable'], 'samples': 0}
 
 
 # -------------------------------------------------------------------------------------------------
@@ -187,7 +197,6 @@ def run_ours(args):
     src_p, indptr_p, shuffled_p = src_h.pin_memory(), indptr_h.pin_memory(), shuffled_h.pin_memory()
     src, indptr, shuffled = src_p.to(dev), indptr_p.to(dev), shuffled_p.to(dev)
     out_csr = torch.empty(ROWS, FEAT, device=dev)
-    out_sc = torch.empty(ROWS, FEAT, device=dev)
     rs_out = torch.empty(ROWS // world, FEAT, device=dev) if world > 1 else None
 
     def step():
@@ -195,10 +204,9 @@ def run_ours(args):
         ts.segment_csr(src, indptr, out=out_csr, reduce='sum')
         # Unsorted scatter shards the edge dimension: every rank reduces its edges into a full-length
         # partial, then a reduce-scatter leaves each rank with its block of target rows.
-        out_sc.zero_()
-        ts.scatter(src, shuffled, dim=0, out=out_sc, reduce='sum')
+        part = ts.scatter(src, shuffled, dim=0, dim_size=ROWS, reduce='sum')
         if world > 1:
-            dist.reduce_scatter_tensor(rs_out, out_sc, op=dist.ReduceOp.SUM)
+            dist.reduce_scatter_tensor(rs_out, part, op=dist.ReduceOp.SUM)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -210,8 +218,7 @@ def run_ours(args):
         step()
     sync_all()
 
-    sampler = ClockSampler(torch.cuda.current_device() if 'CUDA_VISIBLE_DEVICES' not in os.environ else
-                           int(os.environ['CUDA_VISIBLE_DEVICES'].split(',')[local_rank]))
+    sampler = ClockSampler(dev)
     if rank == 0:
         sampler.start()
     stream = torch.cuda.current_stream()
@@ -220,11 +227,10 @@ def run_ours(args):
     for i in range(args.steps):
         ts.segment_csr(src, indptr, out=out_csr, reduce='sum')
         ev[3 * i + 1].record(stream)
-        out_sc.zero_()
-        ts.scatter(src, shuffled, dim=0, out=out_sc, reduce='sum')
+        part = ts.scatter(src, shuffled, dim=0, dim_size=ROWS, reduce='sum')
         ev[3 * i + 2].record(stream)
         if world > 1:
-            dist.reduce_scatter_tensor(rs_out, out_sc, op=dist.ReduceOp.SUM)
+            dist.reduce_scatter_tensor(rs_out, part, op=dist.ReduceOp.SUM)
         ev[3 * i + 3].record(stream)
     sync_all()
     clocks = sampler.stop() if rank == 0 else None
@@ -275,6 +281,7 @@ def run_ours(args):
     nnz_all = [int(x) for x in allt[:, 5].tolist()]
 
     if rank == 0:
+        scatter_passes = -(-(ROWS * FEAT * 4) // (128 << 20))  # 128 MiB output slices
         b = [algorithmic_bytes(ROWS, n) for n in nnz_all]
         b_csr, b_sc = sum(x[0] for x in b), sum(x[1] for x in b)
         ms_per_step = total_ms / args.steps
@@ -301,12 +308,13 @@ def run_ours(args):
             'ops': {'segment_csr_sum': {'ms': csr_ms, 'GB/s': csr_gbs, 'frac_of_peak': csr_gbs / peak},
                     'scatter_sum': {'ms': sc_ms, 'GB/s': sc_gbs, 'frac_of_peak': sc_gbs / peak},
                     'reduce_scatter_ms': coll_ms},
-            'roofline': {'bound': 'hbm', 'kernel': 'csr_reduce_kernel<float,sum,4>', 'achieved': csr_gbs, 'peak': peak,
+            'roofline': {'bound': 'hbm', 'kernel': 'csr_stream_kernel<float,sum,VEC=4,D=8>', 'achieved': csr_gbs, 'peak': peak,
                          'unit': 'GB/s', 'frac': csr_gbs / peak, 'traffic': CSR_KERNEL_DRAM_TRAFFIC_BYTES,
                          'peak_source': peak_src, 'algorithmic_bytes_per_launch': b[0][0]},
             'e2e': {'value': (b_csr + b_sc) / (e2e_ms * 1e-3) / 1e9, 'unit': UNIT, 'ms_per_step': e2e_ms,
                     'steps': e2e_steps, 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h},
-            'gpu_launches': 2 * args.steps,
+            # per step: csr_stream_kernel + csr_fixup_kernel + one scatter_rows_range_kernel per output slice
+            'gpu_launches': (2 + scatter_passes) * args.steps,
             'clocks': clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
@@ -334,7 +342,7 @@ def cpu_baseline(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--steps', type=int, default=100)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--ref-fraction', type=int, default=4, help='reference arm runs on 1/this of the rows')

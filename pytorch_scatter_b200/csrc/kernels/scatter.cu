@@ -18,6 +18,8 @@
 // Replaces scatter_kernel / scatter_arg_kernel of the upstream project
 // (csrc/cuda/scatter_cuda.cu:13-56): one atomic per element, CAS loops for float MIN/MAX and all
 // 16-bit types, K redundant index loads per row and a racy arg pass.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace tsb {
@@ -166,6 +168,90 @@ __global__ void __launch_bounds__(kThreads) scatter_rows_kernel(ScatterParams p)
   for (int64_t c = col; c < Kv; c += L) apply_pack<OP, T, VEC>(trow + c * VEC, ld_stream<T, VEC>(srow + c * VEC));
   // one count per row of the index itself: a batch-broadcast index is counted for b == 0 only
   if (p.count != nullptr && col == 0 && (p.sb != 0 || b == 0)) atomicAdd(p.count + (p.sb ? b : 0) * p.N + idx, 1);
+}
+
+// Row kernel restricted to the target rows [lo, hi) (rows counted over all batches, b*N + idx).
+// When the output is larger than L2, the launcher runs one such pass per slice of the output so that
+// the slice being accumulated stays L2-resident: every pass re-reads the whole index (8 bytes per
+// entry) but only the source rows whose target lies in the slice, and the read-modify-write traffic
+// of the atomics no longer reaches DRAM.  A warp issues the index loads
+// of its 128 consecutive entries, compacts the matching ones through shared memory and then moves
+// them 32/L rows per step, four steps in flight.
+constexpr int kRangeBatches = 4;  // 32-entry batches a warp looks at per launch slot
+
+template <typename T, int OP, int VEC>
+__global__ void __launch_bounds__(kThreads) scatter_rows_range_kernel(ScatterParams p, int64_t lo, int64_t hi) {
+  using U = acc_t<T>;
+  constexpr int kWarps = kThreads / 32;
+  constexpr int kSteps = 4;
+  constexpr int kCap = 32 * kRangeBatches;
+  __shared__ int64_t s_ent[kWarps][kCap];
+  __shared__ int64_t s_trow[kWarps][kCap];
+  const T *__restrict__ src = static_cast<const T *>(p.src);
+  U *target = static_cast<U *>(p.target);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int L = 1 << p.l_log2;
+  const int col = lane & (L - 1);
+  const int sub = lane >> p.l_log2;
+  const int eps = 32 >> p.l_log2;
+  const int64_t Kv = p.K / VEC;
+  const int64_t M = p.B * p.E;
+  const int64_t base = ((int64_t)blockIdx.x * kWarps + warp) * kCap;
+  if (base >= M) return;  // warp-uniform
+  // all index loads of the warp's batches are issued before any is used
+  int64_t ent[kRangeBatches], trow[kRangeBatches];
+#pragma unroll
+  for (int q = 0; q < kRangeBatches; ++q) {
+    ent[q] = base + q * 32 + lane;
+    trow[q] = -1;
+    if (ent[q] < M) {
+      const int64_t b = (p.B == 1) ? 0 : ent[q] / p.E;
+      const int64_t e = ent[q] - b * p.E;
+      const int64_t idx = p.index[b * p.sb + e * p.se];
+      if (idx >= 0 && idx < p.N) trow[q] = b * p.N + idx;
+    }
+  }
+  int n = 0;
+#pragma unroll
+  for (int q = 0; q < kRangeBatches; ++q) {
+    const bool match = trow[q] >= lo && trow[q] < hi;
+    const unsigned mask = __ballot_sync(kFullMask, match);
+    if (match) {
+      const int r = n + __popc(mask & ((1u << lane) - 1u));
+      s_ent[warp][r] = ent[q];
+      s_trow[warp][r] = trow[q];
+    }
+    n += __popc(mask);
+  }
+  __syncwarp();
+  for (int64_t cb = 0; cb < Kv; cb += L) {
+    const int64_t c = cb + col;
+    const bool col_ok = c < Kv;
+    for (int i = 0; i < n; i += kSteps * eps) {
+      Pack<T, VEC> v[kSteps];
+      int64_t tr[kSteps];
+      bool ok[kSteps];
+#pragma unroll
+      for (int u = 0; u < kSteps; ++u) {
+        const int m = i + u * eps + sub;
+        ok[u] = col_ok && m < n;
+        if (ok[u]) {
+          tr[u] = s_trow[warp][m];
+          v[u] = ld_stream<T, VEC>(src + s_ent[warp][m] * p.K + c * VEC);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kSteps; ++u) {
+        if (ok[u]) {
+          apply_pack<OP, T, VEC>(target + tr[u] * p.K + c * VEC, v[u]);
+          if (p.count != nullptr && c == 0) {
+            const int64_t b = tr[u] / p.N;
+            if (p.sb != 0 || b == 0) atomicAdd(p.count + (p.sb ? tr[u] : tr[u] - b * p.N), 1);
+          }
+        }
+      }
+    }
+  }
 }
 
 template <typename T, int OP>
@@ -338,6 +424,13 @@ __global__ void __launch_bounds__(kThreads) scatter_bw_elems_kernel(ScatterBwPar
   gi[i] = v;
 }
 
+inline int64_t env_bytes(const char *name, int64_t fallback) {
+  const char *v = std::getenv(name);
+  if (v == nullptr || *v == '\0') return fallback;
+  const long long x = std::atoll(v);
+  return x > 0 ? (int64_t)x : fallback;
+}
+
 inline bool grid_for(int64_t threads, unsigned *blocks) {
   const int64_t nb = (threads + kThreads - 1) / kThreads;
   if (nb > 2147483647LL) return false;
@@ -356,12 +449,22 @@ int run_scatter(ScatterParams p, int reduce, cudaStream_t stream) {
   const bool mean = reduce == TSB_MEAN;
   unsigned blocks = 0;
 
+  // An output larger than L2 is accumulated slice by slice (see scatter_rows_range_kernel) when the
+  // index is constant along the features and a source row is big enough to pay for re-reading the index.
+  const int64_t slice_bytes = env_bytes("TSB_SCATTER_SLICE_BYTES", 128ll << 20);  // test / tuning hook
+  const int64_t target_row_bytes = p.K * (int64_t)sizeof(U);
+  int64_t slice_rows = target_row_bytes > 0 ? slice_bytes / target_row_bytes : 0;
+  if (slice_rows < 1) slice_rows = 1;
+  const bool sliced = OP == kSum && p.sk == 0 && p.E > 0 && p.B * p.N > slice_rows + slice_rows / 2 &&
+                      p.K * (int64_t)sizeof(T) >= 128;
+
   // 1. bring the target to its starting state
   if (total > 0) {
     const bool need_init = k16 || kKeyed || p.fresh;
     if (need_init) {
       if (!k16 && !kMinMax && OP == kSum) {
-        if (cudaMemsetAsync(p.target, 0, (size_t)total * sizeof(U), stream) != cudaSuccess) return TSB_ERR_LAUNCH;
+        // sliced passes zero each slice right before accumulating into it (it then never leaves L2)
+        if (!sliced && cudaMemsetAsync(p.target, 0, (size_t)total * sizeof(U), stream) != cudaSuccess) return TSB_ERR_LAUNCH;
       } else {
         if (!grid_for(total, &blocks)) return TSB_ERR_TOO_LARGE;
         scatter_init_kernel<T, OP><<<blocks, kThreads, 0, stream>>>(static_cast<const T *>(p.out),
@@ -380,7 +483,18 @@ int run_scatter(ScatterParams p, int reduce, cudaStream_t stream) {
   const int64_t Kv = p.K / (vec_ok ? kFull : 1);
   p.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
   if (total > 0 && p.E > 0) {
-    if (rows) {
+    if (sliced) {
+      if (!grid_for((p.B * p.E + kRangeBatches - 1) / kRangeBatches, &blocks)) return TSB_ERR_TOO_LARGE;  // 128 entries per warp
+      const bool zero_slices = !k16 && p.fresh;
+      for (int64_t lo = 0; lo < p.B * p.N; lo += slice_rows) {
+        const int64_t hi = lo + slice_rows < p.B * p.N ? lo + slice_rows : p.B * p.N;
+        if (zero_slices && cudaMemsetAsync(static_cast<U *>(p.target) + lo * p.K, 0,
+                                           (size_t)((hi - lo) * p.K) * sizeof(U), stream) != cudaSuccess)
+          return TSB_ERR_LAUNCH;
+        if (vec_ok) scatter_rows_range_kernel<T, OP, kFull><<<blocks, kThreads, 0, stream>>>(p, lo, hi);
+        else scatter_rows_range_kernel<T, OP, 1><<<blocks, kThreads, 0, stream>>>(p, lo, hi);
+      }
+    } else if (rows) {
       if (!grid_for((p.B * p.E) << p.l_log2, &blocks)) return TSB_ERR_TOO_LARGE;
       if (vec_ok) scatter_rows_kernel<T, OP, kFull><<<blocks, kThreads, 0, stream>>>(p);
       else scatter_rows_kernel<T, OP, 1><<<blocks, kThreads, 0, stream>>>(p);

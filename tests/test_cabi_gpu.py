@@ -153,8 +153,23 @@ def test_gathers(K):
         assert_close(cabi.gather_coo(table.cuda(), index.cuda(), count.cuda()), want, what='gather_coo divide')
 
 
+@pytest.fixture(params=[None, 4096], ids=['one-pass', 'sliced'])
+def scatter_slices(request):
+    """Forces the sliced multi-pass scatter (normally used when the output exceeds L2) on small outputs."""
+    old = os.environ.get('TSB_SCATTER_SLICE_BYTES')
+    if request.param is None:
+        os.environ.pop('TSB_SCATTER_SLICE_BYTES', None)
+    else:
+        os.environ['TSB_SCATTER_SLICE_BYTES'] = str(request.param)
+    yield request.param
+    if old is None:
+        os.environ.pop('TSB_SCATTER_SLICE_BYTES', None)
+    else:
+        os.environ['TSB_SCATTER_SLICE_BYTES'] = old
+
+
 @pytest.mark.parametrize('K', [1, 3, 4, 16, 33, 64])
-def test_scatter_rows(K):
+def test_scatter_rows(scatter_slices, K):
     """Index constant along the features (a broadcast 1-D index): the vectorised row kernels."""
     gen = torch.Generator().manual_seed(300 + K)
     B, E, N = 2, 3000, 97
