@@ -339,6 +339,23 @@ def cpu_baseline(args):
         return {'value': None, 'unit': UNIT, 'cores': None, 'kind': None, 'sample': f'failed: {e}'}
 
 
+def run_profile_op(args):
+    """Profiling helper: `--profile-op csr|scatter` runs warmup+steps calls of ONE operator on a
+    `--rows`-sized copy of the workload and exits; meant to be wrapped in ncu on a small case."""
+    import pytorch_scatter_b200 as ts
+    indptr, _, shuffled, src = make_workload(args.rows, SEED)
+    src, indptr, shuffled = src.cuda(), indptr.cuda(), shuffled.cuda()
+    out = torch.empty(args.rows, FEAT, device='cuda')
+    for _ in range(args.warmup + args.steps):
+        if args.profile_op == 'csr':
+            ts.segment_csr(src, indptr, out=out, reduce='sum')
+        else:
+            ts.scatter(src, shuffled, dim=0, dim_size=args.rows, reduce='sum')
+    torch.cuda.synchronize()
+    print(json.dumps({'profile_op': args.profile_op, 'rows': args.rows, 'entries': src.size(0),
+                      'calls': args.warmup + args.steps}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -347,7 +364,12 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--ref-fraction', type=int, default=4, help='reference arm runs on 1/this of the rows')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--profile-op', choices=['csr', 'scatter'], default=None)
+    ap.add_argument('--rows', type=int, default=ROWS, help='rows of the workload for --profile-op')
     args = ap.parse_args()
+    if args.profile_op is not None:
+        run_profile_op(args)
+        return
     if args.warmup < 3 and args.impl == 'ours':
         args.warmup = 3
     if args.impl == 'reference':

@@ -1,0 +1,122 @@
+"""Sharding the reductions over the GPUs of one node (one process per GPU, ``torch.distributed``).
+
+Upstream has no distributed code; this follows how the reductions decompose:
+
+* ``segment_csr`` / ``segment_coo`` / the gathers: every output row depends only on its own contiguous
+  source range, so contiguous row ranges are independent units.  :func:`balanced_row_cuts` picks the
+  cut points so that every rank gets about the same number of *entries* (not rows);
+  :func:`shard_csr` slices and rebases.  No collective is needed.
+* ``scatter`` on an unsorted index: shard the **edge** dimension.  Every rank reduces its edges into a
+  full-length partial; one reduce-scatter (sum / min / max) leaves rank ``r`` with output rows
+  ``[r*N/P, (r+1)*N/P)``.  ``mean`` reduce-scatters sums and counts and divides afterwards; the arg index
+  of min/max is the smallest global edge position whose value equals the reduced value, found with a
+  second (min) reduction over int64 candidates - the same first-occurrence rule as the single-GPU path.
+"""
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def balanced_row_cuts(indptr: torch.Tensor, parts: int) -> torch.Tensor:
+    """``parts + 1`` ascending row indices ``c`` with ``c[0] = 0`` and ``c[-1] = rows`` such that every range
+    ``[c[p], c[p+1])`` holds about ``nnz / parts`` entries.  A row is never split."""
+    assert indptr.dim() == 1 and indptr.numel() >= 1
+    rows = indptr.numel() - 1
+    nnz = int(indptr[-1])
+    targets = torch.arange(1, parts, dtype=torch.float64, device=indptr.device) * (nnz / parts)
+    inner = torch.searchsorted(indptr.to(torch.float64), targets, right=False).clamp_(0, rows)
+    cuts = torch.cat([torch.zeros(1, dtype=torch.long, device=indptr.device), inner.long(),
+                      torch.full((1,), rows, dtype=torch.long, device=indptr.device)])
+    return torch.cummax(cuts, 0).values
+
+
+def shard_csr(src: torch.Tensor, indptr: torch.Tensor, rank: int, world: int
+              ) -> Tuple[torch.Tensor, torch.Tensor, Tuple[int, int]]:
+    """The slice of a 1-D-indptr CSR problem that ``rank`` owns: ``(src_local, indptr_local, (row_lo, row_hi))``
+    with ``indptr_local`` rebased to start at 0."""
+    cuts = balanced_row_cuts(indptr, world)
+    lo, hi = int(cuts[rank]), int(cuts[rank + 1])
+    e_lo, e_hi = int(indptr[lo]), int(indptr[hi])
+    return src[e_lo:e_hi], indptr[lo:hi + 1] - e_lo, (lo, hi)
+
+
+def _padded_rows(n: int, world: int) -> int:
+    return (n + world - 1) // world * world
+
+
+def _reduce_scatter(full: torch.Tensor, op, group) -> torch.Tensor:
+    """Row-blocked reduce-scatter of ``full`` [P*rows_per_rank, ...]; falls back to all-reduce + slice on
+    backends without reduce_scatter_tensor (gloo)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    per = full.size(0) // world
+    out = torch.empty((per,) + tuple(full.shape[1:]), dtype=full.dtype, device=full.device)
+    if dist.get_backend(group) == 'nccl':
+        dist.reduce_scatter_tensor(out, full.contiguous(), op=op, group=group)
+        return out
+    tmp = full.clone()
+    dist.all_reduce(tmp, op=op, group=group)
+    return tmp[rank * per:(rank + 1) * per].clone()
+
+
+def scatter_sharded(src_local: torch.Tensor, index_local: torch.Tensor, dim_size: int, reduce: str = 'sum',
+                    edge_offset: int = 0, total_edges: Optional[int] = None, group=None,
+                    local_reduce: Optional[Callable] = None):
+    """Edge-sharded ``scatter`` along dim 0 with a 1-D index.
+
+    ``src_local`` [E_local, ...] and ``index_local`` [E_local] are this rank's edges; ``edge_offset`` is the
+    global position of its first edge and ``total_edges`` the global edge count (both only matter for the arg
+    indices of min/max).  Returns this rank's block of ``ceil(dim_size / P)`` output rows (the last rank's block
+    may include padding rows past ``dim_size``), plus the arg block for min/max.
+
+    ``local_reduce(src, index, dim_size, reduce) -> (out, arg_or_None)`` computes the local partial; it defaults
+    to this package's CUDA operators (tests on CPU ranks inject a reference).
+    """
+    world = dist.get_world_size(group)
+    n_pad = _padded_rows(dim_size, world)
+    if local_reduce is None:
+        local_reduce = _cuda_local_reduce
+    if reduce in ('sum', 'add'):
+        part, _ = local_reduce(src_local, index_local, n_pad, 'sum')
+        return _reduce_scatter(part, dist.ReduceOp.SUM, group)
+    if reduce == 'mean':
+        part, _ = local_reduce(src_local, index_local, n_pad, 'sum')
+        ones = torch.ones(index_local.numel(), dtype=torch.float32, device=src_local.device)
+        count, _ = local_reduce(ones, index_local, n_pad, 'sum')
+        total = _reduce_scatter(part, dist.ReduceOp.SUM, group)
+        count = _reduce_scatter(count, dist.ReduceOp.SUM, group).clamp_(min=1)
+        count = count.view((-1,) + (1,) * (total.dim() - 1))
+        if total.is_floating_point():
+            return total / count.to(total.dtype)
+        return torch.div(total, count.to(total.dtype), rounding_mode='floor')
+    if reduce in ('min', 'max'):
+        op = dist.ReduceOp.MIN if reduce == 'min' else dist.ReduceOp.MAX
+        if total_edges is None:
+            t = torch.tensor([index_local.numel()], dtype=torch.long, device=src_local.device)
+            dist.all_reduce(t, group=group)
+            total_edges = int(t)
+        part, arg = local_reduce(src_local, index_local, n_pad, reduce)
+        # rows nobody on this rank wrote hold 0 with arg == E_local: give them the identity for the reduction
+        untouched = arg >= index_local.numel()
+        if part.is_floating_point():
+            ident = torch.finfo(part.dtype).max if reduce == 'min' else torch.finfo(part.dtype).min
+        else:
+            ident = torch.iinfo(part.dtype).max if reduce == 'min' else torch.iinfo(part.dtype).min
+        vals = torch.where(untouched, torch.full_like(part, ident), part)
+        final = vals.clone()
+        dist.all_reduce(final, op=op, group=group)
+        cand = torch.where((vals == final) & ~untouched, arg + edge_offset, torch.full_like(arg, total_edges))
+        arg_block = _reduce_scatter(cand, dist.ReduceOp.MIN, group)
+        rank, per = dist.get_rank(group), n_pad // world
+        out_block = final[rank * per:(rank + 1) * per].clone()
+        out_block[arg_block >= total_edges] = 0  # targets no edge names, as in the single-GPU operator
+        return out_block, arg_block
+    raise ValueError(reduce)
+
+
+def _cuda_local_reduce(src, index, dim_size, reduce):
+    from . import scatter_max, scatter_min, scatter_sum
+    if reduce == 'sum':
+        return scatter_sum(src, index, 0, None, dim_size), None
+    fn = scatter_min if reduce == 'min' else scatter_max
+    return fn(src, index, 0, None, dim_size)
