@@ -69,6 +69,27 @@ int tsb_segment_csr(const void *src, const int64_t *indptr, void *out, int64_t *
                     int64_t B, int64_t E, int64_t K, int64_t N, int64_t indptr_batch_stride,
                     int dtype, int reduce, void *workspace, size_t workspace_bytes, tsb_stream_t stream);
 
+/* segment_csr for callers that cannot provide a workspace.  It has no counterpart in the upstream
+ * project.  Meant for hosts that cannot allocate device memory at call time: an inference server that
+ * handed the whole GPU to its own memory pool at start-up, a real-time loop where cudaMalloc's implicit
+ * device synchronisation (and its chance of failing under fragmentation) is not acceptable, or a plug-in
+ * that may only launch kernels - and that have no caching allocator to ask for a scratch tensor instead.
+ * Same arguments and results as tsb_segment_csr; the scratch is a fixed array of
+ * TSB_STATIC_SCRATCH_BYTES inside the library (every GPU that loads the library holds it until the
+ * process exits).
+ *   - Problems whose tsb_segment_csr_workspace_bytes(...) exceeds TSB_STATIC_SCRATCH_BYTES are rejected
+ *     with TSB_ERR_TOO_LARGE before anything is launched (fp32, K = 64: about 8 million entries).
+ *   - The call itself allocates nothing (no cudaMalloc / cudaFree, no allocating library routine).
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array.  It keeps the previous call's contents, which is harmless:
+ *     nothing in it has to start at zero.  Two calls that overlap on the GPU (different streams, or
+ *     different host threads) race on it: serialise them, or use tsb_segment_csr with separate workspaces. */
+#define TSB_STATIC_SCRATCH_BYTES (8u << 20)
+int tsb_segment_csr_noalloc(const void *src, const int64_t *indptr, void *out, int64_t *arg_out,
+                            int64_t B, int64_t E, int64_t K, int64_t N, int64_t indptr_batch_stride,
+                            int dtype, int reduce, tsb_stream_t stream);
+
 /* gather_csr: out[b,e,:] = src[b,n,:] for e in [indptr[b,n], indptr[b,n+1]); positions no row covers
  * are left untouched.  Replaces gather_csr_cuda + kernels, csrc/cuda/segment_csr_cuda.cu:219-281,
  * :170-217.  Here src is [B,N,K] and out is [B,E,K].

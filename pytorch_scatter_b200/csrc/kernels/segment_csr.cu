@@ -22,6 +22,7 @@
 // Replaces segment_csr_kernel / segment_csr_broadcast_kernel of the upstream project
 // (csrc/cuda/segment_csr_cuda.cu:15-95), which walk each row with a single thread per feature.
 #include <cstdlib>
+#include <mutex>
 
 #include "csr_reduce.cuh"
 
@@ -519,4 +520,53 @@ extern "C" int tsb_segment_csr(const void *src, const int64_t *indptr, void *out
   p.workspace = workspace;
   p.workspace_bytes = workspace_bytes;
   return tsb::launch_csr_reduce(p, dtype, reduce, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// -------------------------------------------------------------------------------------------------
+// segment_csr without a caller-provided workspace.
+//
+// Some hosts cannot hand this library a scratch buffer: they gave all device memory to their own
+// pool at start-up, or they sit in a latency-critical loop where a cudaMalloc (an implicit device
+// synchronisation that can also fail under fragmentation) is not acceptable, and they have no
+// caching allocator to ask instead.  For them the partial-row scratch of the reduction lives in the
+// fixed array below.  It is part of the library image: every GPU that loads the library holds these
+// 8 MiB until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[TSB_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_scratch_mutex;
+void *g_static_scratch_addr[64] = {nullptr};  // device address of the array, per device ordinal
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address: handing
+// it to a kernel would fault (or, where the GPU can reach host memory, silently use the wrong
+// bytes).  The real address is asked for once per device, with that device current.
+int static_scratch_of_current_device(void **addr) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TSB_ERR_LAUNCH;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void *ptr = nullptr;
+    if (cudaGetSymbolAddress((void **)&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return TSB_ERR_LAUNCH;
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *addr = g_static_scratch_addr[dev];
+  return TSB_OK;
+}
+}  // namespace
+
+extern "C" int tsb_segment_csr_noalloc(const void *src, const int64_t *indptr, void *out, int64_t *arg_out,
+                                       int64_t B, int64_t E, int64_t K, int64_t N, int64_t indptr_batch_stride,
+                                       int dtype, int reduce, tsb_stream_t stream) {
+  if (B < 0 || E < 0 || K < 0 || N < 0) return TSB_ERR_ARG;
+  if (B * N * K == 0) return TSB_OK;
+  // Nothing in the scratch has to start at zero: every chunk stores its row id slot before the
+  // fix-up kernel reads it, and a partial row is only read where this same call stored it.  So the
+  // contents left behind by the previous call are simply overwritten.
+  const size_t need = tsb::csr_reduce_workspace_bytes(B, E, K, N, dtype, reduce);
+  if (need > (size_t)TSB_STATIC_SCRATCH_BYTES) return TSB_ERR_TOO_LARGE;
+  void *scratch = nullptr;
+  const int st = static_scratch_of_current_device(&scratch);
+  if (st != TSB_OK) return st;
+  return tsb_segment_csr(src, indptr, out, arg_out, B, E, K, N, indptr_batch_stride, dtype, reduce, scratch,
+                         (size_t)TSB_STATIC_SCRATCH_BYTES, stream);
 }
