@@ -356,6 +356,116 @@ def run_profile_op(args):
                       'calls': args.warmup + args.steps}))
 
 
+def run_suite(args):
+    """`--suite`: device-time table over the other BASELINE configurations (one JSON line per operator):
+    C1 scatter sum [1,048,576 x 32] -> 65,536; C2 segment_csr sum/mean/min/max at F in {1,16,64,128} and
+    gather_csr; C3 segment_coo / gather_coo / scatter_softmax on the sorted index in fp32/bf16/fp16;
+    C4 scatter sum/max/min with a Zipf(1.2) index over 100,000 targets, [33,554,432 x 16]."""
+    import pytorch_scatter_b200 as ts
+    dev = torch.device('cuda')
+    peaks_path = osp.join(ROOT, 'MEASURED_PEAKS.json')
+    peak = float(json.load(open(peaks_path))['hbm_gbs']) if osp.exists(peaks_path) else 6650.0
+    l2_flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timeit(fn, nbytes, small):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(args.steps):
+            if small:
+                l2_flush.zero_()  # working set below ~250 MB: flush L2 between iterations
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ms = statistics.median(times)
+        return ms, nbytes / ms / 1e6
+
+    only = set(x for x in args.suite_only.split(',') if x)
+
+    def emit(config, op, ms, gbs, **extra):
+        if only and config not in only:
+            return
+        print(json.dumps({'suite': config, 'op': op, 'ms': round(ms, 4), 'GB/s': round(gbs, 1),
+                          'frac_of_measured_peak': round(gbs / peak, 3), **extra}), flush=True)
+
+    g = torch.Generator(device='cuda').manual_seed(SEED)
+
+    def c1():
+        E, F, N = 1 << 20, 32, 65536
+        src = torch.randn(E, F, device=dev, generator=g)
+        idx = torch.randint(0, N, (E,), device=dev, generator=g)
+        nb = E * F * 4 + E * 8 + N * F * 4
+        ms, gbs = timeit(lambda: ts.scatter(src, idx, 0, dim_size=N, reduce='sum'), nb, True)
+        emit('C1', 'scatter sum fp32 [1048576x32]->65536', ms, gbs, l2_flushed=True)
+        del src, idx
+
+    def c2_c3():
+        lens = row_lengths(ROWS, SEED, force_long=8)
+        indptr_h = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)])
+        nnz = int(indptr_h[-1])
+        indptr = indptr_h.to(dev)
+        index = torch.repeat_interleave(torch.arange(ROWS, device=dev), lens.to(dev))
+        for F in (1, 16, 64, 128):
+            src = torch.randn(nnz, F, device=dev, generator=g) if F > 1 else torch.randn(nnz, device=dev, generator=g)
+            small = nnz * F * 4 < (250 << 20)
+            for reduce in ('sum', 'mean', 'min', 'max'):
+                nb = nnz * F * 4 + (ROWS + 1) * 8 + ROWS * F * 4 + (ROWS * F * 8 if reduce in ('min', 'max') else 0)
+                fn = getattr(ts, f'segment_{reduce}_csr')
+                ms, gbs = timeit(lambda: fn(src, indptr), nb, small)
+                emit('C2', f'segment_csr {reduce} fp32 F={F}', ms, gbs, l2_flushed=small)
+            if F == 64:
+                table = torch.randn(ROWS, F, device=dev, generator=g)
+                nb = ROWS * F * 4 + (ROWS + 1) * 8 + nnz * F * 4
+                out = torch.empty(nnz, F, device=dev)
+                ms, gbs = timeit(lambda: ts.gather_csr(table, indptr, out), nb, False)
+                emit('C2', 'gather_csr fp32 F=64', ms, gbs)
+            del src
+        F = 64
+        for dtype, name in ((torch.float32, 'fp32'), (torch.bfloat16, 'bf16'), (torch.float16, 'fp16')):
+            s = 4 if dtype == torch.float32 else 2
+            src = torch.randn(nnz, F, device=dev, generator=g).to(dtype)
+            for reduce in ('sum', 'mean', 'max'):
+                nb = nnz * F * s + nnz * 8 + ROWS * F * s + (ROWS * F * 8 if reduce == 'max' else 0) + (ROWS * s if reduce == 'mean' else 0)
+                fn = getattr(ts, f'segment_{reduce}_coo')
+                ms, gbs = timeit(lambda: fn(src, index, None, ROWS), nb, False)
+                emit('C3', f'segment_coo {reduce} {name} F=64', ms, gbs)
+            table = torch.randn(ROWS, F, device=dev, generator=g).to(dtype)
+            out = torch.empty(nnz, F, device=dev, dtype=dtype)
+            nb = ROWS * F * s + nnz * 8 + nnz * F * s
+            ms, gbs = timeit(lambda: ts.gather_coo(table, index, out), nb, False)
+            emit('C3', f'gather_coo {name} F=64', ms, gbs)
+            if dtype == torch.float32:
+                nb = 2 * nnz * F * s + nnz * 8 + 2 * ROWS * F * s
+                ms, gbs = timeit(lambda: ts.scatter_softmax(src, index, 0, dim_size=ROWS), nb, False)
+                emit('C3', 'scatter_softmax fp32 F=64 (composite)', ms, gbs)
+            del src, table, out
+        del index, indptr
+
+    def c4():
+        E, F, N = 1 << 25, 16, 100000
+        prob = torch.arange(1, N + 1, device=dev, dtype=torch.float64).pow(-1.2)
+        ranks = torch.multinomial((prob / prob.sum()).float(), E, replacement=True, generator=g)
+        idx = torch.randperm(N, device=dev, generator=g)[ranks]
+        del ranks
+        src = torch.randn(E, F, device=dev, generator=g)
+        for reduce in ('sum', 'max', 'min'):
+            nb = E * F * 4 + E * 8 + N * F * 4 + (N * F * 8 if reduce != 'sum' else 0)
+            fn = getattr(ts, f'scatter_{reduce}')
+            ms, gbs = timeit(lambda: fn(src, idx, 0, None, N), nb, False)
+            emit('C4', f'scatter {reduce} fp32 [33554432x16] Zipf(1.2)->100000', ms, gbs)
+
+    if not only or 'C1' in only:
+        c1()
+    if not only or only & {'C2', 'C3'}:
+        c2_c3()
+    if not only or 'C4' in only:
+        c4()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -364,11 +474,16 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--ref-fraction', type=int, default=4, help='reference arm runs on 1/this of the rows')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--suite', action='store_true', help='per-operator table over the other configurations')
+    ap.add_argument('--suite-only', default='', help='comma-separated configs to run, e.g. C3,C4')
     ap.add_argument('--profile-op', choices=['csr', 'scatter'], default=None)
     ap.add_argument('--rows', type=int, default=ROWS, help='rows of the workload for --profile-op')
     args = ap.parse_args()
     if args.profile_op is not None:
         run_profile_op(args)
+        return
+    if args.suite:
+        run_suite(args)
         return
     if args.warmup < 3 and args.impl == 'ours':
         args.warmup = 3

@@ -134,30 +134,69 @@ struct GatherCooParams {
   int l_log2;
 };
 
+// A warp owns 128 consecutive entries: it loads their indices with four coalesced loads, then copies
+// 32/L rows per step (index broadcast by shuffle), four steps of loads in flight before the stores.
+// With a sorted index neighbouring entries name the same source row, which then comes from L1/L2.
+constexpr int kGatherBatches = 4;
+
 template <typename T, int VEC>
 __global__ void __launch_bounds__(kThreads) gather_coo_kernel(GatherCooParams p) {
   const T *__restrict__ src = static_cast<const T *>(p.src);
   T *__restrict__ out = static_cast<T *>(p.out);
   const T *__restrict__ count = static_cast<const T *>(p.count);
+  constexpr int kWarps = kThreads / 32;
+  constexpr int kSteps = 4;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int L = 1 << p.l_log2;
+  const int col = lane & (L - 1);
+  const int sub = lane >> p.l_log2;
+  const int eps = 32 >> p.l_log2;
   const int64_t Kv = p.K / VEC;
-  const int64_t entry = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> p.l_log2;
-  const int col = threadIdx.x & (L - 1);
-  if (entry >= p.B * p.E) return;
-  const int64_t b = entry / p.E, e = entry - b * p.E;
-  const int64_t idx = p.index[b * p.bstride + e];
-  if (idx < 0 || idx >= p.N) return;
-  const T *srow = src + (b * p.N + idx) * p.K;
-  T *orow = out + entry * p.K;
-  T cnt = count_to_t<T>(1);
-  if (count != nullptr) cnt = count[b * p.N + idx];
-  for (int64_t c = col; c < Kv; c += L) {
-    Pack<T, VEC> v = ld_pack<T, VEC>(srow + c * VEC);
-    if (count != nullptr) {
+  const int64_t M = p.B * p.E;
+  const int64_t base = ((int64_t)blockIdx.x * kWarps + warp) * (32 * kGatherBatches);
+  if (base >= M) return;  // warp-uniform
+
+  int64_t srow[kGatherBatches];  // source row (over all batches) of this lane's entry, -1: skip
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) v.v[i] = div_t<T>(v.v[i], cnt);
+  for (int q = 0; q < kGatherBatches; ++q) {
+    const int64_t ent = base + q * 32 + lane;
+    srow[q] = -1;
+    if (ent < M) {
+      const int64_t b = (p.B == 1) ? 0 : ent / p.E;
+      const int64_t idx = p.index[b * p.bstride + (ent - b * p.E)];
+      if (idx >= 0 && idx < p.N) srow[q] = b * p.N + idx;
     }
-    st_stream<T, VEC>(orow + c * VEC, v);
+  }
+#pragma unroll
+  for (int q = 0; q < kGatherBatches; ++q) {
+    const int64_t ent0 = base + q * 32;
+    if (ent0 >= M) break;  // warp-uniform
+    for (int64_t cb = 0; cb < Kv; cb += L) {
+      const int64_t c = cb + col;
+      const bool col_ok = c < Kv;
+      for (int i = 0; i < 32; i += kSteps * eps) {
+        Pack<T, VEC> v[kSteps];
+        int64_t r[kSteps];
+#pragma unroll
+        for (int u = 0; u < kSteps; ++u) {
+          const int m = i + u * eps + sub;  // entry within the batch handled by this lane group
+          r[u] = __shfl_sync(kFullMask, (long long)srow[q], m & 31);
+          if (m >= 32 || !col_ok) r[u] = -1;
+          if (r[u] >= 0) v[u] = ld_pack<T, VEC>(src + r[u] * p.K + c * VEC);
+        }
+#pragma unroll
+        for (int u = 0; u < kSteps; ++u) {
+          if (r[u] >= 0) {
+            if (count != nullptr) {
+              const T cnt = count[r[u]];
+#pragma unroll
+              for (int k = 0; k < VEC; ++k) v[u].v[k] = div_t<T>(v[u].v[k], cnt);
+            }
+            st_stream<T, VEC>(out + (ent0 + i + u * eps + sub) * p.K + c * VEC, v[u]);
+          }
+        }
+      }
+    }
   }
 }
 
@@ -169,8 +208,8 @@ int launch_gather_coo(GatherCooParams p, cudaStream_t stream) {
   const bool vec_ok = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.out);
   const int64_t Kv = p.K / (vec_ok ? kFull : 1);
   p.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
-  const int64_t threads = entries << p.l_log2;
-  const int64_t blocks = (threads + kThreads - 1) / kThreads;
+  const int64_t per_cta = (int64_t)(kThreads / 32) * 32 * kGatherBatches;
+  const int64_t blocks = (entries + per_cta - 1) / per_cta;
   if (blocks > 2147483647LL) return TSB_ERR_TOO_LARGE;
   if (vec_ok) gather_coo_kernel<T, kFull><<<(unsigned)blocks, kThreads, 0, stream>>>(p);
   else gather_coo_kernel<T, 1><<<(unsigned)blocks, kThreads, 0, stream>>>(p);

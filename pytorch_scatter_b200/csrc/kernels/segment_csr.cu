@@ -52,9 +52,12 @@ struct CsrGeom {
   int64_t *head_row;
 };
 
-// Chunk length: a power of two holding about kChunkBytes of source, at least one full warp step.
-inline int chunk_entries_for(int64_t K, size_t elem) {
+// Chunk length: a power of two holding about kChunkBytes of source, shortened (down to one full
+// warp step) when the whole reduced dimension would otherwise give too few chunks to occupy the GPU.
+inline int chunk_entries_for(int64_t K, size_t elem, int64_t E) {
   int64_t c = kChunkBytes / (K * (int64_t)elem);
+  const int64_t want_chunks = 16384;  // ~7 single-warp CTAs per resident slot of a 148-SM part
+  if (E / want_chunks < c) c = E / want_chunks;
   if (const char *forced = std::getenv("TSB_CSR_CHUNK_ENTRIES")) {  // test hook: force short chunks
     const long long v = std::atoll(forced);
     if (v >= 32) c = v;
@@ -64,13 +67,13 @@ inline int chunk_entries_for(int64_t K, size_t elem) {
   return (int)pow2;
 }
 
-template <typename T, int REDUCE, int VEC> struct RowAcc {
+template <typename T, int REDUCE, int VEC, typename ArgT = int64_t> struct RowAcc {
   using A = acc_t<T>;
   static constexpr bool kArg = (REDUCE == kMin || REDUCE == kMax);
   A val[VEC];
-  int64_t arg[kArg ? VEC : 1];
+  ArgT arg[kArg ? VEC : 1];
 
-  __device__ __forceinline__ void init(int64_t sentinel) {
+  __device__ __forceinline__ void init(ArgT sentinel) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       val[i] = reduce_identity<T, REDUCE>();
@@ -79,7 +82,7 @@ template <typename T, int REDUCE, int VEC> struct RowAcc {
   }
   // Entries arrive in increasing e within a lane, so strict comparisons keep the first winner
   // (csrc/cpu/reducer.h:63-67).
-  __device__ __forceinline__ void update(const Pack<T, VEC> &v, int64_t e) {
+  __device__ __forceinline__ void update(const Pack<T, VEC> &v, ArgT e) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const A x = to_acc<T>(v.v[i]);
@@ -94,7 +97,7 @@ template <typename T, int REDUCE, int VEC> struct RowAcc {
   }
   // Merge another lane's partial; on equal values the smaller position wins so that the final
   // arg is the first occurrence over the whole row.
-  __device__ __forceinline__ void merge(const A *oval, const int64_t *oarg) {
+  __device__ __forceinline__ void merge(const A *oval, const ArgT *oarg) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       if (REDUCE == kSum || REDUCE == kMean) {
@@ -108,34 +111,45 @@ template <typename T, int REDUCE, int VEC> struct RowAcc {
   __device__ __forceinline__ void butterfly(int from, int to) {
     for (int off = from; off < to; off <<= 1) {
       A oval[VEC];
-      int64_t oarg[kArg ? VEC : 1];
+      ArgT oarg[kArg ? VEC : 1];
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
         oval[i] = shfl_xor<A>(val[i], off);
-        if (kArg) oarg[i] = shfl_xor<int64_t>(arg[i], off);
+        if (kArg) oarg[i] = shfl_xor<ArgT>(arg[i], off);
       }
       merge(oval, oarg);
     }
   }
 };
 
-// value / count in the arithmetic of T, count converted the way the upstream writer does
-// (csrc/cpu/reducer.h:74-75: `val / (scalar_t)(count > 0 ? count : 1)` with an int count).
-template <typename T> __device__ __forceinline__ T div_by_count(T v, int64_t count) { return v / (T)(int)count; }
-template <> __device__ __forceinline__ __half div_by_count<__half>(__half v, int64_t count) {
-  return __float2half_rn(__half2float(v) / __half2float(__int2half_rn((int)count)));
-}
-template <> __device__ __forceinline__ __nv_bfloat16 div_by_count<__nv_bfloat16>(__nv_bfloat16 v, int64_t count) {
-  return __float2bfloat16_rn(__bfloat162float(v) / __bfloat162float(__int2bfloat16_rn((int)count)));
-}
+// MEAN: the row total times 1/count (count as upstream's writer converts it: an int, at least 1;
+// csrc/cpu/reducer.h:74-75).  For floating types one reciprocal per row replaces VEC divisions; the
+// result differs from a true division by at most one ulp, far inside the 1e-5 tolerance.  Integer
+// types divide exactly (truncating, as the CPU loop does).
+template <typename T> struct MeanScale {
+  acc_t<T> inv;
+  __device__ __forceinline__ explicit MeanScale(int64_t count) : inv((acc_t<T>)1 / (acc_t<T>)(int)count) {}
+  __device__ __forceinline__ T apply(acc_t<T> v) const { return from_acc<T>(v * inv); }
+};
+template <> struct MeanScale<int32_t> {
+  int32_t c;
+  __device__ __forceinline__ explicit MeanScale(int64_t count) : c((int32_t)count) {}
+  __device__ __forceinline__ int32_t apply(int32_t v) const { return v / c; }
+};
+template <> struct MeanScale<int64_t> {
+  int64_t c;
+  __device__ __forceinline__ explicit MeanScale(int64_t count) : c((int64_t)(int)count) {}
+  __device__ __forceinline__ int64_t apply(int64_t v) const { return v / c; }
+};
 
 // Writes one finished row (this lane's VEC columns of it).  `acc` is the reduction over the row's
-// source entries only; in kCooSeeded mode the row's previous value of `out` joins here.
-template <typename T, int REDUCE, int VEC>
-__device__ __forceinline__ void write_row(const RowAcc<T, REDUCE, VEC> &acc, T *out_p, int64_t *arg_p,
-                                          int64_t len, int mode, int64_t sentinel) {
+// source entries only; in kCooSeeded mode the row's previous value of `out` joins here.  Arg indices
+// in `acc` are relative to `arg_base`; `arg_none` marks "no element won" and becomes `sentinel`.
+template <typename T, int REDUCE, int VEC, typename ArgT>
+__device__ __forceinline__ void write_row(const RowAcc<T, REDUCE, VEC, ArgT> &acc, T *out_p, int64_t *arg_p,
+                                          int64_t len, int mode, int64_t sentinel, int64_t arg_base, ArgT arg_none) {
   using A = acc_t<T>;
-  constexpr bool kArg = RowAcc<T, REDUCE, VEC>::kArg;
+  constexpr bool kArg = RowAcc<T, REDUCE, VEC, ArgT>::kArg;
   if (mode == kCooSeeded && len == 0) {  // a row the index never names keeps its value
     if (kArg) {
 #pragma unroll
@@ -146,16 +160,15 @@ __device__ __forceinline__ void write_row(const RowAcc<T, REDUCE, VEC> &acc, T *
   Pack<T, VEC> seed;
   if (mode == kCooSeeded) seed = ld_pack<T, VEC>(out_p);
   Pack<T, VEC> o;
+  const MeanScale<T> scale(REDUCE == kMean && len > 0 ? len : 1);
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
     A v = acc.val[i];
     if (!kArg) {
       if (mode == kCooSeeded) v += to_acc<T>(seed.v[i]);
-      T r = from_acc<T>(v);
-      if (REDUCE == kMean) r = div_by_count<T>(r, len > 0 ? len : 1);
-      o.v[i] = r;
+      o.v[i] = (REDUCE == kMean) ? scale.apply(v) : from_acc<T>(v);
     } else {
-      int64_t a = acc.arg[i];
+      int64_t a = (acc.arg[i] == arg_none) ? sentinel : arg_base + (int64_t)acc.arg[i];
       if (mode == kCsr) {
         if (len == 0) { v = (A)0; a = sentinel; }
       } else if (mode == kCooFresh) {
@@ -176,7 +189,7 @@ __device__ __forceinline__ void write_row(const RowAcc<T, REDUCE, VEC> &acc, T *
 template <typename T, int REDUCE, int VEC, int D>
 __global__ void __launch_bounds__(32, TSB_CSR_MIN_BLOCKS) csr_stream_kernel(CsrParams p, CsrGeom g) {
   using A = acc_t<T>;
-  using Acc = RowAcc<T, REDUCE, VEC>;
+  using Acc = RowAcc<T, REDUCE, VEC, int>;  // arg indices relative to the chunk start inside the stream
   constexpr bool kArg = Acc::kArg;
 
   const T *__restrict__ src = static_cast<const T *>(p.src);
@@ -261,13 +274,13 @@ __global__ void __launch_bounds__(32, TSB_CSR_MIN_BLOCKS) csr_stream_kernel(CsrP
     int cur_end = __shfl_sync(kFullMask, rel, 1);
     if (r_win >= p.N) { cur_start = kRelInf; cur_end = kRelInf; }
     Acc acc;
-    acc.init(p.E);
+    acc.init(kRelInf);
 
     // Closes every row that ends at or before `step_end`; `v` is this lane's entry `e` of the step.
     auto close_rows = [&](const Pack<T, VEC> &v, int e, int step_end) {
       while (cur_end <= step_end) {
         Acc tot = acc;
-        if (e >= cur_start && e < cur_end) tot.update(v, cs + e);
+        if (e >= cur_start && e < cur_end) tot.update(v, e);
         tot.butterfly(L, 32);
         const int64_t row = r_win + cur;
         if (head_pending) {
@@ -276,7 +289,7 @@ __global__ void __launch_bounds__(32, TSB_CSR_MIN_BLOCKS) csr_stream_kernel(CsrP
 #pragma unroll
             for (int i = 0; i < VEC; ++i) {
               carry[c * VEC + i] = tot.val[i];
-              if (kArg) carry_arg[c * VEC + i] = tot.arg[i];
+              if (kArg) carry_arg[c * VEC + i] = tot.arg[i] == kRelInf ? p.E : cs + tot.arg[i];
             }
           }
           if (lane == 0 && cb == 0) g.head_row[chunk_id] = row;
@@ -284,15 +297,16 @@ __global__ void __launch_bounds__(32, TSB_CSR_MIN_BLOCKS) csr_stream_kernel(CsrP
         } else {
           const int64_t grow = b * p.N + row;
           if (sub == 0 && col_ok) {
-            write_row<T, REDUCE, VEC>(tot, out + grow * p.K + c * VEC, kArg ? p.arg_out + grow * p.K + c * VEC : nullptr,
-                                      (int64_t)(cur_end - cur_start), p.mode, p.E);
+            write_row<T, REDUCE, VEC, int>(tot, out + grow * p.K + c * VEC,
+                                           kArg ? p.arg_out + grow * p.K + c * VEC : nullptr,
+                                           (int64_t)(cur_end - cur_start), p.mode, p.E, cs, kRelInf);
           }
           if (lane == 0 && cb == 0 && p.count_out != nullptr) {
             const int len = cur_end - cur_start;
             static_cast<T *>(p.count_out)[grow] = from_acc<T>((A)(len > 0 ? len : 1));
           }
         }
-        acc.init(p.E);
+        acc.init(kRelInf);
         ++cur;
         if (cur == kWindowRows) {
           r_win += kWindowRows;
@@ -328,7 +342,7 @@ __global__ void __launch_bounds__(32, TSB_CSR_MIN_BLOCKS) csr_stream_kernel(CsrP
           const int e = pos + sub;
           const int step_end = (pos + eps < t) ? pos + eps : t;
           if (cur_end <= step_end) close_rows(v, e, step_end);
-          if (e >= cur_start) acc.update(v, cs + e);  // the row still open after this step
+          if (e >= cur_start) acc.update(v, e);  // the row still open after this step
         }
       }
     }
@@ -342,7 +356,7 @@ __global__ void __launch_bounds__(32, TSB_CSR_MIN_BLOCKS) csr_stream_kernel(CsrP
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
           carry[p.K + c * VEC + i] = acc.val[i];
-          if (kArg) carry_arg[p.K + c * VEC + i] = acc.arg[i];
+          if (kArg) carry_arg[p.K + c * VEC + i] = acc.arg[i] == kRelInf ? p.E : cs + acc.arg[i];
         }
       }
     }
@@ -406,8 +420,9 @@ __global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeo
         if (kArg) oarg[i] = g.carry_arg[at + i];
       }
       acc.merge(oval, oarg);
-      write_row<T, REDUCE, VEC>(acc, out + grow * p.K + c * VEC, kArg ? p.arg_out + grow * p.K + c * VEC : nullptr,
-                                re - rs, p.mode, p.E);
+      write_row<T, REDUCE, VEC, int64_t>(acc, out + grow * p.K + c * VEC,
+                                         kArg ? p.arg_out + grow * p.K + c * VEC : nullptr, re - rs, p.mode, p.E,
+                                         0, p.E);
     }
   }
   if (lane == 0 && p.count_out != nullptr) {
@@ -428,7 +443,11 @@ size_t carry_bytes(int64_t total_chunks, int64_t K, size_t acc_size, bool with_a
 template <typename T, int REDUCE, int VEC>
 int launch_vec(const CsrParams &p, CsrGeom g, cudaStream_t stream) {
   constexpr bool kArg = (REDUCE == kMin || REDUCE == kMax);
-  constexpr int kDepth = kArg ? 4 : TSB_CSR_DEPTH;  // load ring depth: 8 steps (4 KiB per warp) in flight for sums
+  // Load ring depth: 8 steps (4 KiB per warp) in flight; 4 where the accumulators (fp32 values of a
+  // 16-bit pack plus arg indices, 64-bit types) would push the ring out of the 128-register budget.
+  constexpr bool kWide = sizeof(acc_t<T>) * VEC > 16;
+  constexpr bool kHeavy = (kArg && (kWide || sizeof(T) == 8)) || (REDUCE == kMean && (kWide || sizeof(T) == 8));
+  constexpr int kDepth = (kHeavy || kArg) ? 4 : TSB_CSR_DEPTH;  // MIN/MAX: the unrolled close path is large
   const int64_t Kv = p.K / VEC;
   g.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
   const int64_t total_chunks = p.B * g.chunks;
@@ -449,7 +468,7 @@ int launch_typed(const CsrParams &p, cudaStream_t stream) {
   if (p.B * p.N == 0) return TSB_OK;
   CsrGeom g;
   g.l_log2 = 0;
-  g.chunk_entries = chunk_entries_for(p.K, sizeof(T));
+  g.chunk_entries = chunk_entries_for(p.K, sizeof(T), p.E);
   g.chunks = (p.E + g.chunk_entries - 1) / g.chunk_entries;
   if (g.chunks < 1) g.chunks = 1;
   size_t arg_off = 0, row_off = 0;
@@ -474,7 +493,7 @@ size_t csr_reduce_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, in
     case TSB_F16: case TSB_BF16: elem = 2; acc = 4; break;
     default: break;
   }
-  const int c = chunk_entries_for(K, elem);
+  const int c = chunk_entries_for(K, elem, E);
   int64_t chunks = (E + c - 1) / c;
   if (chunks < 1) chunks = 1;
   size_t a = 0, r = 0;
