@@ -121,6 +121,26 @@ template <typename T, int VEC> __device__ __forceinline__ void st_stream(T *p, c
   }
 }
 
+// Asynchronous global -> shared copy of one pack by the calling lane (cp.async; 16-byte packs bypass
+// L1).  Packs of less than 4 bytes have no asynchronous form and are copied through a register.
+template <typename T, int VEC> __device__ __forceinline__ void async_copy_pack(Pack<T, VEC> *smem_dst, const T *gsrc) {
+  constexpr int bytes = sizeof(T) * VEC;
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+  if constexpr (bytes == 16) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gsrc) : "memory");
+  } else if constexpr (bytes == 8) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(gsrc) : "memory");
+  } else if constexpr (bytes == 4) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(gsrc) : "memory");
+  } else {
+    *smem_dst = *reinterpret_cast<const Pack<T, VEC> *>(gsrc);
+  }
+}
+__device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void async_wait_all_but() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // Shuffles for every accumulator type we use.
 template <typename A> __device__ __forceinline__ A shfl_xor(A v, int mask) { return __shfl_xor_sync(kFullMask, v, mask); }
 template <> __device__ __forceinline__ int64_t shfl_xor<int64_t>(int64_t v, int mask) {

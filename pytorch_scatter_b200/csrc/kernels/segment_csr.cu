@@ -7,9 +7,10 @@
 //   * the warp finds the first row that ends inside its chunk with a cooperative 32-ary search over
 //     the row pointers (4 rounds for a million rows);
 //   * an entry (K contiguous elements) is covered by L lanes holding one 16-byte pack each, so the
-//     warp consumes 32/L entries (512 contiguous bytes for 16-byte packs) per step; loads run D steps
-//     ahead of consumption through a register ring, so D*512 bytes stay in flight per warp no matter
-//     how short the rows are;
+//     warp consumes 32/L entries (512 contiguous bytes for 16-byte packs) per step; loads run 16 steps
+//     ahead of consumption through a shared-memory ring filled by per-lane cp.async copies (global ->
+//     shared without passing through registers), so 8 KiB stay in flight per warp no matter how short
+//     the rows are, the consuming loop is not unrolled and the kernel fits in 80 registers;
 //   * row boundaries live in registers, 31 rows at a time (lane j holds row pointer j of the window);
 //     all control flow that depends on them is warp-uniform.  When rows end inside a step, the lanes
 //     whose entry belongs to the closing row feed a shuffle butterfly and the row is written;
@@ -30,13 +31,11 @@ namespace tsb {
 
 namespace {
 
-// Resident single-warp CTAs per SM the streaming kernel is compiled for (caps its registers).
-#ifndef TSB_CSR_MIN_BLOCKS
-#define TSB_CSR_MIN_BLOCKS 16
-#endif
-#ifndef TSB_CSR_DEPTH
-#define TSB_CSR_DEPTH 8
-#endif
+// Resident single-warp CTAs per SM the streaming kernel is compiled for (caps its registers at 80),
+// and the depth of its shared-memory load ring (a power of two): 16 steps of 512 bytes = 8 KiB in
+// flight per warp, 192 KiB per SM.
+constexpr int kMinCtasPerSm = 24;
+constexpr int kRingDepth = 16;
 constexpr int kWindowRows = 31;          // lane j holds row pointer j of the window, so rows+1 <= 32
 constexpr int kRelInf = 0x3fffffff;      // "never ends inside this chunk"
 constexpr int64_t kChunkBytes = 128 * 1024;
@@ -186,8 +185,8 @@ __device__ __forceinline__ void write_row(const RowAcc<T, REDUCE, VEC, ArgT> &ac
 }
 
 // Streaming kernel: blockIdx.x = (batch, chunk); one warp.
-template <typename T, int REDUCE, int VEC, int D>
-__global__ void __launch_bounds__(32, TSB_CSR_MIN_BLOCKS) csr_stream_kernel(CsrParams p, CsrGeom g) {
+template <typename T, int REDUCE, int VEC>
+__global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams p, CsrGeom g) {
   using A = acc_t<T>;
   using Acc = RowAcc<T, REDUCE, VEC, int>;  // arg indices relative to the chunk start inside the stream
   constexpr bool kArg = Acc::kArg;
@@ -323,29 +322,33 @@ __global__ void __launch_bounds__(32, TSB_CSR_MIN_BLOCKS) csr_stream_kernel(CsrP
 
     const T *next_ptr = bsrc + (cs + sub) * p.K + c * VEC;
     int next_rel = sub;
-    Pack<T, VEC> ring[D];
+    // Load ring in shared memory, filled by per-lane asynchronous copies (global -> shared without
+    // passing through registers).  Every lane reads back only the slot it copied itself, so the
+    // per-thread completion of cp.async.wait_group is all the synchronisation the ring needs.
+    constexpr int S = kRingDepth;
+    __shared__ Pack<T, VEC> s_ring[S][32];
 #pragma unroll
-    for (int j = 0; j < D; ++j) {
-      ring[j] = (col_ok && next_rel < t) ? ld_stream<T, VEC>(next_ptr) : fill;
+    for (int j = 0; j < S; ++j) {
+      if (col_ok && next_rel < t) async_copy_pack<T, VEC>(&s_ring[j][lane], next_ptr);
+      async_commit();
       next_ptr += step_stride;
       next_rel += eps;
     }
-    for (int pos0 = 0; pos0 < t; pos0 += D * eps) {
-#pragma unroll
-      for (int j = 0; j < D; ++j) {
-        const int pos = pos0 + j * eps;
-        if (pos < t) {  // warp-uniform
-          const Pack<T, VEC> v = ring[j];
-          ring[j] = (col_ok && next_rel < t) ? ld_stream<T, VEC>(next_ptr) : fill;
-          next_ptr += step_stride;
-          next_rel += eps;
-          const int e = pos + sub;
-          const int step_end = (pos + eps < t) ? pos + eps : t;
-          if (cur_end <= step_end) close_rows(v, e, step_end);
-          if (e >= cur_start) acc.update(v, e);  // the row still open after this step
-        }
-      }
+    int slot = 0;
+    for (int pos = 0; pos < t; pos += eps) {
+      async_wait_all_but<S - 1>();  // the oldest copy in flight, this slot's, has landed
+      const int e = pos + sub;
+      const Pack<T, VEC> v = (col_ok && e < t) ? s_ring[slot][lane] : fill;
+      const int step_end = (pos + eps < t) ? pos + eps : t;
+      if (cur_end <= step_end) close_rows(v, e, step_end);
+      if (e >= cur_start) acc.update(v, e);  // the row still open after this step
+      if (col_ok && next_rel < t) async_copy_pack<T, VEC>(&s_ring[slot][lane], next_ptr);
+      async_commit();
+      next_ptr += step_stride;
+      next_rel += eps;
+      slot = (slot + 1) & (S - 1);
     }
+    async_wait_all_but<0>();
     // rows that end exactly at the chunk's end, including rows without entries there
     close_rows(fill, t, t);
 
@@ -443,16 +446,11 @@ size_t carry_bytes(int64_t total_chunks, int64_t K, size_t acc_size, bool with_a
 template <typename T, int REDUCE, int VEC>
 int launch_vec(const CsrParams &p, CsrGeom g, cudaStream_t stream) {
   constexpr bool kArg = (REDUCE == kMin || REDUCE == kMax);
-  // Load ring depth: 8 steps (4 KiB per warp) in flight; 4 where the accumulators (fp32 values of a
-  // 16-bit pack plus arg indices, 64-bit types) would push the ring out of the 128-register budget.
-  constexpr bool kWide = sizeof(acc_t<T>) * VEC > 16;
-  constexpr bool kHeavy = (kArg && (kWide || sizeof(T) == 8)) || (REDUCE == kMean && (kWide || sizeof(T) == 8));
-  constexpr int kDepth = (kHeavy || kArg) ? 4 : TSB_CSR_DEPTH;  // MIN/MAX: the unrolled close path is large
   const int64_t Kv = p.K / VEC;
   g.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
   const int64_t total_chunks = p.B * g.chunks;
   if (total_chunks > 2147483647LL) return TSB_ERR_TOO_LARGE;
-  csr_stream_kernel<T, REDUCE, VEC, kDepth><<<(unsigned)total_chunks, 32, 0, stream>>>(p, g);
+  csr_stream_kernel<T, REDUCE, VEC><<<(unsigned)total_chunks, 32, 0, stream>>>(p, g);
   if (g.chunks > 1) {  // a single chunk per batch cannot split a row
     const int64_t blocks = (total_chunks + (kThreads / 32) - 1) / (kThreads / 32);
     csr_fixup_kernel<T, REDUCE, VEC><<<(unsigned)blocks, kThreads, 0, stream>>>(p, g);
