@@ -140,7 +140,9 @@ int tsb_gather_coo(const void *src, const int64_t *index, void *out, const void 
  *   arg_out              [B,N,K] int64 for MIN/MAX: smallest e whose value equals the result, else E
  *   count_out            MEAN only: int32 [Bc,N,Kc] with Bc = idx_stride_b ? B : 1 and
  *                        Kc = idx_stride_k ? K : 1; receives the per-target element count
- *   workspace            tsb_scatter_workspace_bytes(...) bytes (fp32 accumulators for 16-bit dtypes)
+ *   workspace            tsb_scatter_workspace_bytes(...) bytes, 256-byte aligned, always at least 256: a
+ *                        flag for the variant choice, fp32 accumulators for 16-bit dtypes, and copies
+ *                        of small outputs that contended updates are spread over
  * Float SUM/MEAN/MUL use atomics: the summation order is not fixed.  MIN/MAX and arg are exact. */
 size_t tsb_scatter_workspace_bytes(int64_t B, int64_t N, int64_t K, int dtype, int reduce);
 int tsb_scatter(const void *src, const int64_t *index, void *out, int64_t *arg_out, int32_t *count_out,

@@ -12,6 +12,12 @@ from ..scatter import scatter_max, scatter_sum
 from ..utils import broadcast
 
 
+def _read_back(per_group: torch.Tensor, index: torch.Tensor, full_index: torch.Tensor, dim: int) -> torch.Tensor:
+    """``per_group`` read back at every element's group, i.e. ``per_group.gather(dim, full_index)``, done by
+    this package's row-gather kernel (the index is read once per entry, rows move in 16-byte packs)."""
+    return torch.ops.torch_scatter.gather_rows(per_group, full_index, dim)
+
+
 def _require_float(src: torch.Tensor, name: str) -> None:
     if not torch.is_floating_point(src):
         raise ValueError(f'`{name}` can only be computed over tensors '
@@ -22,20 +28,20 @@ def scatter_softmax(src: torch.Tensor, index: torch.Tensor,
                     dim: int = -1,
                     dim_size: Optional[int] = None) -> torch.Tensor:
     _require_float(src, 'scatter_softmax')
-    index = broadcast(index, src, dim)
-    group_max = scatter_max(src, index, dim=dim, dim_size=dim_size)[0]
-    shifted_exp = (src - group_max.gather(dim, index)).exp_()
-    group_sum = scatter_sum(shifted_exp, index, dim, dim_size=dim_size)
-    return shifted_exp.div(group_sum.gather(dim, index))
+    full_index = broadcast(index, src, dim)
+    group_max = scatter_max(src, full_index, dim=dim, dim_size=dim_size)[0]
+    shifted_exp = (src - _read_back(group_max, index, full_index, dim)).exp_()
+    group_sum = scatter_sum(shifted_exp, full_index, dim, dim_size=dim_size)
+    return shifted_exp.div(_read_back(group_sum, index, full_index, dim))
 
 
 def scatter_log_softmax(src: torch.Tensor, index: torch.Tensor, dim: int = -1,
                         eps: float = 1e-12,
                         dim_size: Optional[int] = None) -> torch.Tensor:
     _require_float(src, 'scatter_log_softmax')
-    index = broadcast(index, src, dim)
-    group_max = scatter_max(src, index, dim=dim, dim_size=dim_size)[0]
-    shifted = src - group_max.gather(dim, index)
-    group_sum = scatter_sum(shifted.exp(), index, dim, dim_size=dim_size)
-    log_norm = group_sum.add_(eps).log_().gather(dim, index)
+    full_index = broadcast(index, src, dim)
+    group_max = scatter_max(src, full_index, dim=dim, dim_size=dim_size)[0]
+    shifted = src - _read_back(group_max, index, full_index, dim)
+    group_sum = scatter_sum(shifted.exp(), full_index, dim, dim_size=dim_size)
+    log_norm = _read_back(group_sum.add_(eps).log_(), index, full_index, dim)
     return shifted.sub_(log_norm)

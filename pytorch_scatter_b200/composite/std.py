@@ -10,6 +10,7 @@ import torch
 
 from ..scatter import scatter_sum
 from ..utils import broadcast
+from .softmax import _read_back
 
 
 def scatter_std(src: torch.Tensor, index: torch.Tensor, dim: int = -1,
@@ -26,13 +27,13 @@ def scatter_std(src: torch.Tensor, index: torch.Tensor, dim: int = -1,
     ones = torch.ones(index.size(), dtype=src.dtype, device=src.device)
     count = scatter_sum(ones, index, index_dim, dim_size=dim_size)
 
-    index = broadcast(index, src, dim)
-    total = scatter_sum(src, index, dim, dim_size=dim_size)
+    full_index = broadcast(index, src, dim)
+    total = scatter_sum(src, full_index, dim, dim_size=dim_size)
     count = broadcast(count, total, dim).clamp(1)
     mean = total.div(count)
 
-    deviation = src - mean.gather(dim, index)
-    out = scatter_sum(deviation * deviation, index, dim, out, dim_size)
+    deviation = src - _read_back(mean, index, full_index, dim)
+    out = scatter_sum(deviation * deviation, full_index, dim, out, dim_size)
 
     if unbiased:
         count = count.sub(1).clamp_(1)

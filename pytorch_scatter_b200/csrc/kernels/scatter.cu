@@ -12,8 +12,10 @@
 //             (csrc/cpu/reducer.h:63-67).
 //   MUL       compare-and-swap loop (kept for operator-set completeness).
 // When the index is the same for all K features of a row (a broadcast 1-D index, stride_k == 0) the
-// row kernels read it once per row and move the row in 16-byte packs; otherwise an element kernel
-// handles one (b,e,k) per thread.
+// row kernel reads it once per row, moves the row in 16-byte packs and combines the entries of a warp
+// that share a target before touching global memory; otherwise an element kernel handles one (b,e,k)
+// per thread.  Small outputs are accumulated into several copies (less contention per address),
+// outputs larger than L2 slice by slice (the slice being accumulated stays L2-resident).
 //
 // Replaces scatter_kernel / scatter_arg_kernel of the upstream project
 // (csrc/cuda/scatter_cuda.cu:13-56): one atomic per element, CAS loops for float MIN/MAX and all
@@ -147,14 +149,64 @@ struct ScatterParams {
   int64_t B, E, K, N, sb, se, sk;
   int l_log2;
   int fresh;
+  int replicas;        // copies of the output the updates are spread over (1: none)
+  const int *clustered;  // device flag written by scatter_probe_kernel: 1 = neighbouring entries share targets
 };
 
-// ---- row kernels: index constant along k ------------------------------------------------------
+// One CTA looks at four windows of 256 consecutive index entries and counts neighbours that name the
+// same target.  An index where that is common (an edge list sorted or clustered by destination) is
+// handed to the run-combining kernel, any other to the direct kernels; the verdict is a device-side
+// flag, so choosing the variant costs no host synchronisation.
+__global__ void __launch_bounds__(kThreads) scatter_probe_kernel(ScatterParams p, int *clustered, int forced) {
+  if (forced >= 0) {  // test hook: the caller dictates the verdict
+    if (threadIdx.x == 0) *clustered = forced;
+    return;
+  }
+  __shared__ int s_equal, s_pairs;
+  if (threadIdx.x == 0) { s_equal = 0; s_pairs = 0; }
+  __syncthreads();
+  const int64_t M = p.B * p.E;
+  // four windows of 256 neighbouring pairs; all eight loads of a thread are independent
+  int64_t x[4], y[4];
+  bool ok[4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const int64_t i = (M / 4) * w + threadIdx.x;
+    ok[w] = i + 1 < M;
+    if (ok[w]) {
+      const int64_t b0 = (p.B == 1) ? 0 : i / p.E, b1 = (p.B == 1) ? 0 : (i + 1) / p.E;
+      x[w] = p.index[b0 * p.sb + (i - b0 * p.E) * p.se];
+      y[w] = p.index[b1 * p.sb + (i + 1 - b1 * p.E) * p.se];
+      ok[w] = b0 == b1;
+    }
+  }
+  int equal = 0, pairs = 0;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    if (ok[w]) {
+      pairs += 1;
+      equal += (x[w] == y[w]) ? 1 : 0;
+    }
+  }
+  atomicAdd(&s_equal, equal);
+  atomicAdd(&s_pairs, pairs);
+  __syncthreads();
+  if (threadIdx.x == 0) *clustered = (s_pairs > 0 && s_equal * 8 >= s_pairs) ? 1 : 0;
+}
+
+// ---- direct row kernels: one update per entry ---------------------------------------------------
+// L lanes own one entry and move its K values in 16-byte packs; the index is read once per entry.
+// The second kernel is the same restricted to the target rows [lo, hi) (rows counted over all batches):
+// when the output is larger than L2 the launcher runs one such pass per slice of the output, so that
+// the slice being accumulated stays L2-resident.  Every pass re-reads the whole index (8 bytes per
+// entry) but only the source rows whose target lies in the slice.
 template <typename T, int OP, int VEC>
-__global__ void __launch_bounds__(kThreads) scatter_rows_kernel(ScatterParams p) {
+__global__ void __launch_bounds__(kThreads) scatter_rows_direct_kernel(ScatterParams p) {
   using U = acc_t<T>;
   const T *__restrict__ src = static_cast<const T *>(p.src);
+  if (*p.clustered != 0) return;  // the run-combining kernel takes clustered indices
   U *target = static_cast<U *>(p.target);
+  if (p.replicas > 1) target += (blockIdx.x % p.replicas) * (p.B * p.N * p.K);
   const int L = 1 << p.l_log2;
   const int64_t Kv = p.K / VEC;
   const int64_t entry = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> p.l_log2;
@@ -170,13 +222,6 @@ __global__ void __launch_bounds__(kThreads) scatter_rows_kernel(ScatterParams p)
   if (p.count != nullptr && col == 0 && (p.sb != 0 || b == 0)) atomicAdd(p.count + (p.sb ? b : 0) * p.N + idx, 1);
 }
 
-// Row kernel restricted to the target rows [lo, hi) (rows counted over all batches, b*N + idx).
-// When the output is larger than L2, the launcher runs one such pass per slice of the output so that
-// the slice being accumulated stays L2-resident: every pass re-reads the whole index (8 bytes per
-// entry) but only the source rows whose target lies in the slice, and the read-modify-write traffic
-// of the atomics no longer reaches DRAM.  A warp issues the index loads
-// of its 128 consecutive entries, compacts the matching ones through shared memory and then moves
-// them 32/L rows per step, four steps in flight.
 constexpr int kRangeBatches = 4;  // 32-entry batches a warp looks at per launch slot
 
 template <typename T, int OP, int VEC>
@@ -197,7 +242,7 @@ __global__ void __launch_bounds__(kThreads) scatter_rows_range_kernel(ScatterPar
   const int64_t Kv = p.K / VEC;
   const int64_t M = p.B * p.E;
   const int64_t base = ((int64_t)blockIdx.x * kWarps + warp) * kCap;
-  if (base >= M) return;  // warp-uniform
+  if (base >= M || *p.clustered != 0) return;  // warp-uniform
   // all index loads of the warp's batches are issued before any is used
   int64_t ent[kRangeBatches], trow[kRangeBatches];
 #pragma unroll
@@ -254,6 +299,190 @@ __global__ void __launch_bounds__(kThreads) scatter_rows_range_kernel(ScatterPar
   }
 }
 
+// ---- row kernel: index constant along k ---------------------------------------------------------
+// A warp owns 128 consecutive entries.  It loads their 128 targets with four coalesced loads, keeps
+// the ones that fall into the target-row range [lo, hi) of this pass and streams them 32/L rows per
+// step, the rows arriving through a shared-memory ring eight steps deep.  If neighbouring entries share a target (an edge list
+// sorted by destination, or any clustered index), a segmented scan over the step's lane groups plus a
+// carry from step to step combines each run of equal targets, so that ONE update goes to global
+// memory per run instead of one per entry; a list without such neighbours takes a direct path.
+// (Sorting the warp's entries by target to also combine scattered duplicates was tried: the hardware
+// match instruction used to detect duplicates costs more than it saves on duplicate-free indices.)
+// With `replicas` > 1 (small outputs under heavy contention) warps spread their updates over several
+// copies of the output; the finalize pass folds the copies.
+constexpr int kBatches = 4;               // 32-entry batches per warp
+constexpr int kWarpEntries = 32 * kBatches;
+
+template <int OP, typename U> __device__ __forceinline__ U combine(U a, U b) {
+  if (OP == kSum) return a + b;
+  if (OP == kMul) return a * b;
+  if (OP == kMin) return b < a ? b : a;
+  return b > a ? b : a;
+}
+
+template <int OP, typename U, int VEC> __device__ __forceinline__ void apply_acc(U *addr, const U *v) {
+  if constexpr (OP == kSum && std::is_same<U, float>::value && (VEC % 4 == 0)) {
+#pragma unroll
+    for (int i = 0; i < VEC; i += 4) red_add_v4(addr + i, v[i], v[i + 1], v[i + 2], v[i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) apply_one<OP, U>(addr + i, v[i]);
+  }
+}
+
+template <typename T, int OP, int VEC>
+__global__ void __launch_bounds__(kThreads, 4) scatter_rows_runs_kernel(ScatterParams p, int64_t lo, int64_t hi, int replicas) {
+  using U = acc_t<T>;
+  constexpr int kWarps = kThreads / 32;
+  constexpr int kRing = 8;                         // ring depth in steps (power of two)
+  __shared__ int64_t s_key[kWarps][kWarpEntries];  // (target row << 7) | entry position within the warp's 128
+  __shared__ Pack<T, VEC> s_ring[kWarps][kRing][32];
+  const T *__restrict__ src = static_cast<const T *>(p.src);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int L = 1 << p.l_log2;
+  const int col = lane & (L - 1);
+  const int sub = lane >> p.l_log2;
+  const int eps = 32 >> p.l_log2;
+  const int64_t Kv = p.K / VEC;
+  const int64_t M = p.B * p.E;
+  const int64_t warp_id = (int64_t)blockIdx.x * kWarps + warp;
+  const int64_t base = warp_id * kWarpEntries;
+  if (base >= M || *p.clustered == 0) return;  // warp-uniform; the direct kernels take unclustered indices
+  U *target = static_cast<U *>(p.target) + (replicas > 1 ? (warp_id % replicas) * (p.B * p.N * p.K) : 0);
+
+  // ---- targets of the warp's entries; all index loads are in flight before any is used
+  int64_t trow[kBatches];
+#pragma unroll
+  for (int q = 0; q < kBatches; ++q) {
+    const int64_t ent = base + q * 32 + lane;
+    trow[q] = -1;
+    if (ent < M) {
+      const int64_t b = (p.B == 1) ? 0 : ent / p.E;
+      const int64_t idx = p.index[b * p.sb + (ent - b * p.E) * p.se];
+      if (idx >= 0 && idx < p.N) {
+        const int64_t r = b * p.N + idx;
+        if (r >= lo && r < hi) trow[q] = r;
+      }
+    }
+  }
+  // ---- compact the kept entries into shared memory, in entry order
+  int n = 0;
+#pragma unroll
+  for (int q = 0; q < kBatches; ++q) {
+    const bool keep = trow[q] >= 0;
+    const unsigned mask = __ballot_sync(kFullMask, keep);
+    if (keep) s_key[warp][n + __popc(mask & ((1u << lane) - 1u))] = (trow[q] << 7) | (int64_t)(q * 32 + lane);
+    n += __popc(mask);
+  }
+  __syncwarp();
+  if (n == 0) return;
+
+  // do neighbouring entries of the list share a target?
+  bool adjacent_equal = false;
+  for (int m = lane; m + 1 < n; m += 32) adjacent_equal = adjacent_equal || (s_key[warp][m] >> 7) == (s_key[warp][m + 1] >> 7);
+  const bool combine_runs = __any_sync(kFullMask, adjacent_equal);
+
+  // Source rows travel through a per-warp shared-memory ring filled by per-lane cp.async copies, kRing
+  // steps (kRing * 512 bytes) ahead of their use; a lane reads back only what it copied itself.
+  const int nsteps = (n + eps - 1) / eps;
+  const int64_t all_rows = p.B * p.N;
+  for (int64_t cb = 0; cb < Kv; cb += L) {
+    const int64_t c = cb + col;
+    const bool col_ok = c < Kv;
+    auto issue = [&](int step, int slot) {
+      const int m = step * eps + sub;
+      if (step < nsteps && m < n && col_ok) {
+        const int64_t ent = base + (s_key[warp][m] & 127);
+        if (ent < M) async_copy_pack<T, VEC>(&s_ring[warp][slot][lane], src + ent * p.K + c * VEC);
+      }
+      async_commit();
+    };
+    auto flush = [&](int64_t key, const U *v, int cnt) {  // one update for an entry or a finished run
+      if (key < 0 || key >= all_rows) return;  // cannot happen; keeps a logic error from becoming a fault
+      if (col_ok) apply_acc<OP, U, VEC>(target + key * p.K + c * VEC, v);
+      if (p.count != nullptr && c == 0) {
+        const int64_t b = key / p.N;
+        if (p.sb != 0 || b == 0) atomicAdd(p.count + (p.sb ? key : key - b * p.N), cnt);
+      }
+    };
+#pragma unroll
+    for (int j = 0; j < kRing; ++j) issue(j, j);
+
+    int64_t carry_key = -1;
+    int carry_cnt = 0;
+    U carry[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) carry[k] = reduce_identity<T, OP>();
+
+    int slot = 0;
+    for (int step = 0; step < nsteps; ++step) {
+      async_wait_all_but<kRing - 1>();
+      const int m = step * eps + sub;
+      const int64_t key = (m < n) ? (s_key[warp][m] >> 7) : -1;
+      U val[VEC];
+      {
+        const Pack<T, VEC> v = s_ring[warp][slot][lane];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          val[k] = (key >= 0 && col_ok) ? to_acc<T>(v.v[k]) : reduce_identity<T, OP>();
+          if ((OP == kMin || OP == kMax) && is_nan(val[k])) val[k] = reduce_identity<T, OP>();
+        }
+      }
+      issue(step + kRing, slot);
+      slot = (slot + 1) & (kRing - 1);
+
+      if (!combine_runs) {  // warp-uniform: every entry goes straight to global memory
+        if (key >= 0) flush(key, val, 1);
+        continue;
+      }
+      int cnt = key >= 0 ? 1 : 0;
+      const int nvalid = (n - step * eps) < eps ? (n - step * eps) : eps;  // lane groups with an entry
+      // the run carried over from the previous step continues in lane group 0, or is finished
+      if (carry_key >= 0) {
+        const int64_t first_key = __shfl_sync(kFullMask, (long long)key, 0);
+        if (carry_key == first_key) {
+          if (sub == 0) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) val[k] = combine<OP, U>(carry[k], val[k]);
+            cnt += carry_cnt;
+          }
+        } else if (sub == 0) {
+          flush(carry_key, carry, carry_cnt);
+        }
+        carry_key = -1;
+      }
+      // inclusive segmented scan over the lane groups: only ADJACENT groups with the same target
+      // merge (`head` = a run starts in this group)
+      const int64_t prev_key = __shfl_up_sync(kFullMask, (long long)key, L);
+      int head = (sub == 0 || prev_key != key || key < 0) ? 1 : 0;
+      for (int d = 1; d < eps; d <<= 1) {
+        const int ohead = __shfl_up_sync(kFullMask, head, d << p.l_log2);
+        const int ocnt = __shfl_up_sync(kFullMask, cnt, d << p.l_log2);
+        const bool take = sub >= d && !head;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          const U o = __shfl_up_sync(kFullMask, val[k], d << p.l_log2);
+          if (take) val[k] = combine<OP, U>(o, val[k]);
+        }
+        if (take) {
+          cnt += ocnt;
+          head = ohead;
+        }
+      }
+      // a lane group ends a run when its successor has another target; the last group's run may go on
+      const int64_t next_key = __shfl_down_sync(kFullMask, (long long)key, L);
+      const int last = nvalid - 1;
+      if (key >= 0 && sub < last && next_key != key) flush(key, val, cnt);
+      carry_key = __shfl_sync(kFullMask, (long long)key, last << p.l_log2);
+      carry_cnt = __shfl_sync(kFullMask, cnt, last << p.l_log2);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) carry[k] = __shfl_sync(kFullMask, val[k], (last << p.l_log2) + col);
+    }
+    async_wait_all_but<0>();
+    if (carry_key >= 0 && sub == 0) flush(carry_key, carry, carry_cnt);
+  }
+}
+
 template <typename T, int OP>
 __global__ void __launch_bounds__(kThreads) scatter_elems_kernel(ScatterParams p) {
   using U = acc_t<T>;
@@ -270,12 +499,15 @@ __global__ void __launch_bounds__(kThreads) scatter_elems_kernel(ScatterParams p
 }
 
 // ---- init / finalize ---------------------------------------------------------------------------
+// target[r][i] for r < replicas: copy 0 starts from `out` when accumulating into it, everything else
+// from the identity (as an ordered key for MIN/MAX).
 template <typename T, int OP>
-__global__ void __launch_bounds__(kThreads) scatter_init_kernel(const T *out, acc_t<T> *target, int64_t total, int fresh) {
+__global__ void __launch_bounds__(kThreads)
+scatter_init_kernel(const T *out, acc_t<T> *target, int64_t total, int fresh, int replicas) {
   using U = acc_t<T>;
   const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-  if (i >= total) return;
-  const U v = fresh ? reduce_identity<T, OP>() : to_acc<T>(out[i]);
+  if (i >= total * replicas) return;
+  const U v = (fresh || i >= total) ? reduce_identity<T, OP>() : to_acc<T>(out[i]);
   if (OP == kMin || OP == kMax) reinterpret_cast<key_t<U> *>(target)[i] = enc_key(v);
   else target[i] = v;
 }
@@ -302,16 +534,23 @@ template <> __device__ __forceinline__ int64_t mean_div<int64_t>(int64_t v, int3
 template <typename T, int OP>
 __global__ void __launch_bounds__(kThreads)
 scatter_finalize_kernel(T *out, const acc_t<T> *target, const int32_t *count, int64_t total, int64_t N, int64_t K,
-                        int fresh, int count_b, int count_k) {
+                        int fresh, int count_b, int count_k, int replicas) {
   using U = acc_t<T>;
   const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
   if (i >= total) return;
   U v;
   if (OP == kMin || OP == kMax) {
-    v = dec_key<U>(reinterpret_cast<const key_t<U> *>(target)[i]);
+    const key_t<U> *keys = reinterpret_cast<const key_t<U> *>(target);
+    key_t<U> best = keys[i];
+    for (int r = 1; r < replicas; ++r) {
+      const key_t<U> o = keys[(int64_t)r * total + i];
+      if ((OP == kMin) ? (o < best) : (o > best)) best = o;
+    }
+    v = dec_key<U>(best);
     if (fresh && v == reduce_identity<T, OP>()) v = (U)0;
   } else {
     v = target[i];
+    for (int r = 1; r < replicas; ++r) v = combine<OP, U>(v, target[(int64_t)r * total + i]);
   }
   T r = from_acc<T>(v);
   if (count != nullptr) {
@@ -438,8 +677,16 @@ inline bool grid_for(int64_t threads, unsigned *blocks) {
   return true;
 }
 
+// Copies of the output that warps spread their updates over.  Only small outputs are replicated
+// (the copies stay L2-resident); they are the ones where many entries pile onto few addresses.
+inline int replicas_for(int64_t target_bytes) {
+  if (target_bytes <= 0 || target_bytes > (8ll << 20)) return 1;
+  const int64_t r = (64ll << 20) / target_bytes;
+  return (int)(r > 16 ? 16 : (r < 1 ? 1 : r));
+}
+
 template <typename T, int OP>
-int run_scatter(ScatterParams p, int reduce, cudaStream_t stream) {
+int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t stream) {
   using U = acc_t<T>;
   constexpr bool k16 = sizeof(T) == 2;
   constexpr bool kMinMax = (OP == kMin || OP == kMax);
@@ -447,28 +694,40 @@ int run_scatter(ScatterParams p, int reduce, cudaStream_t stream) {
   constexpr int kFull = full_vec<T>();
   const int64_t total = p.B * p.N * p.K;
   const bool mean = reduce == TSB_MEAN;
+  const bool rows = p.sk == 0;
   unsigned blocks = 0;
 
-  // An output larger than L2 is accumulated slice by slice (see scatter_rows_range_kernel) when the
-  // index is constant along the features and a source row is big enough to pay for re-reading the index.
+  // Replicated accumulation: small output, index constant along the features, enough entries to matter.
+  int replicas = replicas_for(total * (int64_t)sizeof(U));
+  if (!rows || p.B * p.E < (1 << 16)) replicas = 1;
+  replicas = (int)env_bytes("TSB_SCATTER_REPLICAS", replicas);  // test / tuning hook
+  if (replicas > replicas_for(total * (int64_t)sizeof(U))) replicas = replicas_for(total * (int64_t)sizeof(U));
+  int *flag = static_cast<int *>(workspace);                       // first 256 bytes: the probe's verdict
+  void *scratch = static_cast<unsigned char *>(workspace) + 256;  // then accumulators / replicas
+  p.target = (k16 || replicas > 1) ? scratch : p.out;
+  p.replicas = replicas;
+  p.clustered = flag;
+
+  // An output larger than L2 is accumulated slice by slice when the index is constant along the
+  // features and a source row is big enough to pay for re-reading the index once per slice.
   const int64_t slice_bytes = env_bytes("TSB_SCATTER_SLICE_BYTES", 128ll << 20);  // test / tuning hook
   const int64_t target_row_bytes = p.K * (int64_t)sizeof(U);
   int64_t slice_rows = target_row_bytes > 0 ? slice_bytes / target_row_bytes : 0;
   if (slice_rows < 1) slice_rows = 1;
-  const bool sliced = OP == kSum && p.sk == 0 && p.E > 0 && p.B * p.N > slice_rows + slice_rows / 2 &&
+  const bool sliced = OP == kSum && rows && replicas == 1 && p.E > 0 && p.B * p.N > slice_rows + slice_rows / 2 &&
                       p.K * (int64_t)sizeof(T) >= 128;
 
   // 1. bring the target to its starting state
   if (total > 0) {
-    const bool need_init = k16 || kKeyed || p.fresh;
+    const bool need_init = k16 || kKeyed || p.fresh || replicas > 1;
     if (need_init) {
-      if (!k16 && !kMinMax && OP == kSum) {
+      if (!k16 && OP == kSum && replicas == 1) {
         // sliced passes zero each slice right before accumulating into it (it then never leaves L2)
         if (!sliced && cudaMemsetAsync(p.target, 0, (size_t)total * sizeof(U), stream) != cudaSuccess) return TSB_ERR_LAUNCH;
       } else {
-        if (!grid_for(total, &blocks)) return TSB_ERR_TOO_LARGE;
+        if (!grid_for(total * replicas, &blocks)) return TSB_ERR_TOO_LARGE;
         scatter_init_kernel<T, OP><<<blocks, kThreads, 0, stream>>>(static_cast<const T *>(p.out),
-                                                                     static_cast<U *>(p.target), total, p.fresh);
+                                                                     static_cast<U *>(p.target), total, p.fresh, replicas);
       }
     }
     if (mean) {
@@ -477,39 +736,50 @@ int run_scatter(ScatterParams p, int reduce, cudaStream_t stream) {
     }
   }
 
-  // 2. the atomics pass
-  const bool rows = p.sk == 0;
+  // 2. the accumulation pass(es)
   const bool vec_ok = rows && (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.target) && aligned16(p.out);
   const int64_t Kv = p.K / (vec_ok ? kFull : 1);
   p.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
   if (total > 0 && p.E > 0) {
-    if (sliced) {
-      if (!grid_for((p.B * p.E + kRangeBatches - 1) / kRangeBatches, &blocks)) return TSB_ERR_TOO_LARGE;  // 128 entries per warp
-      const bool zero_slices = !k16 && p.fresh;
-      for (int64_t lo = 0; lo < p.B * p.N; lo += slice_rows) {
-        const int64_t hi = lo + slice_rows < p.B * p.N ? lo + slice_rows : p.B * p.N;
+    if (rows) {
+      // A probe over a few windows of the index sets a device flag; the direct kernels and the
+      // run-combining kernel are both launched and the one the flag does not select exits at once.
+      const char *force_env = std::getenv("TSB_SCATTER_CLUSTERED");  // test hook: "0" / "1"
+      const int forced = (force_env != nullptr && (*force_env == '0' || *force_env == '1')) ? (*force_env - '0') : -1;
+      scatter_probe_kernel<<<1, kThreads, 0, stream>>>(p, flag, forced);
+      unsigned blocks_direct = 0, blocks_batched = 0;
+      if (!grid_for((p.B * p.E) << p.l_log2, &blocks_direct)) return TSB_ERR_TOO_LARGE;                    // L lanes per entry
+      if (!grid_for((p.B * p.E + kBatches - 1) / kBatches, &blocks_batched)) return TSB_ERR_TOO_LARGE;  // 128 entries per warp
+      const bool zero_slices = sliced && !k16 && p.fresh;
+      const int64_t all_rows = p.B * p.N;
+      const int64_t step = sliced ? slice_rows : all_rows;
+      for (int64_t lo = 0; lo < all_rows; lo += step) {
+        const int64_t hi = lo + step < all_rows ? lo + step : all_rows;
         if (zero_slices && cudaMemsetAsync(static_cast<U *>(p.target) + lo * p.K, 0,
                                            (size_t)((hi - lo) * p.K) * sizeof(U), stream) != cudaSuccess)
           return TSB_ERR_LAUNCH;
-        if (vec_ok) scatter_rows_range_kernel<T, OP, kFull><<<blocks, kThreads, 0, stream>>>(p, lo, hi);
-        else scatter_rows_range_kernel<T, OP, 1><<<blocks, kThreads, 0, stream>>>(p, lo, hi);
+        if (vec_ok) {
+          if (sliced) scatter_rows_range_kernel<T, OP, kFull><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi);
+          else scatter_rows_direct_kernel<T, OP, kFull><<<blocks_direct, kThreads, 0, stream>>>(p);
+          scatter_rows_runs_kernel<T, OP, kFull><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi, replicas);
+        } else {
+          if (sliced) scatter_rows_range_kernel<T, OP, 1><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi);
+          else scatter_rows_direct_kernel<T, OP, 1><<<blocks_direct, kThreads, 0, stream>>>(p);
+          scatter_rows_runs_kernel<T, OP, 1><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi, replicas);
+        }
       }
-    } else if (rows) {
-      if (!grid_for((p.B * p.E) << p.l_log2, &blocks)) return TSB_ERR_TOO_LARGE;
-      if (vec_ok) scatter_rows_kernel<T, OP, kFull><<<blocks, kThreads, 0, stream>>>(p);
-      else scatter_rows_kernel<T, OP, 1><<<blocks, kThreads, 0, stream>>>(p);
     } else {
       if (!grid_for(p.B * p.E * p.K, &blocks)) return TSB_ERR_TOO_LARGE;
       scatter_elems_kernel<T, OP><<<blocks, kThreads, 0, stream>>>(p);
     }
   }
 
-  // 3. finalize: decode keys, mask untouched MIN/MAX slots, round fp32 accumulators, divide for MEAN
-  if (total > 0 && (k16 || kMinMax || mean)) {
+  // 3. finalize: fold replicas, decode keys, mask untouched MIN/MAX slots, round fp32 accumulators, divide for MEAN
+  if (total > 0 && (k16 || kMinMax || mean || replicas > 1)) {
     if (!grid_for(total, &blocks)) return TSB_ERR_TOO_LARGE;
     scatter_finalize_kernel<T, OP><<<blocks, kThreads, 0, stream>>>(
         static_cast<T *>(p.out), static_cast<const U *>(p.target), mean ? p.count : nullptr, total, p.N, p.K,
-        p.fresh, p.sb != 0, p.sk != 0);
+        p.fresh, p.sb != 0, p.sk != 0, replicas);
   }
 
   // 4. arg pass
@@ -556,8 +826,11 @@ int run_scatter_backward(ScatterBwParams p, cudaStream_t stream) {
 extern "C" size_t tsb_scatter_workspace_bytes(int64_t B, int64_t N, int64_t K, int dtype, int reduce) {
   (void)reduce;
   if (B < 0 || N < 0 || K < 0) return 0;
-  if (dtype == TSB_F16 || dtype == TSB_BF16) return (size_t)B * (size_t)N * (size_t)K * sizeof(float);
-  return 0;
+  const bool k16 = dtype == TSB_F16 || dtype == TSB_BF16;
+  const size_t acc = (dtype == TSB_F64 || dtype == TSB_I64) ? 8 : 4;
+  const size_t target = (size_t)B * (size_t)N * (size_t)K * acc;
+  const int replicas = tsb::replicas_for((int64_t)target);
+  return 256 + ((k16 || replicas > 1) ? target * (size_t)replicas : 0);  // 256: the index probe's flag
 }
 
 extern "C" int tsb_scatter(const void *src, const int64_t *index, void *out, int64_t *arg_out, int32_t *count_out,
@@ -573,23 +846,26 @@ extern "C" int tsb_scatter(const void *src, const int64_t *index, void *out, int
   if ((reduce == TSB_MIN || reduce == TSB_MAX) && arg_out == nullptr) return TSB_ERR_ARG;
   if (reduce == TSB_MEAN && count_out == nullptr) return TSB_ERR_ARG;
   const size_t need = tsb_scatter_workspace_bytes(B, N, K, dtype, reduce);
-  if (need > 0 && (workspace == nullptr || workspace_bytes < need)) return TSB_ERR_WORKSPACE;
+  if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+    return TSB_ERR_WORKSPACE;
   ScatterParams p;
   p.src = src; p.index = index; p.out = out;
-  p.target = need > 0 ? workspace : out;
+  p.target = out;  // run_scatter redirects it to the workspace where that is used
   p.arg_out = arg_out;
   p.count = reduce == TSB_MEAN ? count_out : nullptr;
   p.B = B; p.E = E; p.K = K; p.N = N;
   p.sb = idx_stride_b; p.se = idx_stride_e; p.sk = idx_stride_k;
   p.l_log2 = 0;
   p.fresh = out_seeded ? 0 : 1;
+  p.replicas = 1;
+  p.clustered = nullptr;
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
     switch (reduce) {
       case TSB_SUM:
-      case TSB_MEAN: return run_scatter<scalar_t, kSum>(p, reduce, stream);
-      case TSB_MIN: return run_scatter<scalar_t, kMin>(p, reduce, stream);
-      case TSB_MAX: return run_scatter<scalar_t, kMax>(p, reduce, stream);
-      case TSB_MUL: return run_scatter<scalar_t, kMul>(p, reduce, stream);
+      case TSB_MEAN: return run_scatter<scalar_t, kSum>(p, reduce, workspace, stream);
+      case TSB_MIN: return run_scatter<scalar_t, kMin>(p, reduce, workspace, stream);
+      case TSB_MAX: return run_scatter<scalar_t, kMax>(p, reduce, workspace, stream);
+      case TSB_MUL: return run_scatter<scalar_t, kMul>(p, reduce, workspace, stream);
       default: return TSB_ERR_REDUCE;
     }
   });
@@ -607,6 +883,10 @@ extern "C" int tsb_scatter_backward(const void *grad_out, const int64_t *index, 
   p.B = B; p.E = E; p.K = K; p.N = N;
   p.sb = idx_stride_b; p.se = idx_stride_e; p.sk = idx_stride_k;
   p.l_log2 = 0;
+  // Rows named by a unit-stride index, no divide: the warp-batched streaming copy of tsb_gather_coo
+  // (it does not need the index to be sorted) is the fastest kernel for it.
+  if (count == nullptr && idx_stride_k == 0 && (idx_stride_e == 1 || E == 1) && (B == 1 || idx_stride_b == 0 || idx_stride_b == E))
+    return tsb_gather_coo(grad_out, index, grad_in, nullptr, B, E, K, N, B == 1 ? 0 : idx_stride_b, dtype, stream);
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
     return run_scatter_backward<scalar_t>(p, reinterpret_cast<cudaStream_t>(stream));
   });

@@ -124,13 +124,12 @@ ScatterResult scatter_fw(torch::Tensor src, torch::Tensor index, int64_t dim,
   }
   if (r.out.numel() > 0) {
     const size_t ws_bytes = tsb_scatter_workspace_bytes(B, N, K, dtype_enum(src), red);
-    torch::Tensor workspace;
-    if (ws_bytes > 0) workspace = torch::empty({(int64_t)ws_bytes}, src.options().dtype(torch::kUInt8));
+    auto workspace = torch::empty({(int64_t)ws_bytes}, src.options().dtype(torch::kUInt8));
     check_status(tsb_scatter(src.data_ptr(), fi.holder.data_ptr<int64_t>(), r.out.data_ptr(),
                              minmax ? r.arg_out.value().data_ptr<int64_t>() : nullptr,
                              red == TSB_MEAN ? r.count.value().data_ptr<int32_t>() : nullptr, B, E, K, N, fi.sb,
                              fi.se, fi.sk, dtype_enum(src), red, optional_out.has_value() ? 1 : 0,
-                             ws_bytes > 0 ? workspace.data_ptr() : nullptr, ws_bytes, current_stream()),
+                             workspace.data_ptr(), ws_bytes, current_stream()),
                  "tsb_scatter");
   }
   if (copy_back) {
@@ -243,6 +242,36 @@ public:
   }
 };
 
+// Read-back used by the composites: out[.., e, ..] = src[.., index[e], ..] along `dim` for an index in
+// any order (the backward kernel of scatter sum used as a forward); its own backward is a scatter sum.
+class GatherRows : public torch::autograd::Function<GatherRows> {
+public:
+  static variable_list forward(AutogradContext *ctx, Variable src, Variable index, int64_t dim) {
+    dim = dim < 0 ? src.dim() + dim : dim;
+    TSB_CHECK_CUDA(src);
+    TSB_CHECK_CUDA(index);
+    check_index_dtype(index, "index");
+    auto shape = src.sizes().vec();
+    ctx->saved_data["dim"] = dim;
+    ctx->saved_data["dim_size"] = shape[dim];
+    shape[dim] = index.dim() == 1 ? index.size(0) : index.size(dim);
+    auto like = torch::empty(shape, src.options().device(torch::kMeta));
+    index = broadcast(index, like, dim);
+    ctx->save_for_backward({index});
+    return {scatter_bw(src, index, dim, shape, std::nullopt)};
+  }
+  static variable_list backward(AutogradContext *ctx, variable_list grad_outs) {
+    auto index = ctx->get_saved_variables()[0];
+    auto dim = ctx->saved_data["dim"].toInt();
+    auto result = scatter_fw(grad_outs[0], index, dim, std::nullopt, ctx->saved_data["dim_size"].toInt(), "sum");
+    return {result.out, Variable(), Variable()};
+  }
+};
+
+torch::Tensor gather_rows(torch::Tensor src, torch::Tensor index, int64_t dim) {
+  return GatherRows::apply(src, index, dim)[0];
+}
+
 torch::Tensor scatter_sum(torch::Tensor src, torch::Tensor index, int64_t dim,
                           std::optional<torch::Tensor> optional_out, std::optional<int64_t> dim_size) {
   return ScatterSumMean<false>::apply(src, index, dim, optional_out, dim_size)[0];
@@ -277,4 +306,6 @@ TORCH_LIBRARY_FRAGMENT(torch_scatter, m) {
   m.def("scatter_mean", &tsb_ops::scatter_mean);
   m.def("scatter_min", &tsb_ops::scatter_min);
   m.def("scatter_max", &tsb_ops::scatter_max);
+  // not part of upstream's operator set: the index read-back its composites do with Tensor.gather
+  m.def("gather_rows", &tsb_ops::gather_rows);
 }

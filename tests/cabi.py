@@ -110,7 +110,7 @@ def scatter(src, index, N, reduce, strides, out=None):
     nbytes = lib().tsb_scatter_workspace_bytes(_i(B), _i(N), _i(K), d, r)
     ws = _ws(nbytes, src.device)
     _check(lib().tsb_scatter(_p(src), _p(index), _p(out), _p(arg), _p(count), _i(B), _i(E), _i(K), _i(N), _i(sb), _i(se),
-                             _i(sk), d, r, int(seeded), _p(ws) if nbytes else None, ctypes.c_size_t(nbytes), _stream()),
+                             _i(sk), d, r, int(seeded), _p(ws), ctypes.c_size_t(nbytes), _stream()),
            'tsb_scatter')
     return out, arg, count
 

@@ -153,19 +153,29 @@ def test_gathers(K):
         assert_close(cabi.gather_coo(table.cuda(), index.cuda(), count.cuda()), want, what='gather_coo divide')
 
 
-@pytest.fixture(params=[None, 4096], ids=['one-pass', 'sliced'])
+@pytest.fixture(params=['one-pass', 'sliced', 'replicated', 'runs', 'runs-sliced', 'direct'])
 def scatter_slices(request):
-    """Forces the sliced multi-pass scatter (normally used when the output exceeds L2) on small outputs."""
-    old = os.environ.get('TSB_SCATTER_SLICE_BYTES')
-    if request.param is None:
-        os.environ.pop('TSB_SCATTER_SLICE_BYTES', None)
-    else:
-        os.environ['TSB_SCATTER_SLICE_BYTES'] = str(request.param)
+    """Forces the variants the launcher normally picks by size or by probing the index: sliced multi-pass
+    accumulation (outputs larger than L2), accumulation into several copies of the output (small,
+    contended outputs), and the run-combining versus the direct kernels."""
+    names = ('TSB_SCATTER_SLICE_BYTES', 'TSB_SCATTER_REPLICAS', 'TSB_SCATTER_CLUSTERED')
+    old = {k: os.environ.get(k) for k in names}
+    for k in names:
+        os.environ.pop(k, None)
+    if 'sliced' in request.param:
+        os.environ['TSB_SCATTER_SLICE_BYTES'] = '4096'
+    if request.param == 'replicated':
+        os.environ['TSB_SCATTER_REPLICAS'] = '4'
+    if request.param.startswith('runs'):   # the run-combining kernel on any index, clustered or not
+        os.environ['TSB_SCATTER_CLUSTERED'] = '1'
+    if request.param == 'direct':          # the one-update-per-entry kernels, even on a sorted index
+        os.environ['TSB_SCATTER_CLUSTERED'] = '0'
     yield request.param
-    if old is None:
-        os.environ.pop('TSB_SCATTER_SLICE_BYTES', None)
-    else:
-        os.environ['TSB_SCATTER_SLICE_BYTES'] = old
+    for k, v in old.items():
+        if v is None:
+            os.environ.pop(k, None)
+        else:
+            os.environ[k] = v
 
 
 @pytest.mark.parametrize('K', [1, 3, 4, 16, 33, 64])
@@ -175,15 +185,24 @@ def test_scatter_rows(scatter_slices, K):
     B, E, N = 2, 3000, 97
     index = torch.randint(0, N, (1, E, 1), generator=gen)
     index[0, :200, 0] = 5  # a hot target
+    ascending = index.sort(1).values  # an edge list sorted by destination: runs of equal targets
     for dtype in DTYPES:
         src = rand_src(gen, (B, E, K), dtype)
-        for reduce in ('sum', 'mean', 'min', 'max'):
-            want, want_arg = oracle.scatter(src, index, N, reduce)
-            got, got_arg, _ = cabi.scatter(src.cuda(), index.cuda(), N, reduce, (0, 1, 0))
-            what = f'scatter {reduce} {dtype} K={K}'
-            assert_close(got, want, what=what)
-            if want_arg is not None:
-                assert torch.equal(got_arg.cpu(), want_arg), what + ' arg'
+        for ix, order in ((index, 'shuffled'), (ascending, 'ascending')):
+            for reduce in ('sum', 'mean', 'min', 'max'):
+                if order == 'ascending' and dtype not in (torch.float32, torch.int64, torch.bfloat16):
+                    continue
+                want, want_arg = oracle.scatter(src, ix, N, reduce)
+                got, got_arg, _ = cabi.scatter(src.cuda(), ix.cuda(), N, reduce, (0, 1, 0))
+                what = f'scatter {reduce} {dtype} K={K} {order}'
+                if dtype.is_floating_point and reduce in ('sum', 'mean'):
+                    want64 = oracle.scatter(src.double(), ix, N, reduce)[0]
+                    mass64 = oracle.scatter(src.double().abs(), ix, N, reduce)[0]
+                    assert_sum_close(got, want64, mass64, what=what)
+                else:
+                    assert_close(got, want, what=what)
+                if want_arg is not None:
+                    assert torch.equal(got_arg.cpu(), want_arg), what + ' arg'
 
 
 def test_scatter_elements_and_ties():
