@@ -5,11 +5,12 @@
 //   SUM/MEAN  vectorised reductions: one red.global.add.v4.f32 per 16 bytes for fp32 targets, native
 //             atomic adds for f64/i32/i64.  MEAN counts elements per target in an int32 tensor and a
 //             finalize pass divides.
-//   MIN/MAX   floating targets are kept as order-preserving integer keys so that a single native
-//             atomicMin/atomicMax resolves each update; a plain load filters updates that cannot win.
-//             A second pass finds the arg index as the smallest position whose value equals the
-//             result (atomicMin on int64), which is the first-occurrence rule of the CPU loop
-//             (csrc/cpu/reducer.h:63-67).
+//   MIN/MAX   4-byte accumulation types (fp32, int32, and fp16/bf16 compared as fp32): the value's
+//             order-preserving key and the element's position are packed into 64 bits and ONE native
+//             64-bit atomicMax/atomicMin settles value and arg together, first occurrence winning ties
+//             as in the CPU loop (csrc/cpu/reducer.h:63-67); a plain load filters updates that cannot
+//             win.  8-byte types keep ordered keys plus a second pass that takes the smallest position
+//             whose value equals the result.
 //   MUL       compare-and-swap loop (kept for operator-set completeness).
 // When the index is the same for all K features of a row (a broadcast 1-D index, stride_k == 0) the
 // row kernel reads it once per row, moves the row in 16-byte packs and combines the entries of a warp
@@ -567,6 +568,97 @@ __global__ void __launch_bounds__(kThreads) fill_i64_kernel(int64_t *p, int64_t 
   if (i < total) p[i] = value;
 }
 
+// ---- MIN / MAX with arg in ONE pass for 4-byte accumulation types --------------------------------
+// For fp32 / int32 values (fp16 / bf16 compare as fp32) the value's order-preserving 32-bit key and the
+// element's position are packed into one 64-bit word, so a single native 64-bit atomicMax / atomicMin
+// settles value and arg together: MAX keeps (key << 32 | ~pos), MIN keeps (key << 32 | pos), which on
+// equal values prefers the smaller position - the first-occurrence rule of the CPU loop
+// (csrc/cpu/reducer.h:63-67).  The int64 arg_out tensor itself holds the packed words until the
+// finalize kernel splits them, so the source is read once and no extra memory is needed.  Requires
+// E < 2^32 - 1; 8-byte types keep the two-pass scheme further down.
+constexpr uint64_t kNoPos = 0xffffffffull;
+
+template <int OP> __device__ __forceinline__ uint64_t pack_minmax(int32_t key, uint64_t pos) {
+  const uint64_t ukey = (uint32_t)key ^ 0x80000000u;  // signed order -> unsigned order
+  return (ukey << 32) | (OP == kMax ? (kNoPos - pos) : pos);
+}
+template <int OP> __device__ __forceinline__ void atom_packed(uint64_t *addr, uint64_t v) {
+  const uint64_t cur = *reinterpret_cast<volatile uint64_t *>(addr);  // filters updates that cannot win
+  if (OP == kMax) {
+    if (v > cur) atomicMax(reinterpret_cast<unsigned long long *>(addr), (unsigned long long)v);
+  } else {
+    if (v < cur) atomicMin(reinterpret_cast<unsigned long long *>(addr), (unsigned long long)v);
+  }
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(kThreads) packed_init_kernel(const T *out, uint64_t *packed, int64_t total, int fresh) {
+  using U = acc_t<T>;
+  const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i >= total) return;
+  const U v = fresh ? reduce_identity<T, OP>() : to_acc<T>(out[i]);
+  packed[i] = pack_minmax<OP>(enc_key(v), kNoPos);  // position "none"
+}
+
+// One element: NaN never wins; on a write-only output a value equal to the identity never wins either
+// (the CPU loop compares strictly against the identity it started from).
+template <typename T, int OP>
+__device__ __forceinline__ void packed_update(uint64_t *addr, T x, int64_t e, int fresh) {
+  using U = acc_t<T>;
+  const U v = to_acc<T>(x);
+  if (is_nan(v) || (fresh && v == reduce_identity<T, OP>())) return;
+  atom_packed<OP>(addr, pack_minmax<OP>(enc_key(v), (uint64_t)e));
+}
+
+template <typename T, int OP, int VEC>
+__global__ void __launch_bounds__(kThreads) packed_rows_kernel(ScatterParams p) {
+  const T *__restrict__ src = static_cast<const T *>(p.src);
+  uint64_t *packed = reinterpret_cast<uint64_t *>(p.arg_out);
+  const int L = 1 << p.l_log2;
+  const int64_t Kv = p.K / VEC;
+  const int64_t entry = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> p.l_log2;
+  const int col = threadIdx.x & (L - 1);
+  if (entry >= p.B * p.E) return;
+  const int64_t b = entry / p.E, e = entry - b * p.E;
+  const int64_t idx = p.index[b * p.sb + e * p.se];
+  if (idx < 0 || idx >= p.N) return;
+  const int64_t obase = (b * p.N + idx) * p.K;
+  for (int64_t c = col; c < Kv; c += L) {
+    const Pack<T, VEC> v = ld_stream<T, VEC>(src + entry * p.K + c * VEC);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) packed_update<T, OP>(packed + obase + c * VEC + i, v.v[i], e, p.fresh);
+  }
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(kThreads) packed_elems_kernel(ScatterParams p) {
+  const T *__restrict__ src = static_cast<const T *>(p.src);
+  uint64_t *packed = reinterpret_cast<uint64_t *>(p.arg_out);
+  const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i >= p.B * p.E * p.K) return;
+  const int64_t k = i % p.K, be = i / p.K;
+  const int64_t b = be / p.E, e = be - b * p.E;
+  const int64_t idx = p.index[b * p.sb + e * p.se + k * p.sk];
+  if (idx < 0 || idx >= p.N) return;
+  packed_update<T, OP>(packed + (b * p.N + idx) * p.K + k, src[i], e, p.fresh);
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(kThreads)
+packed_finalize_kernel(T *out, int64_t *arg_out, int64_t total, int64_t E, int fresh) {
+  using U = acc_t<T>;
+  const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i >= total) return;
+  const uint64_t w = reinterpret_cast<const uint64_t *>(arg_out)[i];
+  const int32_t key = (int32_t)((uint32_t)(w >> 32) ^ 0x80000000u);
+  U v = dec_key<U>(key);
+  uint64_t pos = w & kNoPos;
+  if (OP == kMax) pos = kNoPos - pos;
+  if (fresh && pos == kNoPos) v = (U)0;  // nothing won: the identity is masked to 0
+  out[i] = from_acc<T>(v);
+  arg_out[i] = pos == kNoPos ? E : (int64_t)pos;
+}
+
 // ---- arg pass ----------------------------------------------------------------------------------
 __device__ __forceinline__ void arg_min(int64_t *a, int64_t e) {
   if (e < *reinterpret_cast<volatile int64_t *>(a)) atomicMin(reinterpret_cast<long long *>(a), (long long)e);
@@ -716,6 +808,33 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
   if (slice_rows < 1) slice_rows = 1;
   const bool sliced = OP == kSum && rows && replicas == 1 && p.E > 0 && p.B * p.N > slice_rows + slice_rows / 2 &&
                       p.K * (int64_t)sizeof(T) >= 128;
+
+  // MIN / MAX on 4-byte accumulation types: value and arg in one pass through packed 64-bit atomics
+  if constexpr (kMinMax && sizeof(U) == 4) {
+    // (small, contended outputs do better with the replicated two-pass scheme below)
+    if (p.E < 0xfffffffell && replicas == 1) {
+      if (total == 0) return TSB_OK;
+      if (!grid_for(total, &blocks)) return TSB_ERR_TOO_LARGE;
+      packed_init_kernel<T, OP><<<blocks, kThreads, 0, stream>>>(static_cast<const T *>(p.out),
+                                                                  reinterpret_cast<uint64_t *>(p.arg_out), total, p.fresh);
+      if (p.E > 0) {
+        const bool vec_ok = rows && (p.K % kFull == 0) && aligned16(p.src);
+        const int64_t Kv = p.K / (vec_ok ? kFull : 1);
+        p.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
+        if (rows) {
+          if (!grid_for((p.B * p.E) << p.l_log2, &blocks)) return TSB_ERR_TOO_LARGE;
+          if (vec_ok) packed_rows_kernel<T, OP, kFull><<<blocks, kThreads, 0, stream>>>(p);
+          else packed_rows_kernel<T, OP, 1><<<blocks, kThreads, 0, stream>>>(p);
+        } else {
+          if (!grid_for(p.B * p.E * p.K, &blocks)) return TSB_ERR_TOO_LARGE;
+          packed_elems_kernel<T, OP><<<blocks, kThreads, 0, stream>>>(p);
+        }
+      }
+      if (!grid_for(total, &blocks)) return TSB_ERR_TOO_LARGE;
+      packed_finalize_kernel<T, OP><<<blocks, kThreads, 0, stream>>>(static_cast<T *>(p.out), p.arg_out, total, p.E, p.fresh);
+      return launch_status();
+    }
+  }
 
   // 1. bring the target to its starting state
   if (total > 0) {
