@@ -31,9 +31,10 @@ FEAT = 64
 SEED = 20240602
 METRIC = 'segment_csr+scatter sum effective HBM bandwidth (F=64, fp32, power-law CSR)'
 UNIT = 'GB/s'
-# Per-launch DRAM traffic of csr_stream_kernel on the full workload, from the ncu capture summarised
-# in profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until a capture exists.
-CSR_KERNEL_DRAM_TRAFFIC_BYTES = None
+# Per-launch DRAM traffic of csr_stream_kernel on the full workload (dram__bytes_read.sum 4341.2 MB +
+# dram__bytes_write.sum 270.5 MB, 1-pass ncu capture summarised in
+# profiles/bench_launch_list_csr_scatter_F64_fp32.md); the algorithmic bytes are 4603.0 MB.
+CSR_KERNEL_DRAM_TRAFFIC_BYTES = 4_611_700_000
 
 
 def row_lengths(rows, seed, force_long=8):
@@ -308,13 +309,14 @@ def run_ours(args):
             'ops': {'segment_csr_sum': {'ms': csr_ms, 'GB/s': csr_gbs, 'frac_of_peak': csr_gbs / peak},
                     'scatter_sum': {'ms': sc_ms, 'GB/s': sc_gbs, 'frac_of_peak': sc_gbs / peak},
                     'reduce_scatter_ms': coll_ms},
-            'roofline': {'bound': 'hbm', 'kernel': 'csr_stream_kernel<float,sum,VEC=4,D=8>', 'achieved': csr_gbs, 'peak': peak,
+            'roofline': {'bound': 'hbm', 'kernel': 'csr_stream_kernel<float,sum,VEC=4>', 'achieved': csr_gbs, 'peak': peak,
                          'unit': 'GB/s', 'frac': csr_gbs / peak, 'traffic': CSR_KERNEL_DRAM_TRAFFIC_BYTES,
                          'peak_source': peak_src, 'algorithmic_bytes_per_launch': b[0][0]},
             'e2e': {'value': (b_csr + b_sc) / (e2e_ms * 1e-3) / 1e9, 'unit': UNIT, 'ms_per_step': e2e_ms,
                     'steps': e2e_steps, 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h},
-            # per step: csr_stream_kernel + csr_fixup_kernel + one scatter_rows_range_kernel per output slice
-            'gpu_launches': (2 + scatter_passes) * args.steps,
+            # per step: csr_stream_kernel + csr_fixup_kernel + scatter_probe_kernel + per output slice one
+            # scatter_rows_range_kernel and one scatter_rows_runs_kernel (the probe's flag makes one of them exit)
+            'gpu_launches': (3 + 2 * scatter_passes) * args.steps,
             'clocks': clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
