@@ -151,6 +151,17 @@ int tsb_scatter(const void *src, const int64_t *index, void *out, int64_t *arg_o
                 int dtype, int reduce, int out_seeded,
                 void *workspace, size_t workspace_bytes, tsb_stream_t stream);
 
+/* One slice of an unsorted scatter SUM, for sharded use: adds the E edges of this call (src [E,K], 1-D index [E])
+ * into the target rows [row_lo, row_hi) of `partial` [N,K], after zeroing exactly those rows; targets outside the
+ * slice are ignored.  `partial` is held in accumulation precision: fp32 for fp32/fp16/bf16 sources, the source
+ * type otherwise.  A caller that shards the edge dimension over GPUs runs one call per slice and can hand each
+ * finished slice to a collective while the next slice is being accumulated (upstream has no sharded path; this
+ * is the building block of the multi-GPU scatter here, built on the kernels of tsb_scatter).
+ *   workspace            at least 256 bytes, 256-byte aligned (the index probe's flag). */
+int tsb_scatter_sum_slice(const void *src, const int64_t *index, void *partial, int64_t E, int64_t K, int64_t N,
+                          int dtype, int64_t row_lo, int64_t row_hi, void *workspace, size_t workspace_bytes,
+                          tsb_stream_t stream);
+
 /* Backward of scatter SUM / MEAN: grad_in[b,e,k] = grad_out[b, index(b,e,k), k] (/ max(count,1)).
  * Replaces the torch::gather calls in ScatterSum/ScatterMean::backward, csrc/scatter.cpp:72-80,149-160.
  * count may be null (SUM); otherwise the int32 tensor tsb_scatter filled for MEAN. */

@@ -223,7 +223,8 @@ __global__ void __launch_bounds__(kThreads) scatter_rows_direct_kernel(ScatterPa
   if (p.count != nullptr && col == 0 && (p.sb != 0 || b == 0)) atomicAdd(p.count + (p.sb ? b : 0) * p.N + idx, 1);
 }
 
-constexpr int kRangeBatches = 4;  // 32-entry batches a warp looks at per launch slot
+constexpr int kRangeBatches = 4;  // 32-entry batches per group: a group is 128 consecutive entries
+constexpr int kRangeGroups = 8;   // consecutive groups a warp walks through
 
 template <typename T, int OP, int VEC>
 __global__ void __launch_bounds__(kThreads) scatter_rows_range_kernel(ScatterParams p, int64_t lo, int64_t hi) {
@@ -242,61 +243,77 @@ __global__ void __launch_bounds__(kThreads) scatter_rows_range_kernel(ScatterPar
   const int eps = 32 >> p.l_log2;
   const int64_t Kv = p.K / VEC;
   const int64_t M = p.B * p.E;
-  const int64_t base = ((int64_t)blockIdx.x * kWarps + warp) * kCap;
-  if (base >= M || *p.clustered != 0) return;  // warp-uniform
-  // all index loads of the warp's batches are issued before any is used
-  int64_t ent[kRangeBatches], trow[kRangeBatches];
+  const int64_t first = ((int64_t)blockIdx.x * kWarps + warp) * (kCap * kRangeGroups);
+  if (first >= M || *p.clustered != 0) return;  // warp-uniform
+
+  // target rows (over all batches) of the 128 entries starting at `gbase`; -1: none / out of range
+  auto load_targets = [&](int64_t gbase, int64_t (&t)[kRangeBatches]) {
 #pragma unroll
-  for (int q = 0; q < kRangeBatches; ++q) {
-    ent[q] = base + q * 32 + lane;
-    trow[q] = -1;
-    if (ent[q] < M) {
-      const int64_t b = (p.B == 1) ? 0 : ent[q] / p.E;
-      const int64_t e = ent[q] - b * p.E;
-      const int64_t idx = p.index[b * p.sb + e * p.se];
-      if (idx >= 0 && idx < p.N) trow[q] = b * p.N + idx;
-    }
-  }
-  int n = 0;
-#pragma unroll
-  for (int q = 0; q < kRangeBatches; ++q) {
-    const bool match = trow[q] >= lo && trow[q] < hi;
-    const unsigned mask = __ballot_sync(kFullMask, match);
-    if (match) {
-      const int r = n + __popc(mask & ((1u << lane) - 1u));
-      s_ent[warp][r] = ent[q];
-      s_trow[warp][r] = trow[q];
-    }
-    n += __popc(mask);
-  }
-  __syncwarp();
-  for (int64_t cb = 0; cb < Kv; cb += L) {
-    const int64_t c = cb + col;
-    const bool col_ok = c < Kv;
-    for (int i = 0; i < n; i += kSteps * eps) {
-      Pack<T, VEC> v[kSteps];
-      int64_t tr[kSteps];
-      bool ok[kSteps];
-#pragma unroll
-      for (int u = 0; u < kSteps; ++u) {
-        const int m = i + u * eps + sub;
-        ok[u] = col_ok && m < n;
-        if (ok[u]) {
-          tr[u] = s_trow[warp][m];
-          v[u] = ld_stream<T, VEC>(src + s_ent[warp][m] * p.K + c * VEC);
-        }
+    for (int q = 0; q < kRangeBatches; ++q) {
+      const int64_t ent = gbase + q * 32 + lane;
+      t[q] = -1;
+      if (ent < M) {
+        const int64_t b = (p.B == 1) ? 0 : ent / p.E;
+        const int64_t idx = p.index[b * p.sb + (ent - b * p.E) * p.se];
+        if (idx >= 0 && idx < p.N) t[q] = b * p.N + idx;
       }
+    }
+  };
+
+  int64_t next[kRangeBatches];
+  load_targets(first, next);
+  for (int g = 0; g < kRangeGroups; ++g) {
+    const int64_t gbase = first + (int64_t)g * kCap;
+    if (gbase >= M) break;  // warp-uniform
+    int64_t trow[kRangeBatches];
 #pragma unroll
-      for (int u = 0; u < kSteps; ++u) {
-        if (ok[u]) {
-          apply_pack<OP, T, VEC>(target + tr[u] * p.K + c * VEC, v[u]);
-          if (p.count != nullptr && c == 0) {
-            const int64_t b = tr[u] / p.N;
-            if (p.sb != 0 || b == 0) atomicAdd(p.count + (p.sb ? tr[u] : tr[u] - b * p.N), 1);
+    for (int q = 0; q < kRangeBatches; ++q) trow[q] = next[q];
+    // the next group's index loads stay in flight while this group's rows are moved: with few matches
+    // per group (many slices) a warp would otherwise spend most of its time waiting for indices
+    if (g + 1 < kRangeGroups && gbase + kCap < M) load_targets(gbase + kCap, next);
+
+    int n = 0;
+#pragma unroll
+    for (int q = 0; q < kRangeBatches; ++q) {
+      const bool match = trow[q] >= lo && trow[q] < hi;
+      const unsigned mask = __ballot_sync(kFullMask, match);
+      if (match) {
+        const int r = n + __popc(mask & ((1u << lane) - 1u));
+        s_ent[warp][r] = gbase + q * 32 + lane;
+        s_trow[warp][r] = trow[q];
+      }
+      n += __popc(mask);
+    }
+    __syncwarp();
+    for (int64_t cb = 0; cb < Kv; cb += L) {
+      const int64_t c = cb + col;
+      const bool col_ok = c < Kv;
+      for (int i = 0; i < n; i += kSteps * eps) {
+        Pack<T, VEC> v[kSteps];
+        int64_t tr[kSteps];
+        bool ok[kSteps];
+#pragma unroll
+        for (int u = 0; u < kSteps; ++u) {
+          const int m = i + u * eps + sub;
+          ok[u] = col_ok && m < n;
+          if (ok[u]) {
+            tr[u] = s_trow[warp][m];
+            v[u] = ld_stream<T, VEC>(src + s_ent[warp][m] * p.K + c * VEC);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kSteps; ++u) {
+          if (ok[u]) {
+            apply_pack<OP, T, VEC>(target + tr[u] * p.K + c * VEC, v[u]);
+            if (p.count != nullptr && c == 0) {
+              const int64_t b = tr[u] / p.N;
+              if (p.sb != 0 || b == 0) atomicAdd(p.count + (p.sb ? tr[u] : tr[u] - b * p.N), 1);
+            }
           }
         }
       }
     }
+    __syncwarp();  // the list is rebuilt by the next group
   }
 }
 
@@ -866,7 +883,8 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
       const char *force_env = std::getenv("TSB_SCATTER_CLUSTERED");  // test hook: "0" / "1"
       const int forced = (force_env != nullptr && (*force_env == '0' || *force_env == '1')) ? (*force_env - '0') : -1;
       scatter_probe_kernel<<<1, kThreads, 0, stream>>>(p, flag, forced);
-      unsigned blocks_direct = 0, blocks_batched = 0;
+      unsigned blocks_direct = 0, blocks_batched = 0, blocks_range = 0;
+      if (!grid_for((p.B * p.E + kRangeBatches * kRangeGroups - 1) / (kRangeBatches * kRangeGroups), &blocks_range)) return TSB_ERR_TOO_LARGE;  // 1024 entries per warp
       if (!grid_for((p.B * p.E) << p.l_log2, &blocks_direct)) return TSB_ERR_TOO_LARGE;                    // L lanes per entry
       if (!grid_for((p.B * p.E + kBatches - 1) / kBatches, &blocks_batched)) return TSB_ERR_TOO_LARGE;  // 128 entries per warp
       const bool zero_slices = sliced && !k16 && p.fresh;
@@ -878,11 +896,11 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
                                            (size_t)((hi - lo) * p.K) * sizeof(U), stream) != cudaSuccess)
           return TSB_ERR_LAUNCH;
         if (vec_ok) {
-          if (sliced) scatter_rows_range_kernel<T, OP, kFull><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi);
+          if (sliced) scatter_rows_range_kernel<T, OP, kFull><<<blocks_range, kThreads, 0, stream>>>(p, lo, hi);
           else scatter_rows_direct_kernel<T, OP, kFull><<<blocks_direct, kThreads, 0, stream>>>(p);
           scatter_rows_runs_kernel<T, OP, kFull><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi, replicas);
         } else {
-          if (sliced) scatter_rows_range_kernel<T, OP, 1><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi);
+          if (sliced) scatter_rows_range_kernel<T, OP, 1><<<blocks_range, kThreads, 0, stream>>>(p, lo, hi);
           else scatter_rows_direct_kernel<T, OP, 1><<<blocks_direct, kThreads, 0, stream>>>(p);
           scatter_rows_runs_kernel<T, OP, 1><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi, replicas);
         }
@@ -987,6 +1005,59 @@ extern "C" int tsb_scatter(const void *src, const int64_t *index, void *out, int
       case TSB_MUL: return run_scatter<scalar_t, kMul>(p, reduce, workspace, stream);
       default: return TSB_ERR_REDUCE;
     }
+  });
+}
+
+namespace tsb {
+namespace {
+// Sums of one edge shard into the target rows [row_lo, row_hi) of a partial held in accumulation
+// precision: zero the slice, then the probe and the row kernels restricted to the slice.
+template <typename T>
+int run_scatter_sum_slice(ScatterParams p, int64_t row_lo, int64_t row_hi, int *flag, cudaStream_t stream) {
+  using U = acc_t<T>;
+  constexpr int kFull = full_vec<T>();
+  if (row_hi <= row_lo || p.K == 0) return TSB_OK;
+  if (cudaMemsetAsync(static_cast<U *>(p.target) + row_lo * p.K, 0, (size_t)((row_hi - row_lo) * p.K) * sizeof(U),
+                      stream) != cudaSuccess)
+    return TSB_ERR_LAUNCH;
+  if (p.E == 0) return TSB_OK;
+  const bool vec_ok = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.target);
+  const int64_t Kv = p.K / (vec_ok ? kFull : 1);
+  p.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
+  p.clustered = flag;
+  unsigned blocks = 0, blocks_range = 0;
+  if (!grid_for((p.E + kBatches - 1) / kBatches, &blocks)) return TSB_ERR_TOO_LARGE;
+  if (!grid_for((p.E + kRangeBatches * kRangeGroups - 1) / (kRangeBatches * kRangeGroups), &blocks_range)) return TSB_ERR_TOO_LARGE;
+  scatter_probe_kernel<<<1, kThreads, 0, stream>>>(p, flag, -1);
+  if (vec_ok) {
+    scatter_rows_range_kernel<T, kSum, kFull><<<blocks_range, kThreads, 0, stream>>>(p, row_lo, row_hi);
+    scatter_rows_runs_kernel<T, kSum, kFull><<<blocks, kThreads, 0, stream>>>(p, row_lo, row_hi, 1);
+  } else {
+    scatter_rows_range_kernel<T, kSum, 1><<<blocks_range, kThreads, 0, stream>>>(p, row_lo, row_hi);
+    scatter_rows_runs_kernel<T, kSum, 1><<<blocks, kThreads, 0, stream>>>(p, row_lo, row_hi, 1);
+  }
+  return launch_status();
+}
+}  // namespace
+}  // namespace tsb
+
+extern "C" int tsb_scatter_sum_slice(const void *src, const int64_t *index, void *partial, int64_t E, int64_t K,
+                                     int64_t N, int dtype, int64_t row_lo, int64_t row_hi, void *workspace,
+                                     size_t workspace_bytes, tsb_stream_t stream) {
+  using namespace tsb;
+  if (E < 0 || K < 0 || N < 0 || row_lo < 0 || row_hi > N) return TSB_ERR_ARG;
+  if (N * K == 0 || row_hi <= row_lo) return TSB_OK;
+  if (partial == nullptr || (E > 0 && (src == nullptr || index == nullptr))) return TSB_ERR_ARG;
+  if (workspace == nullptr || workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return TSB_ERR_WORKSPACE;
+  ScatterParams p;
+  p.src = src; p.index = index; p.out = partial; p.target = partial;
+  p.arg_out = nullptr; p.count = nullptr;
+  p.B = 1; p.E = E; p.K = K; p.N = N;
+  p.sb = 0; p.se = 1; p.sk = 0;
+  p.l_log2 = 0; p.fresh = 1; p.replicas = 1; p.clustered = nullptr;
+  return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
+    return run_scatter_sum_slice<scalar_t>(p, row_lo, row_hi, static_cast<int *>(workspace),
+                                           reinterpret_cast<cudaStream_t>(stream));
   });
 }
 

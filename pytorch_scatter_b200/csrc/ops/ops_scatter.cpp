@@ -272,6 +272,33 @@ torch::Tensor gather_rows(torch::Tensor src, torch::Tensor index, int64_t dim) {
   return GatherRows::apply(src, index, dim)[0];
 }
 
+// Sharded building block: sums of this rank's edges (src [E, ...], 1-D index [E]) into the target rows
+// [row_lo, row_hi) of `partial` [N, ...], which is held in accumulation precision (fp32 for 16-bit sources).
+// Not differentiable; used by pytorch_scatter_b200.dist to overlap the collective with the next slice.
+torch::Tensor scatter_sum_slice(torch::Tensor src, torch::Tensor index, torch::Tensor partial, int64_t row_lo,
+                                int64_t row_hi) {
+  TSB_CHECK_CUDA(src);
+  TSB_CHECK_CUDA(index);
+  TSB_CHECK_CUDA(partial);
+  check_index_dtype(index, "index");
+  c10::cuda::CUDAGuard guard(src.device());
+  TSB_CHECK_INPUT(index.dim() == 1 && src.dim() >= 1 && src.size(0) == index.size(0));
+  TSB_CHECK_INPUT(partial.dim() == src.dim() && partial.is_contiguous());
+  for (int64_t i = 1; i < src.dim(); i++) TSB_CHECK_INPUT(src.size(i) == partial.size(i));
+  const bool k16 = src.scalar_type() == at::ScalarType::Half || src.scalar_type() == at::ScalarType::BFloat16;
+  TORCH_CHECK(partial.scalar_type() == (k16 ? at::ScalarType::Float : src.scalar_type()),
+              "partial must be float32 for 16-bit sources and of the source dtype otherwise");
+  src = src.contiguous();
+  index = index.contiguous();
+  const int64_t E = src.size(0), N = partial.size(0);
+  const int64_t K = E > 0 ? src.numel() / E : (N > 0 ? partial.numel() / N : 0);
+  auto workspace = torch::empty({256}, src.options().dtype(torch::kUInt8));
+  check_status(tsb_scatter_sum_slice(src.data_ptr(), index.data_ptr<int64_t>(), partial.data_ptr(), E, K, N,
+                                     dtype_enum(src), row_lo, row_hi, workspace.data_ptr(), 256, current_stream()),
+               "tsb_scatter_sum_slice");
+  return partial;
+}
+
 torch::Tensor scatter_sum(torch::Tensor src, torch::Tensor index, int64_t dim,
                           std::optional<torch::Tensor> optional_out, std::optional<int64_t> dim_size) {
   return ScatterSumMean<false>::apply(src, index, dim, optional_out, dim_size)[0];
@@ -308,4 +335,5 @@ TORCH_LIBRARY_FRAGMENT(torch_scatter, m) {
   m.def("scatter_max", &tsb_ops::scatter_max);
   // not part of upstream's operator set: the index read-back its composites do with Tensor.gather
   m.def("gather_rows", &tsb_ops::gather_rows);
+  m.def("scatter_sum_slice", &tsb_ops::scatter_sum_slice);
 }

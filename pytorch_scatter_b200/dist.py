@@ -114,6 +114,73 @@ def scatter_sharded(src_local: torch.Tensor, index_local: torch.Tensor, dim_size
     raise ValueError(reduce)
 
 
+def overlapped_layout(dim_size: int, world: int, row_bytes: int, pass_bytes: int = 128 << 20) -> Tuple[int, int]:
+    """``(passes, sub)`` of :func:`scatter_sum_overlapped`: the output rows are processed in ``passes`` slices of
+    ``sub * world`` rows each (about ``pass_bytes``), and within every slice rank ``r`` owns the ``r``-th run of
+    ``sub`` rows."""
+    rows_per_pass = max(world, min(max(dim_size, 1), pass_bytes // max(1, row_bytes)))
+    passes = max(1, -(-dim_size // rows_per_pass))
+    sub = -(-dim_size // (passes * world))
+    return passes, sub
+
+
+def owned_rows(dim_size: int, world: int, rank: int, passes: int, sub: int, device=None) -> torch.Tensor:
+    """Global output rows behind the tensor :func:`scatter_sum_overlapped` returns on ``rank`` (ids past
+    ``dim_size`` are padding)."""
+    base = torch.arange(passes, device=device).view(-1, 1) * (sub * world) + rank * sub
+    return (base + torch.arange(sub, device=device).view(1, -1)).reshape(-1)
+
+
+def scatter_sum_overlapped(src_local: torch.Tensor, index_local: torch.Tensor, dim_size: int, group=None,
+                           pass_bytes: int = 128 << 20, slice_reduce: Optional[Callable] = None) -> torch.Tensor:
+    """Edge-sharded ``scatter(sum)`` along dim 0 whose collective overlaps the local accumulation.
+
+    The local accumulation runs slice by slice over the output rows (a slice of about ``pass_bytes`` stays
+    L2-resident, which is also how the single-GPU scatter treats large outputs).  As soon as a slice is final
+    it is reduce-scattered over the ranks on a side stream - all links busy, every rank receiving its share of
+    the slice - while the next slice is accumulated.  Ownership is therefore interleaved: within every slice,
+    rank ``r`` owns the ``r``-th run of ``sub`` rows (see :func:`overlapped_layout` / :func:`owned_rows`).
+    Returns this rank's ``passes * sub`` rows in accumulation precision (fp32 for 16-bit sources).
+
+    ``slice_reduce(src, index, partial, row_lo, row_hi)`` fills the slice; it defaults to this package's
+    ``scatter_sum_slice`` operator (CPU tests inject a reference).
+    """
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    feat = tuple(src_local.shape[1:])
+    acc_dtype = torch.float32 if src_local.dtype in (torch.float16, torch.bfloat16) else src_local.dtype
+    row_bytes = max(1, int(torch.tensor(feat).prod()) if feat else 1) * torch.empty((), dtype=acc_dtype).element_size()
+    passes, sub = overlapped_layout(dim_size, world, row_bytes, pass_bytes)
+    rows_per_pass = sub * world
+    partial = torch.empty((passes * rows_per_pass,) + feat, dtype=acc_dtype, device=src_local.device)
+    mine = torch.empty((passes * sub,) + feat, dtype=acc_dtype, device=src_local.device)
+    if slice_reduce is None:
+        slice_reduce = torch.ops.torch_scatter.scatter_sum_slice
+    on_gpu = src_local.is_cuda
+    nccl = dist.get_backend(group) == 'nccl'
+    comm = torch.cuda.Stream(device=src_local.device) if on_gpu else None
+    work = []
+    for j in range(passes):
+        lo, hi = j * rows_per_pass, (j + 1) * rows_per_pass
+        slice_reduce(src_local, index_local, partial, lo, hi)
+        if on_gpu:
+            done = torch.cuda.Event()
+            done.record()
+            comm.wait_event(done)
+        piece, dst = partial[lo:hi], mine[j * sub:(j + 1) * sub]
+        if nccl:
+            with torch.cuda.stream(comm):
+                work.append(dist.reduce_scatter_tensor(dst, piece, op=dist.ReduceOp.SUM, group=group, async_op=True))
+        else:  # backends without reduce_scatter_tensor (gloo): all-reduce, keep the own share
+            tmp = piece.clone()
+            dist.all_reduce(tmp, op=dist.ReduceOp.SUM, group=group)
+            dst.copy_(tmp[rank * sub:(rank + 1) * sub])
+    for w in work:
+        w.wait()
+    if on_gpu:
+        torch.cuda.current_stream().wait_stream(comm)
+    return mine
+
+
 def _cuda_local_reduce(src, index, dim_size, reduce):
     from . import scatter_max, scatter_min, scatter_sum
     if reduce == 'sum':

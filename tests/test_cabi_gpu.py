@@ -268,3 +268,23 @@ def test_backward_kernels():
     want = torch.zeros(B, E + 1, K).scatter_(1, arg, grad_out)[:, :E]
     got = cabi.arg_backward(grad_out.cuda(), arg.cuda(), E)
     assert_close(got, want, exact=True, what='arg_backward')
+
+
+def test_scatter_sum_slice():
+    """The sharded building block: each call fills (only) its slice of target rows of the partial."""
+    import pytorch_scatter_b200  # noqa: F401  (registers the operator)
+    gen = torch.Generator().manual_seed(55)
+    E, K, N = 5000, 64, 300
+    index = torch.randint(0, N, (E,), generator=gen)
+    for dtype in (torch.float32, torch.bfloat16, torch.int64):
+        src = rand_src(gen, (E, K), dtype)
+        acc = torch.float32 if dtype == torch.bfloat16 else dtype
+        partial = torch.full((N, K), 7, dtype=acc).cuda()
+        for lo, hi in ((0, 100), (100, 257), (257, 300)):
+            torch.ops.torch_scatter.scatter_sum_slice(src.cuda(), index.cuda(), partial, lo, hi)
+        want = oracle.scatter(src.to(acc).view(1, E, K), index.view(1, E, 1), N, 'sum')[0][0]
+        assert_close(partial, want, what=f'scatter_sum_slice {dtype}')
+        # a slice call leaves the other rows alone
+        before = partial.clone()
+        torch.ops.torch_scatter.scatter_sum_slice(src.cuda(), index.cuda(), partial, 10, 20)
+        assert torch.equal(partial[:10], before[:10]) and torch.equal(partial[20:], before[20:])

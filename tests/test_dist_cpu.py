@@ -77,6 +77,27 @@ def _worker(rank, world, port, results):
             else:
                 got = torch.cat(blocks)[:n_targets]
                 ok[reduce] = torch.allclose(got, want, rtol=1e-5, atol=1e-5)
+        # --- the overlapped variant: slices of whole owner blocks, each reduced to its owner when final
+        from pytorch_scatter_b200.dist import scatter_sum_overlapped
+
+        def slice_reduce(s, ix, partial, lo, hi):
+            keep = (ix >= lo) & (ix < hi)  # targets outside the slice (padding rows included) are ignored
+            full, _ = oracle_scatter(s[keep], ix[keep], 0, partial.size(0), 'sum')
+            partial[lo:hi] = full[lo:hi]
+            return partial
+
+        from pytorch_scatter_b200.dist import overlapped_layout, owned_rows
+        for pass_bytes in (1, 40, 1 << 30):  # smallest slices / several / everything in one pass
+            mine = scatter_sum_overlapped(src_q[e_lo:e_hi], index[e_lo:e_hi], n_targets, pass_bytes=pass_bytes,
+                                          slice_reduce=slice_reduce)
+            passes, sub = overlapped_layout(n_targets, world, feat * 4, pass_bytes)
+            pieces = [None] * world
+            dist.all_gather_object(pieces, (owned_rows(n_targets, world, rank, passes, sub), mine))
+            want, _ = oracle_scatter(src_q, index, 0, n_targets, 'sum')
+            got = torch.zeros(passes * sub * world, feat)
+            for rows_r, vals in pieces:
+                got[rows_r] = vals
+            ok[f'overlapped-{pass_bytes}'] = torch.allclose(got[:n_targets], want, rtol=1e-5, atol=1e-5)
         results[rank] = (ok_csr, ok)
     finally:
         dist.destroy_process_group()
