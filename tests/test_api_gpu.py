@@ -1,0 +1,226 @@
+"""Drop-in behaviour of the public Python API on a GPU, in the style of the upstream test-suite: scripted
+versus eager calls, float64 gradient checks, the `out=` argument, non-contiguous inputs, index
+broadcasting, zero-sized tensors and the composites against torch's own per-group functions.
+Inputs come from the upstream known-answer tables stored in tests/golden/known_answers.pt."""
+from itertools import product
+
+import pytest
+import torch
+from torch.autograd import gradcheck
+
+from helpers import load_golden
+
+pytestmark = pytest.mark.gpu
+
+DEV = 'cuda'
+DTYPES = [torch.half, torch.bfloat16, torch.float, torch.double, torch.int, torch.long]
+REDUCTIONS = ['sum', 'add', 'mean', 'min', 'max']
+
+
+def tens(x, dtype):
+    return torch.tensor(x, device=DEV).to(dtype)
+
+
+@pytest.fixture(scope='module')
+def ts():
+    import pytorch_scatter_b200
+    return pytorch_scatter_b200
+
+
+@pytest.fixture(scope='module')
+def tables():
+    return load_golden('known_answers.pt')
+
+
+def _swap_layout(t):
+    """Same values, strides of the transposed-contiguous layout (what upstream's non-contiguous tests use)."""
+    return t.transpose(0, 1).contiguous().transpose(0, 1) if t.dim() > 1 else t
+
+
+@pytest.mark.parametrize('reduce', REDUCTIONS + ['mul'])
+def test_scatter_scripted_equals_eager(ts, tables, reduce):
+    fn = getattr(ts, 'scatter_' + reduce)
+    scripted = torch.jit.script(fn)
+    for case, dtype in product(tables['scatter'], DTYPES):
+        src, index = tens(case['src'], dtype), tens(case['index'], torch.long)
+        a, b = fn(src, index, case['dim']), scripted(src, index, case['dim'])
+        if isinstance(a, tuple):
+            assert a[1].tolist() == b[1].tolist()
+            a, b = a[0], b[0]
+        assert a.tolist() == b.tolist()
+
+
+@pytest.mark.parametrize('reduce', REDUCTIONS)
+def test_segment_scripted_equals_eager(ts, tables, reduce):
+    for kind, key in (('csr', 'indptr'), ('coo', 'index')):
+        fn = getattr(ts, f'segment_{reduce}_{kind}')
+        scripted = torch.jit.script(fn)
+        for case, dtype in product(tables['segment'], (torch.float, torch.long)):
+            src, ix = tens(case['src'], dtype), tens(case[key], torch.long)
+            a, b = fn(src, ix), scripted(src, ix)
+            a, b = (a[0], b[0]) if isinstance(a, tuple) else (a, b)
+            assert a.tolist() == b.tolist()
+
+
+@pytest.mark.parametrize('reduce', REDUCTIONS)
+def test_gradcheck(ts, tables, reduce):
+    for case in tables['scatter']:
+        src = tens(case['src'], torch.double).requires_grad_()
+        index = tens(case['index'], torch.long)
+        assert gradcheck(ts.scatter, (src, index, case['dim'], None, None, reduce))
+    for case in tables['segment']:
+        src = tens(case['src'], torch.double).requires_grad_()
+        assert gradcheck(ts.segment_csr, (src, tens(case['indptr'], torch.long), None, reduce))
+        assert gradcheck(ts.segment_coo, (src, tens(case['index'], torch.long), None, None, reduce))
+
+
+def test_gather_gradcheck(ts, tables):
+    for case in tables['gather']:
+        src = tens(case['src'], torch.double).requires_grad_()
+        assert gradcheck(ts.gather_csr, (src, tens(case['indptr'], torch.long), None))
+        assert gradcheck(ts.gather_coo, (src, tens(case['index'], torch.long), None))
+
+
+@pytest.mark.parametrize('dtype', DTYPES)
+def test_out_argument(ts, tables, dtype):
+    """A given `out` filled with -2: scatter and segment_coo accumulate into it, segment_csr overwrites it."""
+    for case, reduce in product(tables['scatter'], ['sum', 'min', 'max']):
+        src, index = tens(case['src'], dtype), tens(case['index'], torch.long)
+        expected = tens(case[reduce], dtype)
+        out = torch.full_like(expected, -2)
+        res = getattr(ts, 'scatter_' + reduce)(src, index, case['dim'], out)
+        res = res[0] if isinstance(res, tuple) else res
+        assert res.data_ptr() == out.data_ptr()
+        if reduce == 'sum':
+            want = expected - 2
+        elif reduce == 'min':
+            want = torch.full_like(expected, -2)      # every table value is above -2
+        else:
+            want = expected.clone()
+            want[expected == 0] = -2                  # untouched targets keep the given value
+        assert torch.equal(out, want), (case, reduce)
+    for case, reduce in product(tables['segment'], ['sum', 'mean', 'min', 'max']):
+        src = tens(case['src'], dtype)
+        expected = tens(case[reduce], dtype)
+        out = torch.full_like(expected, -2)
+        getattr(ts, f'segment_{reduce}_csr')(src, tens(case['indptr'], torch.long), out)
+        assert torch.equal(out, expected), (case, reduce)
+        if reduce == 'mean':
+            continue
+        out.fill_(-2)
+        getattr(ts, f'segment_{reduce}_coo')(src, tens(case['index'], torch.long), out)
+        if reduce == 'sum':
+            want = expected - 2
+        elif reduce == 'min':
+            want = torch.full_like(expected, -2)
+        else:
+            want = expected.clone()
+            want[expected == 0] = -2
+        assert torch.equal(out, want), (case, reduce)
+    for case in tables['gather']:
+        src, index, indptr = tens(case['src'], dtype), tens(case['index'], torch.long), tens(case['indptr'], torch.long)
+        size = list(src.size())
+        size[index.dim() - 1] = index.size(-1)
+        out = src.new_full(size, -2)
+        ts.gather_csr(src, indptr, out)
+        assert torch.equal(out, tens(case['expected'], dtype))
+        out.fill_(-2)
+        ts.gather_coo(src, index, out)
+        assert torch.equal(out, tens(case['expected'], dtype))
+
+
+@pytest.mark.parametrize('dtype', (torch.float, torch.long, torch.bfloat16))
+def test_non_contiguous_inputs(ts, tables, dtype):
+    for case, reduce in product(tables['scatter'], REDUCTIONS):
+        src, index = _swap_layout(tens(case['src'], dtype)), _swap_layout(tens(case['index'], torch.long))
+        res = getattr(ts, 'scatter_' + reduce)(src, index, case['dim'])
+        if isinstance(res, tuple):
+            assert torch.equal(res[1], tens(case['arg_' + reduce], torch.long))
+            res = res[0]
+        assert torch.equal(res, tens(case[reduce], dtype)), (case, reduce)
+    for case, reduce in product(tables['segment'], REDUCTIONS):
+        src = _swap_layout(tens(case['src'], dtype))
+        for kind, key in (('csr', 'indptr'), ('coo', 'index')):
+            res = getattr(ts, f'segment_{reduce}_{kind}')(src, _swap_layout(tens(case[key], torch.long)))
+            if isinstance(res, tuple):
+                assert torch.equal(res[1], tens(case['arg_' + reduce], torch.long))
+                res = res[0]
+            assert torch.equal(res, tens(case[reduce], dtype)), (case, reduce, kind)
+    for case in tables['gather']:
+        src = _swap_layout(tens(case['src'], dtype))
+        assert torch.equal(ts.gather_csr(src, _swap_layout(tens(case['indptr'], torch.long))), tens(case['expected'], dtype))
+        assert torch.equal(ts.gather_coo(src, _swap_layout(tens(case['index'], torch.long))), tens(case['expected'], dtype))
+
+
+@pytest.mark.parametrize('reduce', REDUCTIONS)
+def test_index_broadcasting_shapes(ts, reduce):
+    B, C, H, W = 4, 3, 8, 8
+    src = torch.randn(B, C, H, W, device=DEV)
+    for index in (torch.randint(0, H, (H,), device=DEV), torch.randint(0, H, (B, 1, H, W), device=DEV)):
+        out = ts.scatter(src, index, dim=2, dim_size=H, reduce=reduce)
+        assert out.size() == (B, C, H, W)
+    from pytorch_scatter_b200.utils import broadcast
+    index = torch.randint(0, H, (B, 1, H, W), device=DEV)
+    got = ts.scatter(src, index, dim=2, dim_size=H, reduce='sum')
+    want = torch.zeros(B, C, H, W, device=DEV).scatter_add_(2, broadcast(index, src, 2), src)
+    assert torch.allclose(got, want, atol=1e-5)
+
+
+@pytest.mark.parametrize("reduce,dtype", list(product(REDUCTIONS, (torch.float, torch.double))))
+def test_zero_sized_tensors(ts, reduce, dtype):
+    x = torch.randn(0, 0, 0, 16, dtype=dtype, device=DEV, requires_grad=True)
+    index = torch.tensor([], dtype=torch.long, device=DEV)
+    indptr = torch.tensor([], dtype=torch.long, device=DEV)
+    for out in (ts.scatter(x, index, dim=0, dim_size=0, reduce=reduce), ts.segment_coo(x, index, dim_size=0, reduce=reduce),
+                ts.gather_coo(x, index), ts.segment_csr(x, indptr, reduce=reduce), ts.gather_csr(x, indptr)):
+        out.backward(torch.randn_like(out))
+        assert out.size() == (0, 0, 0, 16)
+
+
+def test_softmax_family_against_torch(ts):
+    src = torch.tensor([0.2, 0, 0.2, -2.1, 3.2, 7, -1, float('-inf')], device=DEV, requires_grad=True)
+    index = torch.tensor([0, 1, 0, 1, 1, 2, 4, 4], device=DEV)
+    groups = {0: [0, 2], 1: [1, 3, 4], 2: [5], 4: [6, 7]}
+    for fn, ref in ((ts.scatter_softmax, torch.softmax), (ts.scatter_log_softmax, torch.log_softmax)):
+        out = fn(src, index)
+        want = torch.empty_like(out)
+        for members in groups.values():
+            want[members] = ref(src.detach()[members], dim=-1)
+        assert torch.allclose(out, want, equal_nan=True)
+        out.backward(torch.randn_like(out))
+        assert torch.jit.script(fn)(src, index).tolist() == out.tolist()
+
+
+def test_logsumexp_against_torch(ts):
+    x = torch.tensor([0.5, 0.5, 0.0, -2.1, 3.2, 7.0, -1.0, -100.0], device=DEV, requires_grad=True)
+    index = torch.tensor([0, 0, 1, 1, 1, 2, 4, 4], device=DEV)
+    out = ts.scatter_logsumexp(x, index)
+    for piece, got in zip(x.detach().split([2, 3, 1, 0, 2]), out.unbind()):
+        want = torch.logsumexp(piece, dim=0) if piece.numel() > 0 else torch.tensor(0.0, device=DEV)  # empty group -> 0
+        assert torch.allclose(got, want)
+    out.backward(torch.randn_like(out))
+    assert torch.jit.script(ts.scatter_logsumexp)(x, index).tolist() == out.tolist()
+    # a given `out` takes part in the sum; groups nobody writes keep their value
+    acc = torch.tensor([-10.0, -10.0], device=DEV)
+    ts.scatter_logsumexp(src=torch.tensor([-1.0, -50.0], device=DEV), index=torch.tensor([0, 0], device=DEV), out=acc)
+    assert acc.allclose(torch.tensor([-0.9999, -10.0], device=DEV), atol=1e-4)
+
+
+def test_std_against_torch(ts):
+    src = torch.tensor([[2, 0, 1, 4, 3], [0, 2, 1, 3, 4]], dtype=torch.float, device=DEV, requires_grad=True)
+    index = torch.tensor([[0, 0, 0, 0, 0], [1, 1, 1, 1, 1]], device=DEV)
+    out = ts.scatter_std(src, index, dim=-1, unbiased=True)
+    std = src.detach().std(dim=-1, unbiased=True)[0]
+    assert torch.allclose(out, torch.tensor([[std, 0], [0, std]], device=DEV))
+    out.backward(torch.randn_like(out))
+    assert torch.jit.script(ts.scatter_std)(src, index, dim=-1, unbiased=True).tolist() == out.tolist()
+
+
+def test_second_device_if_present(ts):
+    """Operators run on the device of their tensors, not on the current device."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs two GPUs')
+    src = torch.tensor([1.0, 2.0, 3.0, 4.0], device='cuda:1')
+    index = torch.tensor([0, 0, 1, 1], device='cuda:1')
+    assert ts.scatter(src, index, reduce='sum').tolist() == [3.0, 7.0]
+    assert ts.segment_csr(src, torch.tensor([0, 2, 4], device='cuda:1'), reduce='sum').tolist() == [3.0, 7.0]
