@@ -440,10 +440,16 @@ def run_suite(args):
             nb = ROWS * F * s + nnz * 8 + nnz * F * s
             ms, gbs = timeit(lambda: ts.gather_coo(table, index, out), nb, False)
             emit('C3', f'gather_coo {name} F=64', ms, gbs)
+            # composites: bytes of the ideal single read + single write; the fused path reads src twice
+            nb = 2 * nnz * F * s + nnz * 8
+            ms, gbs = timeit(lambda: ts.scatter_softmax(src, index, 0, dim_size=ROWS), nb, False)
+            emit('C3', f'scatter_softmax {name} F=64 (composite)', ms, gbs)
             if dtype == torch.float32:
-                nb = 2 * nnz * F * s + nnz * 8 + 2 * ROWS * F * s
-                ms, gbs = timeit(lambda: ts.scatter_softmax(src, index, 0, dim_size=ROWS), nb, False)
-                emit('C3', 'scatter_softmax fp32 F=64 (composite)', ms, gbs)
+                ms, gbs = timeit(lambda: ts.scatter_log_softmax(src, index, 0, dim_size=ROWS), nb, False)
+                emit('C3', 'scatter_log_softmax fp32 F=64 (composite)', ms, gbs)
+                nb = nnz * F * s + nnz * 8 + ROWS * F * s
+                ms, gbs = timeit(lambda: ts.scatter_logsumexp(src, index, 0, dim_size=ROWS), nb, False)
+                emit('C3', 'scatter_logsumexp fp32 F=64 (composite)', ms, gbs)
             del src, table, out
         del index, indptr
 

@@ -34,7 +34,12 @@ typedef struct CUstream_st *tsb_stream_t;
 enum tsb_dtype { TSB_F32 = 0, TSB_F64 = 1, TSB_F16 = 2, TSB_BF16 = 3, TSB_I32 = 4, TSB_I64 = 5 };
 
 /* reductions (csrc/cuda/reducer.cuh:8-13; "div" is unreachable upstream and is not provided) */
-enum tsb_reduce { TSB_SUM = 0, TSB_MEAN = 1, TSB_MIN = 2, TSB_MAX = 3, TSB_MUL = 4 };
+enum tsb_reduce { TSB_SUM = 0, TSB_MEAN = 1, TSB_MIN = 2, TSB_MAX = 3, TSB_MUL = 4,
+                  /* log-sum-exp per row, segment_csr / segment_coo only, fp32 / fp16 / bf16 only: the per-group
+                   * statistic behind upstream's softmax composites (torch_scatter/composite/softmax.py:9-51,
+                   * logsumexp.py:8-56), computed online in one pass.  `out` is FP32 [B,N,K] for every source dtype;
+                   * rows without entries give -inf; out_seeded must be 0 */
+                  TSB_LSE = 5 };
 
 enum tsb_status {
   TSB_OK = 0,
@@ -125,6 +130,19 @@ int tsb_segment_coo(const void *src, const int64_t *index, void *out, int64_t *a
 int tsb_gather_coo(const void *src, const int64_t *index, void *out, const void *count,
                    int64_t B, int64_t E, int64_t K, int64_t N, int64_t index_batch_stride,
                    int dtype, tsb_stream_t stream);
+
+/* gather_coo with an element-wise epilogue: out[b,e,:] = op(x[b,e,:], table[b,index[b,e],:]), op 1 = exp(x - row),
+ * op 2 = x - row; x and out fp32 / fp16 / bf16, table always FP32 (what TSB_LSE writes).  With table = the TSB_LSE reduction of x these are the second passes of
+ * upstream's scatter_softmax / scatter_log_softmax (torch_scatter/composite/softmax.py:9-51) on a sorted index:
+ * two passes over the source instead of six. */
+int tsb_gather_coo_apply(const void *x, const void *table, const int64_t *index, void *out,
+                         int64_t B, int64_t E, int64_t K, int64_t N, int64_t index_batch_stride,
+                         int dtype, int op, tsb_stream_t stream);
+
+/* Sets *unsorted_flag (a device int) to 1 if the n index entries are not ascending, else to 0.  Lets a caller
+ * pick the sorted-index kernels for an index of unknown order (upstream asserts sortedness instead,
+ * csrc/cuda/segment_coo_cuda.cu:42,111). */
+int tsb_index_unsorted(const int64_t *index, int64_t n, int *unsorted_flag, tsb_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * scatter: out[b, index(b,e,k), k] (+)= src[b,e,k] for an UNSORTED index.

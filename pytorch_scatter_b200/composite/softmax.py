@@ -18,6 +18,16 @@ def _read_back(per_group: torch.Tensor, index: torch.Tensor, full_index: torch.T
     return torch.ops.torch_scatter.gather_rows(per_group, full_index, dim)
 
 
+def _fused_ok(src: torch.Tensor, index: torch.Tensor) -> bool:
+    """The two-pass fused kernels apply: a 1-D ascending index over fp32 / fp16 / bf16 CUDA data.  Checking the
+    order costs one small kernel and a host sync (the same kind upstream pays to infer ``dim_size``)."""
+    if index.dim() != 1 or index.numel() == 0 or not src.is_cuda:
+        return False
+    if not (src.dtype == torch.float32 or src.dtype == torch.float16 or src.dtype == torch.bfloat16):
+        return False
+    return torch.ops.torch_scatter.index_is_sorted(index)
+
+
 def _require_float(src: torch.Tensor, name: str) -> None:
     if not torch.is_floating_point(src):
         raise ValueError(f'`{name}` can only be computed over tensors '
@@ -28,6 +38,8 @@ def scatter_softmax(src: torch.Tensor, index: torch.Tensor,
                     dim: int = -1,
                     dim_size: Optional[int] = None) -> torch.Tensor:
     _require_float(src, 'scatter_softmax')
+    if _fused_ok(src, index):
+        return torch.ops.torch_scatter.softmax_sorted(src, index, dim, dim_size, False)
     full_index = broadcast(index, src, dim)
     group_max = scatter_max(src, full_index, dim=dim, dim_size=dim_size)[0]
     shifted_exp = (src - _read_back(group_max, index, full_index, dim)).exp_()
@@ -39,6 +51,8 @@ def scatter_log_softmax(src: torch.Tensor, index: torch.Tensor, dim: int = -1,
                         eps: float = 1e-12,
                         dim_size: Optional[int] = None) -> torch.Tensor:
     _require_float(src, 'scatter_log_softmax')
+    if _fused_ok(src, index):  # eps (1e-12 under a sum that is at least 1) is below fp32 resolution
+        return torch.ops.torch_scatter.softmax_sorted(src, index, dim, dim_size, True)
     full_index = broadcast(index, src, dim)
     group_max = scatter_max(src, full_index, dim=dim, dim_size=dim_size)[0]
     shifted = src - _read_back(group_max, index, full_index, dim)

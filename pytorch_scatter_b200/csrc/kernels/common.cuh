@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cmath>
 #include <limits>
 #include <type_traits>
 
@@ -13,7 +14,7 @@
 
 namespace tsb {
 
-constexpr int kSum = TSB_SUM, kMean = TSB_MEAN, kMin = TSB_MIN, kMax = TSB_MAX, kMul = TSB_MUL;
+constexpr int kSum = TSB_SUM, kMean = TSB_MEAN, kMin = TSB_MIN, kMax = TSB_MAX, kMul = TSB_MUL, kLse = TSB_LSE;
 constexpr int kThreads = 256;          // CTA size used by every streaming kernel
 constexpr unsigned kFullMask = 0xffffffffu;
 
@@ -68,6 +69,7 @@ template <typename T, int REDUCE> __host__ __device__ __forceinline__ acc_t<T> r
   if (REDUCE == kMin) return (acc_t<T>)Limits<T>::max();
   if (REDUCE == kMax) return (acc_t<T>)Limits<T>::lowest();
   if (REDUCE == kMul) return (acc_t<T>)1;
+  if (REDUCE == kLse) return (acc_t<T>)(-3.402823466e+38f);  // running maximum of the online log-sum-exp
   return (acc_t<T>)0;
 }
 

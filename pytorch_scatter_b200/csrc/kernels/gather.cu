@@ -130,6 +130,8 @@ struct GatherCooParams {
   const int64_t *index;
   void *out;
   const void *count;
+  const void *x;  // optional per-entry operand [B,E,K]: out = op(x, gathered row)
+  int op;         // 1: exp(x - row), 2: x - row (the second passes of softmax / log_softmax)
   int64_t B, E, K, N, bstride;
   int l_log2;
 };
@@ -139,11 +141,32 @@ struct GatherCooParams {
 // With a sorted index neighbouring entries name the same source row, which then comes from L1/L2.
 constexpr int kGatherBatches = 4;
 
-template <typename T, int VEC>
+// A row piece of the fp32 table of the APPLY form: VEC floats fetched 16 bytes at a time.
+template <int VEC> struct FloatRow { float v[VEC]; };
+template <int VEC> __device__ __forceinline__ FloatRow<VEC> ld_float_row(const float *p) {
+  FloatRow<VEC> r;
+  if constexpr (VEC % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < VEC; i += 4) {
+      const float4 t = *reinterpret_cast<const float4 *>(p + i);
+      r.v[i] = t.x; r.v[i + 1] = t.y; r.v[i + 2] = t.z; r.v[i + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) r.v[i] = p[i];
+  }
+  return r;
+}
+
+// APPLY: src is an fp32 table and out[e] = op(x[e], src[index[e]]) (op 1: exp(x - row), 2: x - row).
+template <typename T, int VEC, bool APPLY>
 __global__ void __launch_bounds__(kThreads) gather_coo_kernel(GatherCooParams p) {
+  using Row = typename std::conditional<APPLY, FloatRow<VEC>, Pack<T, VEC>>::type;
   const T *__restrict__ src = static_cast<const T *>(p.src);
+  const float *__restrict__ table = static_cast<const float *>(p.src);
   T *__restrict__ out = static_cast<T *>(p.out);
   const T *__restrict__ count = static_cast<const T *>(p.count);
+  const T *__restrict__ xs = static_cast<const T *>(p.x);  // APPLY: second operand at the entry's own position
   constexpr int kWarps = kThreads / 32;
   constexpr int kSteps = 4;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -175,24 +198,43 @@ __global__ void __launch_bounds__(kThreads) gather_coo_kernel(GatherCooParams p)
       const int64_t c = cb + col;
       const bool col_ok = c < Kv;
       for (int i = 0; i < 32; i += kSteps * eps) {
-        Pack<T, VEC> v[kSteps];
+        Row v[kSteps];
+        Pack<T, VEC> xv[APPLY ? kSteps : 1];
         int64_t r[kSteps];
 #pragma unroll
         for (int u = 0; u < kSteps; ++u) {
           const int m = i + u * eps + sub;  // entry within the batch handled by this lane group
           r[u] = __shfl_sync(kFullMask, (long long)srow[q], m & 31);
           if (m >= 32 || !col_ok) r[u] = -1;
-          if (r[u] >= 0) v[u] = ld_pack<T, VEC>(src + r[u] * p.K + c * VEC);
+          if (r[u] >= 0) {
+            if constexpr (APPLY) {
+              v[u] = ld_float_row<VEC>(table + r[u] * p.K + c * VEC);
+              xv[u] = ld_stream<T, VEC>(xs + (ent0 + i + u * eps + sub) * p.K + c * VEC);
+            } else {
+              v[u] = ld_pack<T, VEC>(src + r[u] * p.K + c * VEC);
+            }
+          }
         }
 #pragma unroll
         for (int u = 0; u < kSteps; ++u) {
           if (r[u] >= 0) {
-            if (count != nullptr) {
-              const T cnt = count[r[u]];
+            const int64_t at = (ent0 + i + u * eps + sub) * p.K + c * VEC;
+            if constexpr (APPLY) {
+              Pack<T, VEC> o;
 #pragma unroll
-              for (int k = 0; k < VEC; ++k) v[u].v[k] = div_t<T>(v[u].v[k], cnt);
+              for (int k = 0; k < VEC; ++k) {
+                const float d = (float)to_acc<T>(xv[u].v[k]) - v[u].v[k];
+                o.v[k] = from_acc<T>((acc_t<T>)(p.op == 1 ? __expf(d) : d));
+              }
+              st_stream<T, VEC>(out + at, o);
+            } else {
+              if (count != nullptr) {
+                const T cnt = count[r[u]];
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) v[u].v[k] = div_t<T>(v[u].v[k], cnt);
+              }
+              st_stream<T, VEC>(out + at, v[u]);
             }
-            st_stream<T, VEC>(out + (ent0 + i + u * eps + sub) * p.K + c * VEC, v[u]);
           }
         }
       }
@@ -200,19 +242,19 @@ __global__ void __launch_bounds__(kThreads) gather_coo_kernel(GatherCooParams p)
   }
 }
 
-template <typename T>
+template <typename T, bool APPLY>
 int launch_gather_coo(GatherCooParams p, cudaStream_t stream) {
   constexpr int kFull = full_vec<T>();
   const int64_t entries = p.B * p.E;
   if (entries == 0 || p.K == 0 || p.N == 0) return TSB_OK;
-  const bool vec_ok = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.out);
+  const bool vec_ok = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.out) && (p.x == nullptr || aligned16(p.x));
   const int64_t Kv = p.K / (vec_ok ? kFull : 1);
   p.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
   const int64_t per_cta = (int64_t)(kThreads / 32) * 32 * kGatherBatches;
   const int64_t blocks = (entries + per_cta - 1) / per_cta;
   if (blocks > 2147483647LL) return TSB_ERR_TOO_LARGE;
-  if (vec_ok) gather_coo_kernel<T, kFull><<<(unsigned)blocks, kThreads, 0, stream>>>(p);
-  else gather_coo_kernel<T, 1><<<(unsigned)blocks, kThreads, 0, stream>>>(p);
+  if (vec_ok) gather_coo_kernel<T, kFull, APPLY><<<(unsigned)blocks, kThreads, 0, stream>>>(p);
+  else gather_coo_kernel<T, 1, APPLY><<<(unsigned)blocks, kThreads, 0, stream>>>(p);
   return launch_status();
 }
 
@@ -261,10 +303,30 @@ extern "C" int tsb_gather_coo(const void *src, const int64_t *index, void *out, 
   if (count != nullptr && (dtype == TSB_I32 || dtype == TSB_I64)) return TSB_ERR_DTYPE;
   GatherCooParams p;
   p.src = src; p.index = index; p.out = out; p.count = count;
+  p.x = nullptr; p.op = 0;
   p.B = B; p.E = E; p.K = K; p.N = N; p.bstride = index_batch_stride; p.l_log2 = 0;
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
-    return launch_gather_coo<scalar_t>(p, reinterpret_cast<cudaStream_t>(stream));
+    return launch_gather_coo<scalar_t, false>(p, reinterpret_cast<cudaStream_t>(stream));
   });
+}
+
+extern "C" int tsb_gather_coo_apply(const void *x, const void *table, const int64_t *index, void *out, int64_t B,
+                                    int64_t E, int64_t K, int64_t N, int64_t index_batch_stride, int dtype, int op,
+                                    tsb_stream_t stream) {
+  using namespace tsb;
+  if (B < 0 || E < 0 || K < 0 || N < 0) return TSB_ERR_ARG;
+  if (B * E * K == 0 || N == 0) return TSB_OK;
+  if (x == nullptr || table == nullptr || index == nullptr || out == nullptr) return TSB_ERR_ARG;
+  if (op != 1 && op != 2) return TSB_ERR_REDUCE;
+  if (dtype != TSB_F32 && dtype != TSB_F16 && dtype != TSB_BF16) return TSB_ERR_DTYPE;  // computed in fp32
+  GatherCooParams p;
+  p.src = table; p.index = index; p.out = out; p.count = nullptr;
+  p.x = x; p.op = op;
+  p.B = B; p.E = E; p.K = K; p.N = N; p.bstride = index_batch_stride; p.l_log2 = 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == TSB_F32) return launch_gather_coo<float, true>(p, s);
+  if (dtype == TSB_F16) return launch_gather_coo<__half, true>(p, s);
+  return launch_gather_coo<__nv_bfloat16, true>(p, s);
 }
 
 extern "C" int tsb_arg_backward(const void *grad_out, const int64_t *arg, void *grad_in, int64_t B,

@@ -37,6 +37,13 @@ coo_rowptr_kernel(const int64_t *__restrict__ index, int64_t *__restrict__ rowpt
   }
 }
 
+// *unsorted = 1 if some entry is smaller than its predecessor (the flag must be zero beforehand)
+__global__ void __launch_bounds__(kThreads)
+index_unsorted_kernel(const int64_t *__restrict__ index, int64_t n, int *unsorted) {
+  const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i + 1 < n && index[i] > index[i + 1]) *unsorted = 1;
+}
+
 }  // namespace
 }  // namespace tsb
 
@@ -58,6 +65,7 @@ extern "C" int tsb_segment_coo(const void *src, const int64_t *index, void *out,
   using namespace tsb;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (B < 0 || E < 0 || K < 0 || N < 0) return TSB_ERR_ARG;
+  if (reduce == TSB_LSE && out_seeded) return TSB_ERR_ARG;
   if (B * N == 0) return TSB_OK;
   if (workspace == nullptr || workspace_bytes < tsb_segment_coo_workspace_bytes(B, E, K, N, dtype, reduce)) return TSB_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(workspace) & 255u) return TSB_ERR_WORKSPACE;
@@ -83,4 +91,16 @@ extern "C" int tsb_segment_coo(const void *src, const int64_t *index, void *out,
   p.workspace = static_cast<unsigned char *>(workspace) + rowptr_bytes(B, N);
   p.workspace_bytes = workspace_bytes - rowptr_bytes(B, N);
   return launch_csr_reduce(p, dtype, reduce, stream);
+}
+
+extern "C" int tsb_index_unsorted(const int64_t *index, int64_t n, int *unsorted_flag, tsb_stream_t stream_) {
+  using namespace tsb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (n < 0 || unsorted_flag == nullptr || (n > 0 && index == nullptr)) return TSB_ERR_ARG;
+  if (cudaMemsetAsync(unsorted_flag, 0, sizeof(int), stream) != cudaSuccess) return TSB_ERR_LAUNCH;
+  if (n < 2) return TSB_OK;
+  const int64_t blocks = (n + kThreads - 1) / kThreads;
+  if (blocks > 2147483647LL) return TSB_ERR_TOO_LARGE;
+  index_unsorted_kernel<<<(unsigned)blocks, kThreads, 0, stream>>>(index, n, unsorted_flag);
+  return launch_status();
 }

@@ -66,17 +66,28 @@ inline int chunk_entries_for(int64_t K, size_t elem, int64_t E) {
   return (int)pow2;
 }
 
+// Per-lane accumulators of one row: VEC values and, for the reductions that need it, a second word per
+// value - the arg index for MIN/MAX, the bits of the running sum for LSE.
+// LSE is the online log-sum-exp: `val` holds the running maximum m, the second word the running sum
+// s = sum exp(x - m); two partials combine as m = max(m1, m2), s = s1 exp(m1 - m) + s2 exp(m2 - m), and
+// the row result is m + log s.  It exists for fp32 accumulators only (fp32 / fp16 / bf16 sources).
 template <typename T, int REDUCE, int VEC, typename ArgT = int64_t> struct RowAcc {
   using A = acc_t<T>;
   static constexpr bool kArg = (REDUCE == kMin || REDUCE == kMax);
+  static constexpr bool kLseAcc = (REDUCE == kLse);
+  static constexpr bool kPair = kArg || kLseAcc;
   A val[VEC];
-  ArgT arg[kArg ? VEC : 1];
+  ArgT arg[kPair ? VEC : 1];
+
+  static __device__ __forceinline__ float sum_of(ArgT word) { return __int_as_float((int)word); }
+  static __device__ __forceinline__ ArgT word_of(float s) { return (ArgT)__float_as_int(s); }
 
   __device__ __forceinline__ void init(ArgT sentinel) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       val[i] = reduce_identity<T, REDUCE>();
       if (kArg) arg[i] = sentinel;
+      if (kLseAcc) arg[i] = word_of(0.0f);
     }
   }
   // Entries arrive in increasing e within a lane, so strict comparisons keep the first winner
@@ -89,32 +100,49 @@ template <typename T, int REDUCE, int VEC, typename ArgT = int64_t> struct RowAc
         val[i] += x;
       } else if (REDUCE == kMin) {
         if (x < val[i]) { val[i] = x; arg[i] = e; }
-      } else {
+      } else if (REDUCE == kMax) {
         if (x > val[i]) { val[i] = x; arg[i] = e; }
+      } else {
+        // One exponential, no branch: whichever of the running maximum and x is larger becomes the
+        // reference, the other side is scaled by exp(-|x - m|).  The identity is the lowest finite float,
+        // so the first entry gives exp(-huge) = 0 for the empty sum, and an entry of -inf adds 0.
+        const float m = (float)val[i], xf = (float)x;
+        const float d = xf - m;
+        const float e = __expf(-fabsf(d));
+        const float sum = sum_of(arg[i]);
+        arg[i] = word_of(d > 0.0f ? fmaf(sum, e, 1.0f) : sum + e);
+        val[i] = (A)fmaxf(m, xf);
       }
     }
   }
-  // Merge another lane's partial; on equal values the smaller position wins so that the final
-  // arg is the first occurrence over the whole row.
+  // Merge another lane's partial; for MIN/MAX the smaller position wins on equal values so that the
+  // final arg is the first occurrence over the whole row.
   __device__ __forceinline__ void merge(const A *oval, const ArgT *oarg) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       if (REDUCE == kSum || REDUCE == kMean) {
         val[i] += oval[i];
-      } else {
+      } else if (kArg) {
         const bool better = (REDUCE == kMin) ? (oval[i] < val[i]) : (oval[i] > val[i]);
         if (better || (oval[i] == val[i] && oarg[i] < arg[i])) { val[i] = oval[i]; arg[i] = oarg[i]; }
+      } else {
+        const float m1 = (float)val[i], m2 = (float)oval[i];
+        const float d = m2 - m1;
+        const float e = __expf(-fabsf(d));
+        const float s1 = sum_of(arg[i]), s2 = sum_of(oarg[i]);
+        arg[i] = word_of(d > 0.0f ? fmaf(s1, e, s2) : fmaf(s2, e, s1));
+        val[i] = (A)fmaxf(m1, m2);
       }
     }
   }
   __device__ __forceinline__ void butterfly(int from, int to) {
     for (int off = from; off < to; off <<= 1) {
       A oval[VEC];
-      ArgT oarg[kArg ? VEC : 1];
+      ArgT oarg[kPair ? VEC : 1];
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
         oval[i] = shfl_xor<A>(val[i], off);
-        if (kArg) oarg[i] = shfl_xor<ArgT>(arg[i], off);
+        if (kPair) oarg[i] = shfl_xor<ArgT>(arg[i], off);
       }
       merge(oval, oarg);
     }
@@ -141,6 +169,12 @@ template <> struct MeanScale<int64_t> {
   __device__ __forceinline__ int64_t apply(int64_t v) const { return v / c; }
 };
 
+// Address of element `off` of the output: T everywhere except the LSE table, which is fp32.
+template <typename T, int REDUCE> __device__ __forceinline__ T *row_address(void *out, int64_t off) {
+  if constexpr (REDUCE == kLse) return reinterpret_cast<T *>(static_cast<float *>(out) + off);
+  else return static_cast<T *>(out) + off;
+}
+
 // Writes one finished row (this lane's VEC columns of it).  `acc` is the reduction over the row's
 // source entries only; in kCooSeeded mode the row's previous value of `out` joins here.  Arg indices
 // in `acc` are relative to `arg_base`; `arg_none` marks "no element won" and becomes `sentinel`.
@@ -159,6 +193,25 @@ __device__ __forceinline__ void write_row(const RowAcc<T, REDUCE, VEC, ArgT> &ac
   Pack<T, VEC> seed;
   if (mode == kCooSeeded) seed = ld_pack<T, VEC>(out_p);
   Pack<T, VEC> o;
+  if constexpr (REDUCE == kLse) {
+    // m + log s, fp32 whatever T is (a 16-bit table would cost the softmax its accuracy): `out_p` is the
+    // fp32 address.  A row without (finite) entries gives -inf.
+    float *o = reinterpret_cast<float *>(out_p);
+    float r[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const float sum = RowAcc<T, REDUCE, VEC, ArgT>::sum_of(acc.arg[i]);
+      r[i] = sum == 0.0f ? -INFINITY : (float)acc.val[i] + __logf(sum);
+    }
+    if constexpr (VEC % 4 == 0) {
+#pragma unroll
+      for (int i = 0; i < VEC; i += 4) *reinterpret_cast<float4 *>(o + i) = make_float4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o[i] = r[i];
+    }
+    return;
+  }
   const MeanScale<T> scale(REDUCE == kMean && len > 0 ? len : 1);
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
@@ -192,8 +245,6 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
   constexpr bool kArg = Acc::kArg;
 
   const T *__restrict__ src = static_cast<const T *>(p.src);
-  T *__restrict__ out = static_cast<T *>(p.out);
-
   const int L = 1 << g.l_log2;
   const int lane = threadIdx.x;
   const int col = lane & (L - 1);
@@ -242,7 +293,7 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
   for (int i = 0; i < VEC; ++i) fill.v[i] = from_acc<T>(reduce_identity<T, REDUCE>());
 
   A *carry = static_cast<A *>(g.carry_val) + chunk_id * 2 * p.K;
-  int64_t *carry_arg = kArg ? g.carry_arg + chunk_id * 2 * p.K : nullptr;
+  int64_t *carry_arg = Acc::kPair ? g.carry_arg + chunk_id * 2 * p.K : nullptr;  // arg indices / LSE sums
 
   for (int64_t cb = 0; cb < Kv; cb += L) {
     const int64_t c = cb + col;
@@ -289,6 +340,7 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
             for (int i = 0; i < VEC; ++i) {
               carry[c * VEC + i] = tot.val[i];
               if (kArg) carry_arg[c * VEC + i] = tot.arg[i] == kRelInf ? p.E : cs + tot.arg[i];
+              if (Acc::kLseAcc) carry_arg[c * VEC + i] = tot.arg[i];
             }
           }
           if (lane == 0 && cb == 0) g.head_row[chunk_id] = row;
@@ -296,7 +348,7 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
         } else {
           const int64_t grow = b * p.N + row;
           if (sub == 0 && col_ok) {
-            write_row<T, REDUCE, VEC, int>(tot, out + grow * p.K + c * VEC,
+            write_row<T, REDUCE, VEC, int>(tot, row_address<T, REDUCE>(p.out, grow * p.K + c * VEC),
                                            kArg ? p.arg_out + grow * p.K + c * VEC : nullptr,
                                            (int64_t)(cur_end - cur_start), p.mode, p.E, cs, kRelInf);
           }
@@ -360,6 +412,7 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
         for (int i = 0; i < VEC; ++i) {
           carry[p.K + c * VEC + i] = acc.val[i];
           if (kArg) carry_arg[p.K + c * VEC + i] = acc.arg[i] == kRelInf ? p.E : cs + acc.arg[i];
+          if (Acc::kLseAcc) carry_arg[p.K + c * VEC + i] = acc.arg[i];
         }
       }
     }
@@ -374,7 +427,6 @@ __global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeo
   using A = acc_t<T>;
   using Acc = RowAcc<T, REDUCE, VEC>;
   constexpr bool kArg = Acc::kArg;
-  T *__restrict__ out = static_cast<T *>(p.out);
   const int L = 1 << g.l_log2;
   const int lane = threadIdx.x & 31;
   const int col = lane & (L - 1);
@@ -403,11 +455,11 @@ __global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeo
       for (int64_t cc = c1 + sub; cc < w; cc += eps) {  // TAIL partials of the chunks run through
         const int64_t at = ((b * g.chunks + cc) * 2 + 1) * p.K + c * VEC;
         A oval[VEC];
-        int64_t oarg[kArg ? VEC : 1];
+        int64_t oarg[Acc::kPair ? VEC : 1];
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
           oval[i] = carry[at + i];
-          if (kArg) oarg[i] = g.carry_arg[at + i];
+          if (Acc::kPair) oarg[i] = g.carry_arg[at + i];
         }
         acc.merge(oval, oarg);
       }
@@ -416,14 +468,14 @@ __global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeo
     if (sub == 0 && col_ok) {
       const int64_t at = (chunk_id * 2) * p.K + c * VEC;  // this chunk's HEAD partial
       A oval[VEC];
-      int64_t oarg[kArg ? VEC : 1];
+      int64_t oarg[Acc::kPair ? VEC : 1];
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
         oval[i] = carry[at + i];
-        if (kArg) oarg[i] = g.carry_arg[at + i];
+        if (Acc::kPair) oarg[i] = g.carry_arg[at + i];
       }
       acc.merge(oval, oarg);
-      write_row<T, REDUCE, VEC, int64_t>(acc, out + grow * p.K + c * VEC,
+      write_row<T, REDUCE, VEC, int64_t>(acc, row_address<T, REDUCE>(p.out, grow * p.K + c * VEC),
                                          kArg ? p.arg_out + grow * p.K + c * VEC : nullptr, re - rs, p.mode, p.E,
                                          0, p.E);
     }
@@ -445,7 +497,6 @@ size_t carry_bytes(int64_t total_chunks, int64_t K, size_t acc_size, bool with_a
 
 template <typename T, int REDUCE, int VEC>
 int launch_vec(const CsrParams &p, CsrGeom g, cudaStream_t stream) {
-  constexpr bool kArg = (REDUCE == kMin || REDUCE == kMax);
   const int64_t Kv = p.K / VEC;
   g.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
   const int64_t total_chunks = p.B * g.chunks;
@@ -462,7 +513,7 @@ template <typename T, int REDUCE>
 int launch_typed(const CsrParams &p, cudaStream_t stream) {
   using A = acc_t<T>;
   constexpr int kFull = full_vec<T>();
-  constexpr bool kArg = (REDUCE == kMin || REDUCE == kMax);
+  constexpr bool kArg = (REDUCE == kMin || REDUCE == kMax || REDUCE == kLse);  // a second word per value
   if (p.B * p.N == 0) return TSB_OK;
   CsrGeom g;
   g.l_log2 = 0;
@@ -495,7 +546,7 @@ size_t csr_reduce_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, in
   int64_t chunks = (E + c - 1) / c;
   if (chunks < 1) chunks = 1;
   size_t a = 0, r = 0;
-  return carry_bytes(B * chunks, K, acc, reduce == TSB_MIN || reduce == TSB_MAX, &a, &r);
+  return carry_bytes(B * chunks, K, acc, reduce == TSB_MIN || reduce == TSB_MAX || reduce == TSB_LSE, &a, &r);
 }
 
 int launch_csr_reduce(const CsrParams &p, int dtype, int reduce, cudaStream_t stream) {
@@ -510,6 +561,9 @@ int launch_csr_reduce(const CsrParams &p, int dtype, int reduce, cudaStream_t st
       case TSB_MEAN: return launch_typed<scalar_t, kMean>(p, stream);
       case TSB_MIN: return launch_typed<scalar_t, kMin>(p, stream);
       case TSB_MAX: return launch_typed<scalar_t, kMax>(p, stream);
+      case TSB_LSE:
+        if constexpr (std::is_same<acc_t<scalar_t>, float>::value) return launch_typed<scalar_t, kLse>(p, stream);
+        else return TSB_ERR_DTYPE;
       default: return TSB_ERR_REDUCE;
     }
   });

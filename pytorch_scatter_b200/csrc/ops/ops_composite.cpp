@@ -1,0 +1,160 @@
+// Fused forms of upstream's softmax composites (torch_scatter/composite/softmax.py:9-51,
+// logsumexp.py:8-56) for an index that is 1-D and ascending: one online log-sum-exp reduction per group
+// (TSB_LSE through the row-pointer reduction) and one gather pass with the exp / subtract fused in - two
+// passes over the source where the composed form makes six.  Not part of upstream's operator set; the
+// Python composites call these when `index_is_sorted` says the index qualifies, and compose the general
+// operators otherwise.
+#include "ops_common.h"
+
+namespace tsb_ops {
+namespace {
+
+using torch::autograd::AutogradContext;
+using torch::autograd::Variable;
+using torch::autograd::variable_list;
+
+// 1-D index -> a view with `dim` leading singleton dims expanded to src's leading sizes ([.., E])
+torch::Tensor index_view(const torch::Tensor &index, const torch::Tensor &like, int64_t dim) {
+  std::vector<int64_t> shape(dim + 1, 1), full(dim + 1);
+  shape[dim] = index.size(0);
+  for (int64_t i = 0; i < dim; i++) full[i] = like.size(i);
+  full[dim] = index.size(0);
+  return index.view(shape).expand(full);
+}
+
+struct Flat { int64_t B, E, K; };
+Flat flat_dims(const torch::Tensor &x, int64_t dim) {
+  Flat f{1, x.size(dim), 1};
+  for (int64_t i = 0; i < dim; i++) f.B *= x.size(i);
+  for (int64_t i = dim + 1; i < x.dim(); i++) f.K *= x.size(i);
+  return f;
+}
+
+// fp32 table [.., N, ..] of log-sum-exp per group along dim (-inf for groups nobody names)
+torch::Tensor segment_lse(const torch::Tensor &src_, const torch::Tensor &index, int64_t dim, int64_t N) {
+  c10::cuda::CUDAGuard guard(src_.device());
+  auto src = src_.contiguous();
+  auto sizes = src.sizes().vec();
+  sizes[dim] = N;
+  auto table = torch::empty(sizes, src.options().dtype(torch::kFloat32));
+  if (table.numel() == 0) return table;
+  if (src.numel() == 0) return table.fill_(-std::numeric_limits<float>::infinity());
+  const Flat f = flat_dims(src, dim);
+  auto idx = index.contiguous();
+  const size_t ws_bytes = tsb_segment_coo_workspace_bytes(f.B, f.E, f.K, N, dtype_enum(src), TSB_LSE);
+  auto workspace = torch::empty({(int64_t)ws_bytes}, src.options().dtype(torch::kUInt8));
+  check_status(tsb_segment_coo(src.data_ptr(), idx.data_ptr<int64_t>(), table.data_ptr(), nullptr, nullptr, f.B, f.E, f.K,
+                               N, 0, dtype_enum(src), TSB_LSE, 0, workspace.data_ptr(), ws_bytes, current_stream()),
+               "tsb_segment_coo");
+  return table;
+}
+
+// out = op(x, table[.., index, ..]) along dim, table fp32; op 1: exp(x - row), 2: x - row
+torch::Tensor gather_apply(const torch::Tensor &x_, const torch::Tensor &table_, const torch::Tensor &index, int64_t dim,
+                           int op) {
+  c10::cuda::CUDAGuard guard(x_.device());
+  auto x = x_.contiguous();
+  auto table = table_.contiguous();
+  auto out = torch::empty_like(x);
+  if (x.numel() == 0) return out;
+  const Flat f = flat_dims(x, dim);
+  auto idx = index.contiguous();
+  check_status(tsb_gather_coo_apply(x.data_ptr(), table.data_ptr<float>(), idx.data_ptr<int64_t>(), out.data_ptr(), f.B,
+                                    f.E, f.K, table.size(dim), 0, dtype_enum(x), op, current_stream()),
+               "tsb_gather_coo_apply");
+  return out;
+}
+
+bool index_is_sorted(torch::Tensor index) {
+  TSB_CHECK_CUDA(index);
+  check_index_dtype(index, "index");
+  TSB_CHECK_INPUT(index.dim() == 1);
+  c10::cuda::CUDAGuard guard(index.device());
+  auto idx = index.contiguous();
+  auto flag = torch::empty({1}, index.options().dtype(torch::kInt32));
+  check_status(tsb_index_unsorted(idx.data_ptr<int64_t>(), idx.numel(), flag.data_ptr<int32_t>(), current_stream()),
+               "tsb_index_unsorted");
+  return flag.item<int32_t>() == 0;  // one host sync, like upstream's dim_size inference
+}
+
+int64_t groups_of(const torch::Tensor &index, std::optional<int64_t> dim_size) {
+  if (dim_size.has_value()) return dim_size.value();
+  return index.numel() == 0 ? 0 : index[-1].item<int64_t>() + 1;  // ascending: the last entry is the largest
+}
+
+// y = softmax / log_softmax per group.  backward: softmax gx = y * (g - sum_group(g * y));
+// log_softmax gx = g - exp(y) * sum_group(g).
+class SoftmaxSorted : public torch::autograd::Function<SoftmaxSorted> {
+public:
+  static variable_list forward(AutogradContext *ctx, Variable src, Variable index, int64_t dim,
+                               std::optional<int64_t> dim_size, bool log) {
+    dim = dim < 0 ? src.dim() + dim : dim;
+    const int64_t N = groups_of(index, dim_size);
+    auto lse = segment_lse(src, index, dim, N);
+    auto out = gather_apply(src, lse, index, dim, log ? 2 : 1);
+    ctx->saved_data["dim"] = dim;
+    ctx->saved_data["N"] = N;
+    ctx->saved_data["log"] = log;
+    ctx->save_for_backward({index, out});
+    return {out};
+  }
+  static variable_list backward(AutogradContext *ctx, variable_list grad_outs) {
+    auto saved = ctx->get_saved_variables();
+    auto index = saved[0], y = saved[1];
+    const int64_t dim = ctx->saved_data["dim"].toInt(), N = ctx->saved_data["N"].toInt();
+    const bool log = ctx->saved_data["log"].toBool();
+    auto g = grad_outs[0].contiguous();
+    auto iv = index_view(index, g, dim);
+    torch::Tensor grad_in;
+    if (log) {
+      auto total = std::get<0>(segment_coo_fw(g, iv, std::nullopt, N, "sum"));
+      grad_in = g - y.exp() * gather_coo_fw(total, iv, std::nullopt, std::nullopt);
+    } else {
+      auto gy = g * y;
+      auto total = std::get<0>(segment_coo_fw(gy, iv, std::nullopt, N, "sum"));
+      grad_in = gy - y * gather_coo_fw(total, iv, std::nullopt, std::nullopt);
+    }
+    return {grad_in, Variable(), Variable(), Variable(), Variable()};
+  }
+};
+
+// lse per group, 0 for groups nobody names (upstream: nan_to_num_(neginf=0), logsumexp.py:52).
+// backward: gx = g[group] * exp(x - lse[group]).
+class LogSumExpSorted : public torch::autograd::Function<LogSumExpSorted> {
+public:
+  static variable_list forward(AutogradContext *ctx, Variable src, Variable index, int64_t dim,
+                               std::optional<int64_t> dim_size) {
+    dim = dim < 0 ? src.dim() + dim : dim;
+    const int64_t N = groups_of(index, dim_size);
+    auto lse = segment_lse(src, index, dim, N);
+    ctx->saved_data["dim"] = dim;
+    ctx->save_for_backward({src, index, lse});
+    return {lse.nan_to_num(/*nan=*/std::nullopt, /*posinf=*/std::nullopt, /*neginf=*/0.0).to(src.scalar_type())};
+  }
+  static variable_list backward(AutogradContext *ctx, variable_list grad_outs) {
+    auto saved = ctx->get_saved_variables();
+    auto src = saved[0], index = saved[1], lse = saved[2];
+    const int64_t dim = ctx->saved_data["dim"].toInt();
+    auto iv = index_view(index, src, dim);
+    auto weights = gather_apply(src, lse, index, dim, 1);  // softmax weights
+    auto grad_in = weights * gather_coo_fw(grad_outs[0].contiguous(), iv, std::nullopt, std::nullopt);
+    return {grad_in, Variable(), Variable(), Variable()};
+  }
+};
+
+torch::Tensor softmax_sorted(torch::Tensor src, torch::Tensor index, int64_t dim, std::optional<int64_t> dim_size,
+                             bool log) {
+  return SoftmaxSorted::apply(src, index, dim, dim_size, log)[0];
+}
+torch::Tensor logsumexp_sorted(torch::Tensor src, torch::Tensor index, int64_t dim, std::optional<int64_t> dim_size) {
+  return LogSumExpSorted::apply(src, index, dim, dim_size)[0];
+}
+
+}  // namespace
+}  // namespace tsb_ops
+
+TORCH_LIBRARY_FRAGMENT(torch_scatter, m) {
+  m.def("index_is_sorted", &tsb_ops::index_is_sorted);
+  m.def("softmax_sorted", &tsb_ops::softmax_sorted);
+  m.def("logsumexp_sorted", &tsb_ops::logsumexp_sorted);
+}

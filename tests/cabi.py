@@ -7,7 +7,7 @@ import torch
 ROOT = osp.dirname(osp.dirname(osp.abspath(__file__)))
 LIB_PATH = osp.join(ROOT, 'pytorch_scatter_b200', 'libtsb200.so')
 DTYPE = {torch.float32: 0, torch.float64: 1, torch.float16: 2, torch.bfloat16: 3, torch.int32: 4, torch.int64: 5}
-REDUCE = {'sum': 0, 'mean': 1, 'min': 2, 'max': 3, 'mul': 4}
+REDUCE = {'sum': 0, 'mean': 1, 'min': 2, 'max': 3, 'mul': 4, 'lse': 5}
 _lib = None
 
 
@@ -48,7 +48,7 @@ def segment_csr(src, indptr, reduce, bstride=None):
     N = indptr.size(-1) - 1
     if bstride is None:
         bstride = 0 if indptr.size(0) == 1 else N + 1
-    out = torch.empty(B, N, K, dtype=src.dtype, device=src.device)
+    out = torch.empty(B, N, K, dtype=torch.float32 if reduce == 'lse' else src.dtype, device=src.device)
     arg = torch.empty(B, N, K, dtype=torch.int64, device=src.device) if reduce in ('min', 'max') else None
     d, r = DTYPE[src.dtype], REDUCE[reduce]
     nbytes = lib().tsb_segment_csr_workspace_bytes(_i(B), _i(E), _i(K), _i(N), d, r)
@@ -74,7 +74,7 @@ def segment_coo(src, index, N, reduce, out=None):
     bstride = 0 if index.size(0) == 1 else E
     seeded = out is not None
     if out is None:
-        out = torch.empty(B, N, K, dtype=src.dtype, device=src.device)
+        out = torch.empty(B, N, K, dtype=torch.float32 if reduce == 'lse' else src.dtype, device=src.device)
     arg = torch.empty(B, N, K, dtype=torch.int64, device=src.device) if reduce in ('min', 'max') else None
     count = torch.empty(B, N, dtype=src.dtype, device=src.device) if reduce == 'mean' else None
     d, r = DTYPE[src.dtype], REDUCE[reduce]
@@ -93,6 +93,23 @@ def gather_coo(src, index, count=None):
     _check(lib().tsb_gather_coo(_p(src), _p(index), _p(out), _p(count), _i(B), _i(E), _i(K), _i(N), _i(bstride),
                                 DTYPE[src.dtype], _stream()), 'tsb_gather_coo')
     return out
+
+
+def gather_coo_apply(x, table, index, op):
+    """x [B,E,K], table fp32 [B,N,K], index [Bi,E]; op 1: exp(x - table[index]), 2: x - table[index]."""
+    assert table.dtype == torch.float32
+    B, E, K = x.shape
+    bstride = 0 if index.size(0) == 1 else E
+    out = torch.empty_like(x)
+    _check(lib().tsb_gather_coo_apply(_p(x), _p(table), _p(index), _p(out), _i(B), _i(E), _i(K), _i(table.size(1)),
+                                      _i(bstride), DTYPE[x.dtype], int(op), _stream()), 'tsb_gather_coo_apply')
+    return out
+
+
+def index_unsorted(index):
+    flag = torch.full((1,), -1, dtype=torch.int32, device=index.device)
+    _check(lib().tsb_index_unsorted(_p(index), _i(index.numel()), _p(flag), _stream()), 'tsb_index_unsorted')
+    return bool(flag.item())
 
 
 def scatter(src, index, N, reduce, strides, out=None):

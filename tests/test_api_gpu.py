@@ -206,6 +206,64 @@ def test_logsumexp_against_torch(ts):
     assert acc.allclose(torch.tensor([-0.9999, -10.0], device=DEV), atol=1e-4)
 
 
+@pytest.mark.parametrize('dtype', [torch.float32, torch.float16, torch.bfloat16, torch.float64])
+def test_fused_sorted_softmax_family(ts, dtype):
+    """An ascending 1-D index takes the two-pass fused kernels (fp32 / 16-bit).  Judge: the composed operators in
+    float64 on the same groups in permuted order (an unsorted index never takes the fused path)."""
+    torch.manual_seed(3)
+    E, N = 4000, 150
+    index = torch.randint(0, N - 10, (E,), device=DEV).sort()[0]       # the last groups stay empty
+    perm = torch.randperm(E, device=DEV)
+    tol = 1e-5 if dtype in (torch.float32, torch.float64) else 1e-2
+    for shape, dim in (((E,), 0), ((E, 5), 0), ((3, E, 8), 1), ((2, E), -1)):
+        src = (3 * torch.randn(shape, device=DEV)).to(dtype)
+        for fn in (ts.scatter_softmax, ts.scatter_log_softmax, ts.scatter_logsumexp):
+            a = src.clone().requires_grad_()
+            b = src.double().index_select(dim, perm).requires_grad_()
+            out_a = fn(a, index, dim=dim, dim_size=N)
+            out_b = fn(b, index[perm], dim=dim, dim_size=N)
+            g = torch.randn_like(out_a)
+            out_a.backward(g)
+            if fn is ts.scatter_logsumexp:
+                out_b.backward(g.double())
+                want = out_b
+            else:
+                out_b.backward(g.double().index_select(dim, perm))
+                want = torch.empty_like(out_b).index_copy_(dim, perm, out_b)
+            want_grad = torch.empty_like(b.grad).index_copy_(dim, perm, b.grad)
+            assert out_a.dtype == dtype and out_a.shape == want.shape
+            assert torch.allclose(out_a.double(), want, rtol=tol, atol=tol), (fn.__name__, shape)
+            assert torch.allclose(a.grad.double(), want_grad, rtol=5 * tol, atol=5 * tol), (fn.__name__, shape, 'grad')
+        # inferred dim_size (index[-1] + 1) and the scripted form
+        assert ts.scatter_softmax(src, index, dim=dim).shape == src.shape
+        assert ts.scatter_logsumexp(src, index, dim=dim).size(dim) == int(index[-1]) + 1
+        assert torch.equal(torch.jit.script(ts.scatter_softmax)(src, index, dim), ts.scatter_softmax(src, index, dim))
+
+
+def test_fused_sorted_softmax_gradcheck(ts):
+    """float64 does not take the fused path, so check its analytic backward numerically in fp32 against the composed one."""
+    torch.manual_seed(4)
+    index = torch.tensor([0, 0, 0, 1, 3, 3, 3, 3, 6], device=DEV)
+    src = torch.randn(9, 3, device=DEV)
+    g = torch.randn(9, 3, device=DEV)
+    for fn, ref in ((ts.scatter_softmax, torch.softmax), (ts.scatter_log_softmax, torch.log_softmax)):
+        a = src.clone().requires_grad_()
+        fn(a, index, dim=0).backward(g)
+        b = src.clone().requires_grad_()
+        pieces = [ref(p, dim=0) for p in b.split([3, 1, 4, 1])]
+        torch.cat(pieces).backward(g)
+        assert torch.allclose(a.grad, b.grad, atol=1e-5), fn.__name__
+    a = src.clone().requires_grad_()
+    out = ts.scatter_logsumexp(a, index, dim=0)
+    assert out.shape == (7, 3) and torch.all(out[[2, 4, 5]] == 0)
+    go = torch.randn_like(out)
+    out.backward(go)
+    b = src.clone().requires_grad_()
+    ref = torch.stack([torch.logsumexp(p, dim=0) for p in b.split([3, 1, 4, 1])])
+    ref.backward(go[[0, 1, 3, 6]])
+    assert torch.allclose(out[[0, 1, 3, 6]], ref, atol=1e-5) and torch.allclose(a.grad, b.grad, atol=1e-5)
+
+
 def test_std_against_torch(ts):
     src = torch.tensor([[2, 0, 1, 4, 3], [0, 2, 1, 3, 4]], dtype=torch.float, device=DEV, requires_grad=True)
     index = torch.tensor([[0, 0, 0, 0, 0], [1, 1, 1, 1, 1]], device=DEV)

@@ -121,6 +121,60 @@ def test_segment_csr_deterministic(chunk):
     assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize('kind', ['lognormal', 'giant', 'empty_ends'])
+@pytest.mark.parametrize('K', [1, 3, 4, 64])
+def test_log_sum_exp_rows(chunk, kind, K):
+    """TSB_LSE (the reduction behind the fused softmax composites) against float64 torch.logsumexp per row."""
+    gen = torch.Generator().manual_seed(2000 + K)
+    rows = 300
+    lens = row_lengths(gen, rows, kind)
+    indptr = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)]).view(1, -1)
+    index = torch.repeat_interleave(torch.arange(rows), lens).view(1, -1)
+    E = int(indptr[0, -1])
+    for dtype in (torch.float32, torch.float16, torch.bfloat16):   # the table is fp32 for all of them
+        tol = 1e-5
+        src = (4 * torch.randn(1, E, K, generator=gen)).to(dtype)
+        src[0, ::7, 0] = float('-inf')       # entries that contribute nothing
+        want = torch.full((1, rows, K), float('-inf'), dtype=torch.float64)
+        for r in range(rows):
+            lo, hi = int(indptr[0, r]), int(indptr[0, r + 1])
+            if hi > lo:
+                want[0, r] = torch.logsumexp(src[0, lo:hi].double(), dim=0)
+        got = cabi.segment_csr(src.cuda(), indptr.cuda(), 'lse')[0].cpu().double()
+        got2 = cabi.segment_coo(src.cuda(), index.cuda(), rows, 'lse')[0].cpu().double()
+        for g, what in ((got, 'csr'), (got2, 'coo')):
+            assert torch.equal(torch.isinf(g), torch.isinf(want)), f'lse {what} {dtype} K={K} {kind}: -inf rows'
+            fin = torch.isfinite(want)
+            assert torch.allclose(g[fin], want[fin], rtol=tol, atol=tol), f'lse {what} {dtype} K={K} {kind}'
+    for dtype in (torch.float64, torch.int32):   # no such reduction outside fp32 accumulators
+        d = torch.zeros(1, 4, 1).to(dtype).cuda()
+        with pytest.raises(AssertionError, match='dtype'):
+            cabi.segment_csr(d, torch.tensor([[0, 4]]).cuda(), 'lse')
+
+
+def test_gather_coo_apply_and_sortedness():
+    gen = torch.Generator().manual_seed(77)
+    for K in (1, 3, 4, 16, 64):
+        for dtype, tol in ((torch.float32, 1e-6), (torch.float16, 1e-2), (torch.bfloat16, 1e-2)):
+            N, E = 200, 5000
+            index = torch.randint(0, N, (1, E), generator=gen).sort(dim=1)[0]
+            x = torch.randn(2, E, K, generator=gen).to(dtype)
+            table = torch.randn(2, N, K, generator=gen)
+            rows = table[:, index[0]]
+            for op, want in ((1, (x.float() - rows).exp()), (2, x.float() - rows)):
+                got = cabi.gather_coo_apply(x.cuda(), table.cuda(), index.cuda(), op).cpu().float()
+                assert torch.allclose(got, want, rtol=tol, atol=tol), f'apply op={op} {dtype} K={K}'
+    asc = torch.arange(100000).cuda() // 3
+    assert not cabi.index_unsorted(asc)
+    assert not cabi.index_unsorted(asc[:1]) and not cabi.index_unsorted(asc[:0])
+    bad = asc.clone()
+    bad[99999] = 5
+    assert cabi.index_unsorted(bad)
+    bad = asc.clone()
+    bad[0] = 1
+    assert cabi.index_unsorted(bad)
+
+
 def test_segment_csr_bad_pointers_do_not_fault():
     """Row pointers outside [0, E] or not ascending are clamped: garbage in, garbage out, no fault."""
     src = torch.randn(1, 100, 4).cuda()
