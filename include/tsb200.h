@@ -159,10 +159,13 @@ int tsb_index_unsorted(const int64_t *index, int64_t n, int *unsorted_flag, tsb_
  *   count_out            MEAN only: int32 [Bc,N,Kc] with Bc = idx_stride_b ? B : 1 and
  *                        Kc = idx_stride_k ? K : 1; receives the per-target element count
  *   workspace            tsb_scatter_workspace_bytes(...) bytes, 256-byte aligned, always at least 256: a
- *                        flag for the variant choice, fp32 accumulators for 16-bit dtypes, and copies
- *                        of small outputs that contended updates are spread over
- * Float SUM/MEAN/MUL use atomics: the summation order is not fixed.  MIN/MAX and arg are exact. */
-size_t tsb_scatter_workspace_bytes(int64_t B, int64_t N, int64_t K, int dtype, int reduce);
+ *                        flag for the variant choice, fp32 accumulators for 16-bit dtypes, copies of
+ *                        small outputs that contended updates are spread over, and - for outputs too
+ *                        large to stay in L2 - the scratch of the atomics-free path (entries grouped by
+ *                        target row with a counting sort of the index, rows reduced through that
+ *                        permutation: 8 bytes per entry + 12 per row)
+ * Float SUM/MEAN/MUL: the summation order is not fixed.  MIN/MAX and arg are exact. */
+size_t tsb_scatter_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce);
 int tsb_scatter(const void *src, const int64_t *index, void *out, int64_t *arg_out, int32_t *count_out,
                 int64_t B, int64_t E, int64_t K, int64_t N,
                 int64_t idx_stride_b, int64_t idx_stride_e, int64_t idx_stride_k,

@@ -9,7 +9,8 @@ namespace tsb {
 //   kCsr        out overwritten; empty row -> 0, arg E          (csrc/cpu/segment_csr_cpu.cpp:69-87)
 //   kCooFresh   out write-only; absent row -> 0; MIN/MAX equal to the identity -> 0
 //                                                              (csrc/cpu/segment_coo_cpu.cpp:84-85,131-132)
-//   kCooSeeded  accumulate into out; absent rows untouched     (csrc/cpu/segment_coo_cpu.cpp:91-92,120)
+//   kCooSeeded  accumulate into out; absent rows untouched     (csrc/cpu/segment_coo_cpu.cpp:91-92,120);
+//               MIN/MAX: the value already in out wins ties and then the arg is E
 enum CsrMode { kCsr = 0, kCooFresh = 1, kCooSeeded = 2 };
 
 struct CsrParams {
@@ -19,6 +20,11 @@ struct CsrParams {
   int64_t *arg_out;       // [B,N,K] or null
   void *count_out;        // [B,N] of dtype or null (COO mean)
   int64_t B, E, K, N, bstride;
+  // Optional indirection: position q of the reduced dimension reads source entry perm[q] (the same
+  // permutation for every batch).  Lets an unsorted scatter run as "group the entry ids by target row,
+  // then reduce rows" without moving the source.  MIN/MAX then report perm[q] as the arg and break
+  // ties towards the smaller entry id.  Requires E < 2^30.
+  const int32_t *perm = nullptr;
   int mode;
   void *workspace;        // csr_reduce_workspace_bytes(...) bytes, 256-byte aligned
   size_t workspace_bytes;

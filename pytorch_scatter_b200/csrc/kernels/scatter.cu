@@ -24,6 +24,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "scatter_grouped.cuh"
 
 namespace tsb {
 namespace {
@@ -960,14 +961,39 @@ int run_scatter_backward(ScatterBwParams p, cudaStream_t stream) {
 }  // namespace
 }  // namespace tsb
 
-extern "C" size_t tsb_scatter_workspace_bytes(int64_t B, int64_t N, int64_t K, int dtype, int reduce) {
-  (void)reduce;
-  if (B < 0 || N < 0 || K < 0) return 0;
+namespace {
+// The atomics-free path pays about 12 bytes of scratch traffic per entry to group the entries by row;
+// it wins once the accumulation target no longer stays in L2 (the reductions then re-fetch output
+// lines or re-read the index per slice), for MIN/MAX earlier because value+arg targets are twice as big.
+bool prefer_grouped(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce) {
+  (void)E;
+  const int64_t acc = (dtype == TSB_F64 || dtype == TSB_I64) ? 8 : 4;
+  const int64_t elem = (dtype == TSB_F64 || dtype == TSB_I64) ? 8 : (dtype == TSB_F16 || dtype == TSB_BF16) ? 2 : 4;
+  const int64_t target_bytes = B * N * K * acc;
+  if (K * elem < 32) return false;
+  const bool minmax = reduce == TSB_MIN || reduce == TSB_MAX;
+  return target_bytes > (minmax ? (48ll << 20) : (192ll << 20));
+}
+int grouped_override() {  // test / tuning hook: "0" never, "1" whenever the shapes allow it
+  const char *v = std::getenv("TSB_SCATTER_GROUPED");
+  return (v != nullptr && (*v == '0' || *v == '1')) ? (*v - '0') : -1;
+}
+}  // namespace
+
+extern "C" size_t tsb_scatter_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce) {
+  if (B < 0 || E < 0 || N < 0 || K < 0) return 0;
   const bool k16 = dtype == TSB_F16 || dtype == TSB_BF16;
   const size_t acc = (dtype == TSB_F64 || dtype == TSB_I64) ? 8 : 4;
   const size_t target = (size_t)B * (size_t)N * (size_t)K * acc;
   const int replicas = tsb::replicas_for((int64_t)target);
-  return 256 + ((k16 || replicas > 1) ? target * (size_t)replicas : 0);  // 256: the index probe's flag
+  size_t scratch = (k16 || replicas > 1) ? target * (size_t)replicas : 0;
+  // the index strides are not known here: cover both paths
+  const int forced = grouped_override();
+  if (forced == 1 || (forced != 0 && prefer_grouped(B, E, K, N, dtype, reduce))) {
+    const size_t grouped = tsb::scatter_grouped_workspace_bytes(B, E, K, N, dtype, reduce);
+    if (grouped > scratch) scratch = grouped;
+  }
+  return 256 + scratch;  // 256: the index probe's flag
 }
 
 extern "C" int tsb_scatter(const void *src, const int64_t *index, void *out, int64_t *arg_out, int32_t *count_out,
@@ -982,9 +1008,16 @@ extern "C" int tsb_scatter(const void *src, const int64_t *index, void *out, int
   if (B * E * K > 0 && (src == nullptr || index == nullptr)) return TSB_ERR_ARG;
   if ((reduce == TSB_MIN || reduce == TSB_MAX) && arg_out == nullptr) return TSB_ERR_ARG;
   if (reduce == TSB_MEAN && count_out == nullptr) return TSB_ERR_ARG;
-  const size_t need = tsb_scatter_workspace_bytes(B, N, K, dtype, reduce);
+  const size_t need = tsb_scatter_workspace_bytes(B, E, K, N, dtype, reduce);
   if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
     return TSB_ERR_WORKSPACE;
+  {
+    const int forced = grouped_override();
+    if ((forced == 1 || (forced != 0 && prefer_grouped(B, E, K, N, dtype, reduce))) &&
+        scatter_grouped_possible(B, E, K, N, idx_stride_b, idx_stride_e, idx_stride_k, dtype, reduce))
+      return run_scatter_grouped(src, index, out, arg_out, count_out, B, E, K, N, dtype, reduce, out_seeded,
+                                 static_cast<unsigned char *>(workspace) + 256, workspace_bytes - 256, stream);
+  }
   ScatterParams p;
   p.src = src; p.index = index; p.out = out;
   p.target = out;  // run_scatter redirects it to the workspace where that is used

@@ -92,16 +92,17 @@ template <typename T, int REDUCE, int VEC, typename ArgT = int64_t> struct RowAc
   }
   // Entries arrive in increasing e within a lane, so strict comparisons keep the first winner
   // (csrc/cpu/reducer.h:63-67).
-  __device__ __forceinline__ void update(const Pack<T, VEC> &v, ArgT e) {
+  // TIES (entries arrive in no particular order): an equal value wins if its id is smaller.
+  template <bool TIES = false> __device__ __forceinline__ void update(const Pack<T, VEC> &v, ArgT e, ArgT none = 0) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
       const A x = to_acc<T>(v.v[i]);
       if (REDUCE == kSum || REDUCE == kMean) {
         val[i] += x;
       } else if (REDUCE == kMin) {
-        if (x < val[i]) { val[i] = x; arg[i] = e; }
+        if (x < val[i] || (TIES && x == val[i] && e < arg[i] && arg[i] != none)) { val[i] = x; arg[i] = e; }
       } else if (REDUCE == kMax) {
-        if (x > val[i]) { val[i] = x; arg[i] = e; }
+        if (x > val[i] || (TIES && x == val[i] && e < arg[i] && arg[i] != none)) { val[i] = x; arg[i] = e; }
       } else {
         // One exponential, no branch: whichever of the running maximum and x is larger becomes the
         // reference, the other side is scaled by exp(-|x - m|).  The identity is the lowest finite float,
@@ -227,7 +228,7 @@ __device__ __forceinline__ void write_row(const RowAcc<T, REDUCE, VEC, ArgT> &ac
         if (v == reduce_identity<T, REDUCE>()) v = (A)0;
       } else {
         const A s = to_acc<T>(seed.v[i]);
-        const bool seed_wins = (REDUCE == kMin) ? (s < v) : (s > v);
+        const bool seed_wins = (REDUCE == kMin) ? (s <= v) : (s >= v);
         if (seed_wins) { v = s; a = sentinel; }
       }
       o.v[i] = from_acc<T>(v);
@@ -238,7 +239,7 @@ __device__ __forceinline__ void write_row(const RowAcc<T, REDUCE, VEC, ArgT> &ac
 }
 
 // Streaming kernel: blockIdx.x = (batch, chunk); one warp.
-template <typename T, int REDUCE, int VEC>
+template <typename T, int REDUCE, int VEC, bool INDIRECT>
 __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams p, CsrGeom g) {
   using A = acc_t<T>;
   using Acc = RowAcc<T, REDUCE, VEC, int>;  // arg indices relative to the chunk start inside the stream
@@ -327,10 +328,11 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
     acc.init(kRelInf);
 
     // Closes every row that ends at or before `step_end`; `v` is this lane's entry `e` of the step.
-    auto close_rows = [&](const Pack<T, VEC> &v, int e, int step_end) {
+    // `id` is what MIN/MAX record for the entry: its position, or with a permutation its source entry.
+    auto close_rows = [&](const Pack<T, VEC> &v, int e, int id, int step_end) {
       while (cur_end <= step_end) {
         Acc tot = acc;
-        if (e >= cur_start && e < cur_end) tot.update(v, e);
+        if (e >= cur_start && e < cur_end) tot.template update<INDIRECT>(v, id, kRelInf);
         tot.butterfly(L, 32);
         const int64_t row = r_win + cur;
         if (head_pending) {
@@ -339,7 +341,7 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
 #pragma unroll
             for (int i = 0; i < VEC; ++i) {
               carry[c * VEC + i] = tot.val[i];
-              if (kArg) carry_arg[c * VEC + i] = tot.arg[i] == kRelInf ? p.E : cs + tot.arg[i];
+              if (kArg) carry_arg[c * VEC + i] = tot.arg[i] == kRelInf ? p.E : (INDIRECT ? 0 : cs) + tot.arg[i];
               if (Acc::kLseAcc) carry_arg[c * VEC + i] = tot.arg[i];
             }
           }
@@ -350,7 +352,7 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
           if (sub == 0 && col_ok) {
             write_row<T, REDUCE, VEC, int>(tot, row_address<T, REDUCE>(p.out, grow * p.K + c * VEC),
                                            kArg ? p.arg_out + grow * p.K + c * VEC : nullptr,
-                                           (int64_t)(cur_end - cur_start), p.mode, p.E, cs, kRelInf);
+                                           (int64_t)(cur_end - cur_start), p.mode, p.E, INDIRECT ? 0 : cs, kRelInf);
           }
           if (lane == 0 && cb == 0 && p.count_out != nullptr) {
             const int len = cur_end - cur_start;
@@ -379,30 +381,50 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
     // per-thread completion of cp.async.wait_group is all the synchronisation the ring needs.
     constexpr int S = kRingDepth;
     __shared__ Pack<T, VEC> s_ring[S][32];
-#pragma unroll
-    for (int j = 0; j < S; ++j) {
-      if (col_ok && next_rel < t) async_copy_pack<T, VEC>(&s_ring[j][lane], next_ptr);
+    __shared__ int s_id[(INDIRECT && kArg) ? S : 1][32];  // source entry of each slot, for the arg
+    // INDIRECT: the permutation is read 32 positions at a time (lane j holds position 32 w + j of the
+    // chunk), two windows ahead of the one the copies are issued from, and handed out by shuffle.
+    int pw0 = 0, pw1 = 0, pw2 = 0;
+    auto load_perm_window = [&](int first) -> int {
+      const int q = first + lane;
+      int v = (q < t) ? p.perm[cs + q] : 0;
+      const int last = (int)p.E - 1;
+      return v < 0 ? 0 : (v > last ? last : v);  // a stale slot past the last row must stay a valid address
+    };
+    if (INDIRECT) { pw0 = load_perm_window(0); pw1 = load_perm_window(32); pw2 = load_perm_window(64); }
+    auto issue = [&](int into) {
+      if (INDIRECT) {
+        const int step_first = next_rel - sub;  // warp-uniform, a multiple of eps
+        if (step_first > 0 && (step_first & 31) == 0) { pw0 = pw1; pw1 = pw2; pw2 = load_perm_window(step_first + 64); }
+        const int id = __shfl_sync(kFullMask, pw0, (step_first & 31) + sub);
+        if (col_ok && next_rel < t) {
+          async_copy_pack<T, VEC>(&s_ring[into][lane], bsrc + (int64_t)id * p.K + c * VEC);
+          if (kArg) s_id[into][lane] = id;
+        }
+      } else {
+        if (col_ok && next_rel < t) async_copy_pack<T, VEC>(&s_ring[into][lane], next_ptr);
+        next_ptr += step_stride;
+      }
       async_commit();
-      next_ptr += step_stride;
       next_rel += eps;
-    }
+    };
+#pragma unroll
+    for (int j = 0; j < S; ++j) issue(j);
     int slot = 0;
     for (int pos = 0; pos < t; pos += eps) {
       async_wait_all_but<S - 1>();  // the oldest copy in flight, this slot's, has landed
       const int e = pos + sub;
       const Pack<T, VEC> v = (col_ok && e < t) ? s_ring[slot][lane] : fill;
+      const int id = (INDIRECT && kArg) ? s_id[slot][lane] : e;
       const int step_end = (pos + eps < t) ? pos + eps : t;
-      if (cur_end <= step_end) close_rows(v, e, step_end);
-      if (e >= cur_start) acc.update(v, e);  // the row still open after this step
-      if (col_ok && next_rel < t) async_copy_pack<T, VEC>(&s_ring[slot][lane], next_ptr);
-      async_commit();
-      next_ptr += step_stride;
-      next_rel += eps;
+      if (cur_end <= step_end) close_rows(v, e, id, step_end);
+      if (e >= cur_start) acc.template update<INDIRECT>(v, id, kRelInf);  // the row still open after this step
+      issue(slot);
       slot = (slot + 1) & (S - 1);
     }
     async_wait_all_but<0>();
     // rows that end exactly at the chunk's end, including rows without entries there
-    close_rows(fill, t, t);
+    close_rows(fill, t, t, t);
 
     // the row still open runs on into the next chunk: store what this chunk holds of it
     if (r_win + cur < p.N && cur_start < t) {
@@ -411,7 +433,7 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
           carry[p.K + c * VEC + i] = acc.val[i];
-          if (kArg) carry_arg[p.K + c * VEC + i] = acc.arg[i] == kRelInf ? p.E : cs + acc.arg[i];
+          if (kArg) carry_arg[p.K + c * VEC + i] = acc.arg[i] == kRelInf ? p.E : (INDIRECT ? 0 : cs) + acc.arg[i];
           if (Acc::kLseAcc) carry_arg[p.K + c * VEC + i] = acc.arg[i];
         }
       }
@@ -501,7 +523,12 @@ int launch_vec(const CsrParams &p, CsrGeom g, cudaStream_t stream) {
   g.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
   const int64_t total_chunks = p.B * g.chunks;
   if (total_chunks > 2147483647LL) return TSB_ERR_TOO_LARGE;
-  csr_stream_kernel<T, REDUCE, VEC><<<(unsigned)total_chunks, 32, 0, stream>>>(p, g);
+  if (p.perm != nullptr) {
+    if constexpr (REDUCE == kLse) return TSB_ERR_REDUCE;
+    else csr_stream_kernel<T, REDUCE, VEC, true><<<(unsigned)total_chunks, 32, 0, stream>>>(p, g);
+  } else {
+    csr_stream_kernel<T, REDUCE, VEC, false><<<(unsigned)total_chunks, 32, 0, stream>>>(p, g);
+  }
   if (g.chunks > 1) {  // a single chunk per batch cannot split a row
     const int64_t blocks = (total_chunks + (kThreads / 32) - 1) / (kThreads / 32);
     csr_fixup_kernel<T, REDUCE, VEC><<<(unsigned)blocks, kThreads, 0, stream>>>(p, g);
@@ -555,6 +582,7 @@ int launch_csr_reduce(const CsrParams &p, int dtype, int reduce, cudaStream_t st
   if (p.src == nullptr && p.E > 0) return TSB_ERR_ARG;
   if (p.indptr == nullptr || p.out == nullptr) return TSB_ERR_ARG;
   if ((reduce == TSB_MIN || reduce == TSB_MAX) && p.arg_out == nullptr) return TSB_ERR_ARG;
+  if (p.perm != nullptr && p.E >= kRelInf) return TSB_ERR_TOO_LARGE;
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
     switch (reduce) {
       case TSB_SUM: return launch_typed<scalar_t, kSum>(p, stream);

@@ -123,7 +123,7 @@ ScatterResult scatter_fw(torch::Tensor src, torch::Tensor index, int64_t dim,
     r.count = torch::empty({fi.sb ? B : 1, N, fi.sk ? K : 1}, index.options().dtype(torch::kInt32));
   }
   if (r.out.numel() > 0) {
-    const size_t ws_bytes = tsb_scatter_workspace_bytes(B, N, K, dtype_enum(src), red);
+    const size_t ws_bytes = tsb_scatter_workspace_bytes(B, E, K, N, dtype_enum(src), red);
     auto workspace = torch::empty({(int64_t)ws_bytes}, src.options().dtype(torch::kUInt8));
     check_status(tsb_scatter(src.data_ptr(), fi.holder.data_ptr<int64_t>(), r.out.data_ptr(),
                              minmax ? r.arg_out.value().data_ptr<int64_t>() : nullptr,

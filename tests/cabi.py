@@ -124,7 +124,7 @@ def scatter(src, index, N, reduce, strides, out=None):
     if reduce == 'mean':
         count = torch.empty((B if sb else 1) * N * (K if sk else 1), dtype=torch.int32, device=src.device)
     d, r = DTYPE[src.dtype], REDUCE[reduce]
-    nbytes = lib().tsb_scatter_workspace_bytes(_i(B), _i(N), _i(K), d, r)
+    nbytes = lib().tsb_scatter_workspace_bytes(_i(B), _i(E), _i(K), _i(N), d, r)
     ws = _ws(nbytes, src.device)
     _check(lib().tsb_scatter(_p(src), _p(index), _p(out), _p(arg), _p(count), _i(B), _i(E), _i(K), _i(N), _i(sb), _i(se),
                              _i(sk), d, r, int(seeded), _p(ws), ctypes.c_size_t(nbytes), _stream()),

@@ -79,8 +79,8 @@ def test_workspace_queries(lib):
     assert n_arg >= n + 100 * 2 * 64 * 8
     assert lib.tsb_segment_coo_workspace_bytes(I(1), I(512 * 100), I(64), I(1000), 0, 0) >= n + 1001 * 8
     # a flag header, then (small output) 16 copies of the fp32 accumulators
-    assert lib.tsb_scatter_workspace_bytes(I(2), I(10), I(8), 0, 0) == 256 + 16 * 2 * 10 * 8 * 4
-    assert lib.tsb_scatter_workspace_bytes(I(2), I(10), I(8), 3, 0) == 256 + 16 * 2 * 10 * 8 * 4
+    assert lib.tsb_scatter_workspace_bytes(I(2), I(100), I(8), I(10), 0, 0) == 256 + 16 * 2 * 10 * 8 * 4
+    assert lib.tsb_scatter_workspace_bytes(I(2), I(100), I(8), I(10), 3, 0) == 256 + 16 * 2 * 10 * 8 * 4
     # a large output: no copies; 16-bit dtypes still get their fp32 accumulators
-    assert lib.tsb_scatter_workspace_bytes(I(1), I(1 << 20), I(64), 0, 0) == 256
-    assert lib.tsb_scatter_workspace_bytes(I(1), I(1 << 20), I(64), 3, 0) == 256 + (1 << 20) * 64 * 4
+    assert lib.tsb_scatter_workspace_bytes(I(1), I(1000), I(64), I(1 << 19), 0, 0) == 256
+    assert lib.tsb_scatter_workspace_bytes(I(1), I(1000), I(64), I(1 << 19), 3, 0) == 256 + (1 << 19) * 64 * 4

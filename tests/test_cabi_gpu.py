@@ -207,12 +207,15 @@ def test_gathers(K):
         assert_close(cabi.gather_coo(table.cuda(), index.cuda(), count.cuda()), want, what='gather_coo divide')
 
 
-@pytest.fixture(params=['one-pass', 'sliced', 'replicated', 'runs', 'runs-sliced', 'direct'])
+@pytest.fixture(params=['one-pass', 'sliced', 'replicated', 'runs', 'runs-sliced', 'direct', 'grouped', 'grouped-chunk32'])
 def scatter_slices(request):
     """Forces the variants the launcher normally picks by size or by probing the index: sliced multi-pass
     accumulation (outputs larger than L2), accumulation into several copies of the output (small,
-    contended outputs), and the run-combining versus the direct kernels."""
-    names = ('TSB_SCATTER_SLICE_BYTES', 'TSB_SCATTER_REPLICAS', 'TSB_SCATTER_CLUSTERED')
+    contended outputs), the run-combining versus the direct kernels, and the atomics-free path that groups the
+    entries by target row and reduces rows through the permutation (also with 32-entry chunks, so that rows
+    straddle many chunk borders)."""
+    names = ('TSB_SCATTER_SLICE_BYTES', 'TSB_SCATTER_REPLICAS', 'TSB_SCATTER_CLUSTERED', 'TSB_SCATTER_GROUPED',
+             'TSB_CSR_CHUNK_ENTRIES')
     old = {k: os.environ.get(k) for k in names}
     for k in names:
         os.environ.pop(k, None)
@@ -224,6 +227,9 @@ def scatter_slices(request):
         os.environ['TSB_SCATTER_CLUSTERED'] = '1'
     if request.param == 'direct':          # the one-update-per-entry kernels, even on a sorted index
         os.environ['TSB_SCATTER_CLUSTERED'] = '0'
+    os.environ['TSB_SCATTER_GROUPED'] = '1' if request.param.startswith('grouped') else '0'
+    if request.param == 'grouped-chunk32':
+        os.environ['TSB_CSR_CHUNK_ENTRIES'] = '32'
     yield request.param
     for k, v in old.items():
         if v is None:
@@ -283,13 +289,39 @@ def test_scatter_elements_and_ties():
                 assert torch.equal(got_arg.cpu(), want_arg), what + ' arg'
 
 
-def test_scatter_seeded_and_out_of_range():
+def test_scatter_rows_ties(scatter_slices):
+    """Quantised values, hot targets: many exact ties, the arg must be the smallest entry id; also seeded."""
+    gen = torch.Generator().manual_seed(77)
+    B, E, K, N = 2, 4000, 8, 50
+    index = torch.randint(0, N, (1, E, 1), generator=gen)
+    index[0, 100:1500, 0] = 7
+    for dtype in (torch.float32, torch.int32, torch.float16, torch.float64):
+        src = rand_src(gen, (B, E, K), dtype)
+        base = rand_src(gen, (B, N, K), dtype)
+        # seeds never equal an entry (upstream's CPU loop lets the seed win such a tie, its GPU arg pass the entry)
+        if dtype.is_floating_point:
+            src = (src.float() * 2).round().div(2).to(dtype)
+            base = ((base.float() * 2).round().div(2) + 0.25).to(dtype)
+        else:
+            src, base = src * 2, base * 2 + 1
+        for reduce in ('min', 'max'):
+            want, want_arg = oracle.scatter(src, index, N, reduce)
+            got, got_arg, _ = cabi.scatter(src.cuda(), index.cuda(), N, reduce, (0, 1, 0))
+            assert_close(got, want, what=f'ties {reduce} {dtype}')
+            assert torch.equal(got_arg.cpu(), want_arg), f'ties {reduce} {dtype} arg'
+            want, want_arg = oracle.scatter(src, index, N, reduce, base)
+            got, got_arg, _ = cabi.scatter(src.cuda(), index.cuda(), N, reduce, (0, 1, 0), out=base.clone().cuda())
+            assert_close(got, want, what=f'seeded ties {reduce} {dtype}')
+            assert torch.equal(got_arg.cpu(), want_arg), f'seeded ties {reduce} {dtype} arg'
+
+
+def test_scatter_seeded_and_out_of_range(scatter_slices):
     gen = torch.Generator().manual_seed(21)
     E, K, N = 500, 8, 20
     index = torch.randint(0, N, (1, E, 1), generator=gen)
     src = torch.randn(1, E, K, generator=gen)
     base = torch.randn(1, N, K, generator=gen)
-    for reduce in ('sum', 'min', 'max'):
+    for reduce in ('sum', 'mean', 'min', 'max'):
         want, _ = oracle.scatter(src, index, N, reduce, base)
         got, _, _ = cabi.scatter(src.cuda(), index.cuda(), N, reduce, (0, 1, 0), out=base.clone().cuda())
         assert_close(got, want, what=f'scatter seeded {reduce}')
