@@ -37,12 +37,12 @@ UNIT = 'GB/s'
 CSR_KERNEL_DRAM_TRAFFIC_BYTES = 4_611_700_000
 
 
-def row_lengths(rows, seed, force_long=8):
-    """Log-normal row lengths with mean ~16, clipped to 20,000, ~13% empty rows; `force_long` seeded
-    rows are set to 20,000 so that the long-row path is always exercised."""
+def row_lengths(rows, seed, force_long=8, mean=16.0):
+    """Log-normal row lengths with the given mean (16 by default), clipped to 20,000, ~13% empty rows;
+    `force_long` seeded rows are set to 20,000 so that the long-row path is always exercised."""
     g = torch.Generator().manual_seed(seed)
     sigma = 1.5
-    mu = torch.log(torch.tensor(16.5, dtype=torch.float64)) - sigma * sigma / 2
+    mu = torch.log(torch.tensor(mean + 0.5, dtype=torch.float64)) - sigma * sigma / 2
     z = torch.randn(rows, generator=g, dtype=torch.float64)
     lens = torch.exp(mu + sigma * z).floor().clamp_(0, 20000).long()
     if force_long:
@@ -390,7 +390,8 @@ def run_suite(args):
     """`--suite`: device-time table over the other BASELINE configurations (one JSON line per operator):
     C1 scatter sum [1,048,576 x 32] -> 65,536; C2 segment_csr sum/mean/min/max at F in {1,16,64,128} and
     gather_csr; C3 segment_coo / gather_coo / scatter_softmax on the sorted index in fp32/bf16/fp16;
-    C4 scatter sum/max/min with a Zipf(1.2) index over 100,000 targets, [33,554,432 x 16]."""
+    C4 scatter sum/max/min with a Zipf(1.2) index over 100,000 targets, [33,554,432 x 16]; C5 one GPU's 1/8 shard
+    of the 10M-node / 200M-edge bf16 F=128 aggregation."""
     import pytorch_scatter_b200 as ts
     dev = torch.device('cuda')
     peaks_path = osp.join(ROOT, 'MEASURED_PEAKS.json')
@@ -494,12 +495,34 @@ def run_suite(args):
             ms, gbs = timeit(lambda: fn(src, idx, 0, None, N), nb, False)
             emit('C4', f'scatter {reduce} fp32 [33554432x16] Zipf(1.2)->100000', ms, gbs)
 
+    def c5():
+        # One GPU's share of the 8-GPU job: 1/8 of the 200M edges (bf16 [25M x 128]); segment_csr over the
+        # shard's own row range (1.25M rows), scatter over all 10M destination rows (the full-length partial
+        # that the reduce-scatter would consume).  Row lengths: the log-normal recipe with mean 20.
+        rows_csr, n_all, F = 1_250_000, 10_000_000, 128
+        lens = row_lengths(rows_csr, SEED + 5, mean=20.0, force_long=8)
+        indptr = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)]).to(dev)
+        E = int(indptr[-1])
+        src = torch.randn(E, F, device=dev, generator=g).bfloat16()
+        for reduce in ('sum', 'mean'):
+            nb = E * F * 2 + (rows_csr + 1) * 8 + rows_csr * F * 2
+            ms, gbs = timeit(lambda: ts.segment_csr(src, indptr, reduce=reduce), nb, False)
+            emit('C5', f'segment_csr {reduce} bf16 F=128, {rows_csr} rows / {E} edges (1/8 shard)', ms, gbs)
+        idx = torch.randint(0, n_all, (E,), device=dev, generator=g)
+        for reduce in ('sum', 'max'):
+            nb = E * F * 2 + E * 8 + n_all * F * 2 + (n_all * F * 8 if reduce == 'max' else 0)
+            fn = getattr(ts, f'scatter_{reduce}')
+            ms, gbs = timeit(lambda: fn(src, idx, 0, None, n_all), nb, False)
+            emit('C5', f'scatter {reduce} bf16 F=128, {E} edges -> {n_all} rows (1/8 shard, full-length partial)', ms, gbs)
+
     if not only or 'C1' in only:
         c1()
     if not only or only & {'C2', 'C3'}:
         c2_c3()
     if not only or 'C4' in only:
         c4()
+    if not only or 'C5' in only:
+        c5()
 
 
 def main():

@@ -38,8 +38,9 @@ group_rank_kernel(const int64_t *__restrict__ index, int64_t E, int64_t N, int32
   rank[e] = (t >= 0 && t < N) ? atomicAdd(count + t, 1) : -1;  // -1: the entry names no row and is dropped
 }
 
+template <int THREADS = kThreads>
 __device__ __forceinline__ int64_t block_exclusive_scan(int64_t v, int64_t *total) {
-  __shared__ int64_t s_warp[kThreads / 32];
+  __shared__ int64_t s_warp[THREADS / 32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int64_t incl = v;
 #pragma unroll
@@ -51,7 +52,7 @@ __device__ __forceinline__ int64_t block_exclusive_scan(int64_t v, int64_t *tota
   __syncthreads();
   int64_t before = 0, all = 0;
 #pragma unroll
-  for (int w = 0; w < kThreads / 32; ++w) {
+  for (int w = 0; w < THREADS / 32; ++w) {
     if (w < warp) before += s_warp[w];
     all += s_warp[w];
   }
@@ -118,6 +119,226 @@ group_place_kernel(const int64_t *__restrict__ index, int64_t E, const int32_t *
   perm[rowptr[__ldcs(index + e)] + r] = (int32_t)e;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// The same grouping with shared-memory counters instead of one global atomic per entry.
+// Global atomics on random addresses run at some 100 G/s here, so the three random accesses per entry
+// of the kernels above (counter, row pointer, permutation slot) cost more than a third of the whole
+// scatter.  Two levels remove them:
+//   A  bucket_hist_kernel       rows are cut into P buckets of R = 2^shift rows; per-CTA histogram
+//                               of the entries over buckets in shared memory, then P global adds
+//   -  bucket_scan_kernel       exclusive scan -> first slot of every bucket
+//   B  bucket_partition_kernel  a CTA sorts a tile of 16384 entries by bucket in shared memory (rank
+//                               from a shared-memory atomic), reserves its share of every bucket
+//                               with one global add per bucket, writes (entry, row) pairs in runs
+//   C  bucket_finalize_kernel   one CTA per bucket: row counters and cursors in shared memory,
+//                               row pointers out, the bucket's slice of the permutation staged in
+//                               shared memory and written coalesced
+// Traffic: the index twice, the pairs written once and read twice (mostly from L2), permutation and
+// row pointers once.
+constexpr int kPartThreads = 1024;
+constexpr int kFinalThreads = 512;
+constexpr int kMaxBuckets = 4096;
+constexpr int kMaxBucketRows = 16384;
+constexpr int kStageEntries = 49152;  // most permutation slots kernel C stages in shared memory (192 KiB)
+constexpr int kFinalSmemInts = 56832; // rows + staged slots of kernel C (222 KiB)
+
+__global__ void __launch_bounds__(kThreads)
+bucket_hist_kernel(const int64_t *__restrict__ index, int64_t E, int64_t N, int shift, int P, int32_t *__restrict__ hist) {
+  extern __shared__ int s_hist[];
+  for (int b = threadIdx.x; b < P; b += kThreads) s_hist[b] = 0;
+  __syncthreads();
+  const int64_t first = (int64_t)blockIdx.x * (kThreads * 64);
+  for (int j = 0; j < 64; ++j) {
+    const int64_t e = first + (int64_t)j * kThreads + threadIdx.x;
+    if (e < E) {
+      const int64_t t = __ldcs(index + e);
+      if (t >= 0 && t < N) atomicAdd(&s_hist[(int)(t >> shift)], 1);
+    }
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < P; b += kThreads)
+    if (s_hist[b] != 0) atomicAdd(hist + b, s_hist[b]);
+}
+
+// start[b] = entries in the buckets before b, start[P] = all valid entries; cursor[b] = 0
+__global__ void __launch_bounds__(kThreads)
+bucket_scan_kernel(const int32_t *__restrict__ hist, int P, int32_t *__restrict__ start, int32_t *__restrict__ cursor) {
+  constexpr int kItems = kMaxBuckets / kThreads;
+  int c[kItems];
+  int64_t v = 0;
+#pragma unroll
+  for (int i = 0; i < kItems; ++i) {
+    const int b = threadIdx.x * kItems + i;
+    c[i] = b < P ? hist[b] : 0;
+    v += c[i];
+  }
+  int64_t total;
+  int64_t run = block_exclusive_scan(v, &total);
+#pragma unroll
+  for (int i = 0; i < kItems; ++i) {
+    const int b = threadIdx.x * kItems + i;
+    if (b < P) { start[b] = (int32_t)run; cursor[b] = 0; }
+    run += c[i];
+  }
+  if (threadIdx.x == 0) start[P] = (int32_t)total;
+}
+
+template <int kPartItems>  // entries per thread
+__global__ void __launch_bounds__(kPartThreads)
+bucket_partition_kernel(const int64_t *__restrict__ index, int64_t E, int64_t N, int shift, int P,
+                        const int32_t *__restrict__ start, int32_t *__restrict__ cursor, int2 *__restrict__ pairs) {
+  extern __shared__ int s_part[];
+  int *s_cnt = s_part;            // entries of this tile per bucket
+  int *s_off = s_part + P;        // first staging slot of the bucket
+  int *s_dst = s_part + 2 * P;    // first global slot this tile got in the bucket
+  int2 *s_pairs = reinterpret_cast<int2 *>(s_part + 3 * P + (P & 1));  // 8-byte aligned
+  for (int b = threadIdx.x; b < P; b += kPartThreads) s_cnt[b] = 0;
+  __syncthreads();
+  constexpr int kPartTile = kPartThreads * kPartItems;
+  const int64_t first = (int64_t)blockIdx.x * kPartTile;
+  int row[kPartItems], rank[kPartItems];
+#pragma unroll
+  for (int j = 0; j < kPartItems; ++j) {
+    const int64_t e = first + (int64_t)j * kPartThreads + threadIdx.x;
+    row[j] = -1;
+    rank[j] = 0;
+    if (e < E) {
+      const int64_t t = __ldcs(index + e);
+      if (t >= 0 && t < N) {
+        row[j] = (int)t;
+        rank[j] = atomicAdd(&s_cnt[(int)(t >> shift)], 1);
+      }
+    }
+  }
+  __syncthreads();
+  {  // exclusive scan of the tile's bucket counts; reserve the tile's slots in every bucket it feeds
+    constexpr int kItems = kMaxBuckets / kPartThreads;
+    int c[kItems];
+    int64_t v = 0;
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+      const int b = threadIdx.x * kItems + i;
+      c[i] = b < P ? s_cnt[b] : 0;
+      v += c[i];
+    }
+    int64_t total;
+    int run = (int)block_exclusive_scan<kPartThreads>(v, &total);
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+      const int b = threadIdx.x * kItems + i;
+      if (b < P) {
+        s_off[b] = run;
+        if (c[i] != 0) s_dst[b] = start[b] + atomicAdd(cursor + b, c[i]);
+      }
+      run += c[i];
+    }
+    if (threadIdx.x == 0) s_cnt[0] = (int)total;  // s_cnt is free again: keep the tile's valid count
+  }
+  __syncthreads();
+  const int valid = s_cnt[0];
+#pragma unroll
+  for (int j = 0; j < kPartItems; ++j) {
+    if (row[j] >= 0) {
+      const int64_t e = first + (int64_t)j * kPartThreads + threadIdx.x;
+      s_pairs[s_off[row[j] >> shift] + rank[j]] = make_int2((int)e, row[j]);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < valid; i += kPartThreads) {
+    const int2 pr = s_pairs[i];
+    const int b = pr.y >> shift;
+    pairs[s_dst[b] + (i - s_off[b])] = pr;
+  }
+}
+
+__global__ void __launch_bounds__(kFinalThreads)
+bucket_finalize_kernel(const int2 *__restrict__ pairs, const int32_t *__restrict__ start, int64_t N, int shift, int P,
+                       int32_t *__restrict__ perm, int64_t *__restrict__ rowptr, int32_t *__restrict__ count_out,
+                       int stage_entries) {
+  extern __shared__ int s_fin[];
+  const int R = 1 << shift;
+  int *s_rows = s_fin;       // per row of the bucket: count, then first slot, then cursor
+  int *s_perm = s_fin + R;   // the bucket's slice of the permutation, when it fits
+  const int b = blockIdx.x;
+  const int lo = start[b];
+  const int n = start[b + 1] - lo;
+  const int64_t row0 = (int64_t)b << shift;
+  for (int j = threadIdx.x; j < R; j += kFinalThreads) s_rows[j] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += kFinalThreads) atomicAdd(&s_rows[pairs[lo + i].y - (int)row0], 1);
+  __syncthreads();
+  {  // exclusive scan over the R rows: thread t owns rows [t * per, t * per + per)
+    const int per = (R + kFinalThreads - 1) / kFinalThreads;
+    const int j0 = threadIdx.x * per;
+    int64_t v = 0;
+    for (int i = 0; i < per; ++i)
+      if (j0 + i < R) v += s_rows[j0 + i];
+    int64_t total;
+    int run = (int)block_exclusive_scan<kFinalThreads>(v, &total);
+    for (int i = 0; i < per; ++i) {
+      const int j = j0 + i;
+      if (j < R) {
+        const int c = s_rows[j];
+        s_rows[j] = run;
+        if (row0 + j < N) {
+          rowptr[row0 + j] = (int64_t)lo + run;
+          if (count_out != nullptr) count_out[row0 + j] = c;
+        }
+        run += c;
+      }
+    }
+    if (b == P - 1 && threadIdx.x == 0) rowptr[N] = (int64_t)lo + n;
+  }
+  __syncthreads();
+  const bool staged = n <= stage_entries;
+  for (int i = threadIdx.x; i < n; i += kFinalThreads) {
+    const int2 pr = pairs[lo + i];
+    const int slot = atomicAdd(&s_rows[pr.y - (int)row0], 1);
+    if (staged) s_perm[slot] = pr.x;
+    else perm[lo + slot] = pr.x;
+  }
+  if (!staged) return;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += kFinalThreads) perm[lo + i] = s_perm[i];
+}
+
+// Bucket geometry: 12k to 24k entries per bucket on average, so that nearly every bucket's slice of the
+// permutation fits the shared-memory stage.  shift < 0: the shapes do not fit (too many rows for
+// kMaxBuckets buckets of kMaxBucketRows rows) and the global-atomic kernels are used.
+struct BucketGeom { int shift, P; };
+int tuning(const char *name, int fallback) {  // tuning hooks, read per call
+  const char *v = std::getenv(name);
+  const int x = v != nullptr ? std::atoi(v) : 0;
+  return x > 0 ? x : fallback;
+}
+BucketGeom bucket_geom(int64_t E, int64_t N) {
+  const int64_t want = ((int64_t)tuning("TSB_GROUPED_BUCKET_ENTRIES", 12288) * N) / (E > 0 ? E : 1);  // rows holding that many entries
+  int shift = 6;
+  while ((1ll << shift) < want && (1 << shift) < kMaxBucketRows) ++shift;  // rounded up to a power of two
+  while (((N + (1ll << shift) - 1) >> shift) > kMaxBuckets && (1 << shift) < kMaxBucketRows) ++shift;
+  const int64_t P = (N + (1ll << shift) - 1) >> shift;
+  if (P > kMaxBuckets) return BucketGeom{-1, 0};
+  return BucketGeom{shift, (int)P};
+}
+
+// Shared memory above the 48 KiB default has to be allowed per kernel and device, once.
+int allow_bucket_smem() {
+  static bool done[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TSB_ERR_LAUNCH;
+  if (done[dev]) return TSB_OK;
+  const int part = (3 * kMaxBuckets + 1) * (int)sizeof(int);
+  const int pair = kPartThreads * (int)sizeof(int2);
+  const int fin = kFinalSmemInts * (int)sizeof(int);
+  if (cudaFuncSetAttribute(bucket_partition_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, part + 8 * pair) != cudaSuccess ||
+      cudaFuncSetAttribute(bucket_partition_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, part + 16 * pair) != cudaSuccess ||
+      cudaFuncSetAttribute(bucket_finalize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fin) != cudaSuccess)
+    return TSB_ERR_LAUNCH;
+  done[dev] = true;
+  return TSB_OK;
+}
+
 size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 struct GroupedLayout {
@@ -127,10 +348,10 @@ GroupedLayout layout_for(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, 
   GroupedLayout l;
   size_t off = 0;
   l.count = off;  off += up256((size_t)N * sizeof(int32_t));
-  l.rank = off;   off += up256((size_t)E * sizeof(int32_t));
+  l.rank = off;   off += up256((size_t)E * sizeof(int2));  // ranks (global-atomic kernels) or (entry, row) pairs
   l.rowptr = off; off += up256((size_t)(N + 1) * sizeof(int64_t));
   l.perm = off;   off += up256((size_t)E * sizeof(int32_t));
-  l.tiles = off;  off += up256((size_t)((N + kScanTile - 1) / kScanTile + 1) * sizeof(int64_t));
+  l.tiles = off;  off += up256((size_t)((N + kScanTile - 1) / kScanTile + 1) * sizeof(int64_t) + (size_t)(3 * kMaxBuckets + 1) * sizeof(int32_t));
   l.csr = off;    off += up256(csr_reduce_workspace_bytes(B, E, K, N, dtype, reduce));
   l.total = off;
   return l;
@@ -165,15 +386,45 @@ int run_scatter_grouped(const void *src, const int64_t *index, void *out, int64_
   int32_t *perm = reinterpret_cast<int32_t *>(ws + l.perm);
   int64_t *tiles = reinterpret_cast<int64_t *>(ws + l.tiles);
 
-  const int64_t entry_blocks = (E + kThreads - 1) / kThreads;
-  const int64_t n_tiles = (N + kScanTile - 1) / kScanTile;
-  if (entry_blocks > 2147483647LL || n_tiles > 2147483647LL) return TSB_ERR_TOO_LARGE;
-  if (cudaMemsetAsync(count, 0, (size_t)N * sizeof(int32_t), stream) != cudaSuccess) return TSB_ERR_LAUNCH;
-  group_rank_kernel<<<(unsigned)entry_blocks, kThreads, 0, stream>>>(index, E, N, count, rank);
-  scan_tile_sums_kernel<<<(unsigned)n_tiles, kThreads, 0, stream>>>(count, N, tiles);
-  scan_tile_offsets_kernel<<<1, kThreads, 0, stream>>>(tiles, n_tiles);
-  scan_rowptr_kernel<<<(unsigned)n_tiles, kThreads, 0, stream>>>(count, N, tiles, rowptr);
-  group_place_kernel<<<(unsigned)entry_blocks, kThreads, 0, stream>>>(index, E, rank, rowptr, perm);
+  const char *sort_env = std::getenv("TSB_SCATTER_GROUPED_SORT");  // test hook: "atomic" forces the global-atomic kernels
+  const BucketGeom geom = (sort_env != nullptr && sort_env[0] == 'a') ? BucketGeom{-1, 0} : bucket_geom(E, N);
+  if (geom.shift >= 0) {
+    const int st = allow_bucket_smem();
+    if (st != TSB_OK) return st;
+    int32_t *hist = reinterpret_cast<int32_t *>(tiles);
+    int32_t *start = hist + kMaxBuckets;
+    int32_t *cursor = start + kMaxBuckets + 1;
+    int2 *pairs = reinterpret_cast<int2 *>(rank);
+    const int P = geom.P, R = 1 << geom.shift;
+    const int64_t hist_blocks = (E + kThreads * 64 - 1) / (kThreads * 64);
+    const int part_items = tuning("TSB_GROUPED_PART_ITEMS", 16) >= 16 ? 16 : 8;
+    const int part_tile = kPartThreads * part_items;
+    const int64_t part_blocks = (E + part_tile - 1) / part_tile;
+    if (cudaMemsetAsync(hist, 0, (size_t)P * sizeof(int32_t), stream) != cudaSuccess) return TSB_ERR_LAUNCH;
+    bucket_hist_kernel<<<(unsigned)hist_blocks, kThreads, (size_t)P * sizeof(int), stream>>>(index, E, N, geom.shift, P, hist);
+    bucket_scan_kernel<<<1, kThreads, 0, stream>>>(hist, P, start, cursor);
+    const size_t part_smem = (size_t)(3 * P + (P & 1)) * sizeof(int) + (size_t)part_tile * sizeof(int2);
+    if (part_items == 16)
+      bucket_partition_kernel<16><<<(unsigned)part_blocks, kPartThreads, part_smem, stream>>>(index, E, N, geom.shift, P, start, cursor, pairs);
+    else
+      bucket_partition_kernel<8><<<(unsigned)part_blocks, kPartThreads, part_smem, stream>>>(index, E, N, geom.shift, P, start, cursor, pairs);
+    int stage = tuning("TSB_GROUPED_STAGE_ENTRIES", 24576);
+    if (stage > kStageEntries) stage = kStageEntries;
+    if (stage > kFinalSmemInts - R) stage = kFinalSmemInts - R;
+    const size_t fin_smem = (size_t)(R + stage) * sizeof(int);
+    bucket_finalize_kernel<<<(unsigned)P, kFinalThreads, fin_smem, stream>>>(
+        pairs, start, N, geom.shift, P, perm, rowptr, reduce == TSB_MEAN ? count_out : nullptr, stage);
+  } else {
+    const int64_t entry_blocks = (E + kThreads - 1) / kThreads;
+    const int64_t n_tiles = (N + kScanTile - 1) / kScanTile;
+    if (entry_blocks > 2147483647LL || n_tiles > 2147483647LL) return TSB_ERR_TOO_LARGE;
+    if (cudaMemsetAsync(count, 0, (size_t)N * sizeof(int32_t), stream) != cudaSuccess) return TSB_ERR_LAUNCH;
+    group_rank_kernel<<<(unsigned)entry_blocks, kThreads, 0, stream>>>(index, E, N, count, rank);
+    scan_tile_sums_kernel<<<(unsigned)n_tiles, kThreads, 0, stream>>>(count, N, tiles);
+    scan_tile_offsets_kernel<<<1, kThreads, 0, stream>>>(tiles, n_tiles);
+    scan_rowptr_kernel<<<(unsigned)n_tiles, kThreads, 0, stream>>>(count, N, tiles, rowptr);
+    group_place_kernel<<<(unsigned)entry_blocks, kThreads, 0, stream>>>(index, E, rank, rowptr, perm);
+  }
   if (launch_status() != TSB_OK) return TSB_ERR_LAUNCH;
 
   CsrParams p;

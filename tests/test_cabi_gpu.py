@@ -207,7 +207,8 @@ def test_gathers(K):
         assert_close(cabi.gather_coo(table.cuda(), index.cuda(), count.cuda()), want, what='gather_coo divide')
 
 
-@pytest.fixture(params=['one-pass', 'sliced', 'replicated', 'runs', 'runs-sliced', 'direct', 'grouped', 'grouped-chunk32'])
+@pytest.fixture(params=['one-pass', 'sliced', 'replicated', 'runs', 'runs-sliced', 'direct', 'grouped', 'grouped-chunk32',
+                        'grouped-atomic'])
 def scatter_slices(request):
     """Forces the variants the launcher normally picks by size or by probing the index: sliced multi-pass
     accumulation (outputs larger than L2), accumulation into several copies of the output (small,
@@ -215,7 +216,7 @@ def scatter_slices(request):
     entries by target row and reduces rows through the permutation (also with 32-entry chunks, so that rows
     straddle many chunk borders)."""
     names = ('TSB_SCATTER_SLICE_BYTES', 'TSB_SCATTER_REPLICAS', 'TSB_SCATTER_CLUSTERED', 'TSB_SCATTER_GROUPED',
-             'TSB_CSR_CHUNK_ENTRIES')
+             'TSB_CSR_CHUNK_ENTRIES', 'TSB_SCATTER_GROUPED_SORT')
     old = {k: os.environ.get(k) for k in names}
     for k in names:
         os.environ.pop(k, None)
@@ -230,6 +231,8 @@ def scatter_slices(request):
     os.environ['TSB_SCATTER_GROUPED'] = '1' if request.param.startswith('grouped') else '0'
     if request.param == 'grouped-chunk32':
         os.environ['TSB_CSR_CHUNK_ENTRIES'] = '32'
+    if request.param == 'grouped-atomic':  # the grouping by one global atomic per entry (huge row counts)
+        os.environ['TSB_SCATTER_GROUPED_SORT'] = 'atomic'
     yield request.param
     for k, v in old.items():
         if v is None:
@@ -313,6 +316,41 @@ def test_scatter_rows_ties(scatter_slices):
             got, got_arg, _ = cabi.scatter(src.cuda(), index.cuda(), N, reduce, (0, 1, 0), out=base.clone().cuda())
             assert_close(got, want, what=f'seeded ties {reduce} {dtype}')
             assert torch.equal(got_arg.cpu(), want_arg), f'seeded ties {reduce} {dtype} arg'
+
+
+@pytest.mark.parametrize('sort', ['buckets', 'atomic'])
+def test_scatter_grouped_many_buckets(sort):
+    """The atomics-free path at a size with tens of buckets, one of them (a 40,000-entry row) larger than the
+    shared-memory stage, entries that name no row, and a batch dimension sharing the index."""
+    names = ('TSB_SCATTER_GROUPED', 'TSB_SCATTER_GROUPED_SORT')
+    old = {k: os.environ.get(k) for k in names}
+    os.environ['TSB_SCATTER_GROUPED'] = '1'
+    os.environ['TSB_SCATTER_GROUPED_SORT'] = sort
+    try:
+        gen = torch.Generator().manual_seed(91)
+        B, E, K, N = 2, 400000, 4, 300000
+        index = torch.randint(0, N, (1, E, 1), generator=gen)
+        index[0, 1000:41000, 0] = 123456
+        index[0, ::97, 0] = N + 5
+        index[0, 5::101, 0] = -3
+        keep = ((index >= 0) & (index < N)).view(-1)
+        src = torch.randint(-8, 9, (B, E, K), generator=gen).float()   # exact in fp32 in any order
+        for reduce in ('sum', 'mean', 'max'):
+            got, got_arg, count = cabi.scatter(src.cuda(), index.cuda(), N, reduce, (0, 1, 0))
+            kept = torch.nonzero(keep).view(-1)
+            want, want_arg = oracle.scatter(src[:, keep], index[:, keep], N, reduce)
+            assert_close(got, want, what=f'grouped {sort} {reduce}')
+            if want_arg is not None:   # the oracle saw the compacted entries: map its args back
+                lut = torch.cat([kept, torch.tensor([E])])
+                assert torch.equal(got_arg.cpu(), lut[want_arg.clamp(max=kept.numel())]), f'grouped {sort} {reduce} arg'
+            if reduce == 'mean':
+                assert torch.equal(count.cpu().long(), torch.bincount(index.view(-1)[keep], minlength=N))
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
 
 
 def test_scatter_seeded_and_out_of_range(scatter_slices):
