@@ -289,10 +289,6 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
   const T *bsrc = src + (b * p.E) * p.K;
   const int64_t step_stride = (int64_t)eps * p.K;  // elements between consecutive steps of a lane
 
-  Pack<T, VEC> fill;  // what a lane without an entry holds: the identity, so that it never matters
-#pragma unroll
-  for (int i = 0; i < VEC; ++i) fill.v[i] = from_acc<T>(reduce_identity<T, REDUCE>());
-
   A *carry = static_cast<A *>(g.carry_val) + chunk_id * 2 * p.K;
   int64_t *carry_arg = Acc::kPair ? g.carry_arg + chunk_id * 2 * p.K : nullptr;  // arg indices / LSE sums
 
@@ -414,17 +410,19 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
     for (int pos = 0; pos < t; pos += eps) {
       async_wait_all_but<S - 1>();  // the oldest copy in flight, this slot's, has landed
       const int e = pos + sub;
-      const Pack<T, VEC> v = (col_ok && e < t) ? s_ring[slot][lane] : fill;
+      // A lane without an entry (past the chunk's end, or a column beyond K) reads a stale slot; its
+      // value is never used: the updates below are predicated on e, such a column is never written.
+      const Pack<T, VEC> v = s_ring[slot][lane];
       const int id = (INDIRECT && kArg) ? s_id[slot][lane] : e;
       const int step_end = (pos + eps < t) ? pos + eps : t;
       if (cur_end <= step_end) close_rows(v, e, id, step_end);
-      if (e >= cur_start) acc.template update<INDIRECT>(v, id, kRelInf);  // the row still open after this step
+      if (e >= cur_start && e < t) acc.template update<INDIRECT>(v, id, kRelInf);  // the row still open after this step
       issue(slot);
       slot = (slot + 1) & (S - 1);
     }
     async_wait_all_but<0>();
     // rows that end exactly at the chunk's end, including rows without entries there
-    close_rows(fill, t, t, t);
+    close_rows(Pack<T, VEC>(), t, t, t);  // e == t belongs to no row: the value is not looked at
 
     // the row still open runs on into the next chunk: store what this chunk holds of it
     if (r_win + cur < p.N && cur_start < t) {
