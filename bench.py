@@ -342,9 +342,11 @@ def run_ours(args):
                          'peak_source': peak_src, 'algorithmic_bytes_per_launch': b[0][0]},
             'e2e': {'value': (b_csr + b_sc) / (e2e_ms * 1e-3) / 1e9, 'unit': UNIT, 'ms_per_step': e2e_ms,
                     'steps': e2e_steps, 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h},
-            # per step: csr_stream_kernel + csr_fixup_kernel + scatter_probe_kernel + per output slice one
-            # scatter_rows_range_kernel and one scatter_rows_runs_kernel (the probe's flag makes one of them exit)
-            'gpu_launches': (3 + 2 * scatter_passes) * args.steps,
+            # per step, segment_csr: csr_stream_kernel + csr_fixup_kernel.  scatter on one GPU (output larger
+            # than L2: the grouped path): bucket_hist, bucket_scan, bucket_partition, bucket_finalize, then
+            # csr_stream_kernel + csr_fixup_kernel through the permutation.  Several GPUs: the probe plus, per
+            # output slice, one range kernel and one runs kernel (the probe's flag makes one of them exit).
+            'gpu_launches': ((2 + 6) if world == 1 else (3 + 2 * scatter_passes)) * args.steps,
             'clocks': clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
