@@ -172,6 +172,26 @@ int tsb_scatter(const void *src, const int64_t *index, void *out, int64_t *arg_o
                 int dtype, int reduce, int out_seeded,
                 void *workspace, size_t workspace_bytes, tsb_stream_t stream);
 
+/* The two halves of the atomics-free scatter, for callers that reuse one grouping for several reductions or
+ * reduce the rows slice by slice (a sharded scatter hands every finished slice to its collective while the next
+ * one is reduced).  No counterpart upstream.
+ *   tsb_scatter_group     groups the entry ids 0..E-1 by the row index[e] names: rowptr [N+1] int64 (row n owns
+ *                         perm[rowptr[n] .. rowptr[n+1])), perm [E] int32 (entries naming no row are dropped, so
+ *                         only the first rowptr[N] slots are meaningful), count [N] int32 entries per row or NULL
+ *                         (required above 67 M rows).  E < 2^30.  The order inside a row is not fixed.
+ *   tsb_segment_csr_perm  out[b, n, :] = reduce over q in [rowptr[n], rowptr[n+1]) of src[b, perm[q], :] for the rows
+ *                         row_lo <= n < row_hi (other rows of out are not touched; a proper slice needs B == 1),
+ *                         with scatter's write rules (out_seeded as in tsb_scatter; MIN/MAX args are entry ids,
+ *                         ties towards the smaller id).  SUM, MEAN, MIN or MAX. */
+size_t tsb_scatter_group_workspace_bytes(int64_t E, int64_t N);
+int tsb_scatter_group(const int64_t *index, int64_t E, int64_t N, int64_t *rowptr, int32_t *perm, int32_t *count,
+                      void *workspace, size_t workspace_bytes, tsb_stream_t stream);
+size_t tsb_segment_csr_perm_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce);
+int tsb_segment_csr_perm(const void *src, const int64_t *rowptr, const int32_t *perm, void *out, int64_t *arg_out,
+                         int64_t B, int64_t E, int64_t K, int64_t N, int64_t row_lo, int64_t row_hi,
+                         int dtype, int reduce, int out_seeded,
+                         void *workspace, size_t workspace_bytes, tsb_stream_t stream);
+
 /* One slice of an unsorted scatter SUM, for sharded use: adds the E edges of this call (src [E,K], 1-D index [E])
  * into the target rows [row_lo, row_hi) of `partial` [N,K], after zeroing exactly those rows; targets outside the
  * slice are ignored.  `partial` is held in accumulation precision: fp32 for fp32/fp16/bf16 sources, the source

@@ -25,6 +25,10 @@ struct CsrParams {
   // then reduce rows" without moving the source.  MIN/MAX then report perm[q] as the arg and break
   // ties towards the smaller entry id.  Requires E < 2^30.
   const int32_t *perm = nullptr;
+  // Row pointers that cover only part of [0, E) (a slice of the rows of a larger problem): chunks that
+  // lie entirely before indptr[0] or after indptr[N] return at once instead of streaming entries that
+  // belong to no row.  Single batch only.
+  bool skip_outside = false;
   int mode;
   void *workspace;        // csr_reduce_workspace_bytes(...) bytes, 256-byte aligned
   size_t workspace_bytes;

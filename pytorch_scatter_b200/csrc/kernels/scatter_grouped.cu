@@ -342,16 +342,16 @@ int allow_bucket_smem() {
 size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 struct GroupedLayout {
-  size_t count, rank, rowptr, perm, tiles, csr, total;
+  size_t count, rowptr, perm, group, csr, total;
 };
+size_t group_scratch_bytes(int64_t E, int64_t N);
 GroupedLayout layout_for(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce) {
   GroupedLayout l;
   size_t off = 0;
   l.count = off;  off += up256((size_t)N * sizeof(int32_t));
-  l.rank = off;   off += up256((size_t)E * sizeof(int2));  // ranks (global-atomic kernels) or (entry, row) pairs
   l.rowptr = off; off += up256((size_t)(N + 1) * sizeof(int64_t));
   l.perm = off;   off += up256((size_t)E * sizeof(int32_t));
-  l.tiles = off;  off += up256((size_t)((N + kScanTile - 1) / kScanTile + 1) * sizeof(int64_t) + (size_t)(3 * kMaxBuckets + 1) * sizeof(int32_t));
+  l.group = off;  off += up256(group_scratch_bytes(E, N));
   l.csr = off;    off += up256(csr_reduce_workspace_bytes(B, E, K, N, dtype, reduce));
   l.total = off;
   return l;
@@ -373,21 +373,39 @@ size_t scatter_grouped_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t 
   return layout_for(B, E, K, N, dtype, reduce).total;
 }
 
-int run_scatter_grouped(const void *src, const int64_t *index, void *out, int64_t *arg_out, int32_t *count_out,
-                        int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce, int out_seeded,
-                        void *workspace, size_t workspace_bytes, cudaStream_t stream) {
-  const GroupedLayout l = layout_for(B, E, K, N, dtype, reduce);
+namespace {
+struct GroupScratch { size_t pairs, tiles, total; };
+GroupScratch group_scratch(int64_t E, int64_t N);
+size_t group_scratch_bytes(int64_t E, int64_t N) { return group_scratch(E, N).total; }
+GroupScratch group_scratch(int64_t E, int64_t N) {
+  GroupScratch l;
+  size_t off = 0;
+  l.pairs = off; off += up256((size_t)E * sizeof(int2));  // ranks (global-atomic kernels) or (entry, row) pairs
+  l.tiles = off; off += up256((size_t)((N + kScanTile - 1) / kScanTile + 1) * sizeof(int64_t) + (size_t)(3 * kMaxBuckets + 1) * sizeof(int32_t));
+  l.total = off;
+  return l;
+}
+}  // namespace
+
+size_t scatter_group_workspace_bytes(int64_t E, int64_t N) {
+  if (E < 1 || N < 1 || E >= (1ll << 30)) return 256;
+  return group_scratch(E, N).total;
+}
+
+// rowptr [N+1], perm [E] (its first rowptr[N] slots are meaningful), count [N] or null.
+int scatter_group(const int64_t *index, int64_t E, int64_t N, int64_t *rowptr, int32_t *perm, int32_t *count,
+                  void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+  if (E < 1 || N < 1 || E >= (1ll << 30) || N >= (1ll << 31) - 1) return TSB_ERR_TOO_LARGE;
+  const GroupScratch l = group_scratch(E, N);
   if (workspace == nullptr || workspace_bytes < l.total || (reinterpret_cast<uintptr_t>(workspace) & 255u))
     return TSB_ERR_WORKSPACE;
   unsigned char *ws = static_cast<unsigned char *>(workspace);
-  int32_t *count = (reduce == TSB_MEAN && count_out != nullptr) ? count_out : reinterpret_cast<int32_t *>(ws + l.count);
-  int32_t *rank = reinterpret_cast<int32_t *>(ws + l.rank);
-  int64_t *rowptr = reinterpret_cast<int64_t *>(ws + l.rowptr);
-  int32_t *perm = reinterpret_cast<int32_t *>(ws + l.perm);
+  int32_t *rank = reinterpret_cast<int32_t *>(ws + l.pairs);
   int64_t *tiles = reinterpret_cast<int64_t *>(ws + l.tiles);
 
   const char *sort_env = std::getenv("TSB_SCATTER_GROUPED_SORT");  // test hook: "atomic" forces the global-atomic kernels
-  const BucketGeom geom = (sort_env != nullptr && sort_env[0] == 'a') ? BucketGeom{-1, 0} : bucket_geom(E, N);
+  BucketGeom geom = (sort_env != nullptr && sort_env[0] == 'a') ? BucketGeom{-1, 0} : bucket_geom(E, N);
+  if (geom.shift < 0 && count == nullptr) return TSB_ERR_ARG;  // the global-atomic kernels need a counter per row
   if (geom.shift >= 0) {
     const int st = allow_bucket_smem();
     if (st != TSB_OK) return st;
@@ -412,8 +430,7 @@ int run_scatter_grouped(const void *src, const int64_t *index, void *out, int64_
     if (stage > kStageEntries) stage = kStageEntries;
     if (stage > kFinalSmemInts - R) stage = kFinalSmemInts - R;
     const size_t fin_smem = (size_t)(R + stage) * sizeof(int);
-    bucket_finalize_kernel<<<(unsigned)P, kFinalThreads, fin_smem, stream>>>(
-        pairs, start, N, geom.shift, P, perm, rowptr, reduce == TSB_MEAN ? count_out : nullptr, stage);
+    bucket_finalize_kernel<<<(unsigned)P, kFinalThreads, fin_smem, stream>>>(pairs, start, N, geom.shift, P, perm, rowptr, count, stage);
   } else {
     const int64_t entry_blocks = (E + kThreads - 1) / kThreads;
     const int64_t n_tiles = (N + kScanTile - 1) / kScanTile;
@@ -425,7 +442,21 @@ int run_scatter_grouped(const void *src, const int64_t *index, void *out, int64_
     scan_rowptr_kernel<<<(unsigned)n_tiles, kThreads, 0, stream>>>(count, N, tiles, rowptr);
     group_place_kernel<<<(unsigned)entry_blocks, kThreads, 0, stream>>>(index, E, rank, rowptr, perm);
   }
-  if (launch_status() != TSB_OK) return TSB_ERR_LAUNCH;
+  return launch_status();
+}
+
+int run_scatter_grouped(const void *src, const int64_t *index, void *out, int64_t *arg_out, int32_t *count_out,
+                        int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce, int out_seeded,
+                        void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+  const GroupedLayout l = layout_for(B, E, K, N, dtype, reduce);
+  if (workspace == nullptr || workspace_bytes < l.total || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+    return TSB_ERR_WORKSPACE;
+  unsigned char *ws = static_cast<unsigned char *>(workspace);
+  int32_t *count = (reduce == TSB_MEAN && count_out != nullptr) ? count_out : reinterpret_cast<int32_t *>(ws + l.count);
+  int64_t *rowptr = reinterpret_cast<int64_t *>(ws + l.rowptr);
+  int32_t *perm = reinterpret_cast<int32_t *>(ws + l.perm);
+  const int st = scatter_group(index, E, N, rowptr, perm, count, ws + l.group, l.csr - l.group, stream);
+  if (st != TSB_OK) return st;
 
   CsrParams p;
   p.src = src;
@@ -443,3 +474,53 @@ int run_scatter_grouped(const void *src, const int64_t *index, void *out, int64_
 }
 
 }  // namespace tsb
+
+extern "C" size_t tsb_scatter_group_workspace_bytes(int64_t E, int64_t N) { return tsb::scatter_group_workspace_bytes(E, N); }
+
+extern "C" int tsb_scatter_group(const int64_t *index, int64_t E, int64_t N, int64_t *rowptr, int32_t *perm,
+                                 int32_t *count, void *workspace, size_t workspace_bytes, tsb_stream_t stream) {
+  if (E < 0 || N < 1 || rowptr == nullptr) return TSB_ERR_ARG;
+  if (E == 0) {
+    return cudaMemsetAsync(rowptr, 0, (size_t)(N + 1) * sizeof(int64_t), reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess &&
+                   (count == nullptr ||
+                    cudaMemsetAsync(count, 0, (size_t)N * sizeof(int32_t), reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess)
+               ? TSB_OK
+               : TSB_ERR_LAUNCH;
+  }
+  if (index == nullptr || perm == nullptr) return TSB_ERR_ARG;
+  return tsb::scatter_group(index, E, N, rowptr, perm, count, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t tsb_segment_csr_perm_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce) {
+  return tsb::csr_reduce_workspace_bytes(B, E, K, N, dtype, reduce);
+}
+
+extern "C" int tsb_segment_csr_perm(const void *src, const int64_t *rowptr, const int32_t *perm, void *out,
+                                    int64_t *arg_out, int64_t B, int64_t E, int64_t K, int64_t N, int64_t row_lo,
+                                    int64_t row_hi, int dtype, int reduce, int out_seeded, void *workspace,
+                                    size_t workspace_bytes, tsb_stream_t stream) {
+  using namespace tsb;
+  if (B < 0 || E < 0 || K < 0 || N < 0 || row_lo < 0 || row_hi > N) return TSB_ERR_ARG;
+  if (B * K == 0 || row_hi <= row_lo) return TSB_OK;
+  if (rowptr == nullptr || out == nullptr || (E > 0 && (src == nullptr || perm == nullptr))) return TSB_ERR_ARG;
+  const bool slice = row_lo != 0 || row_hi != N;
+  if (slice && B != 1) return TSB_ERR_ARG;
+  size_t elem = 4;
+  if (dtype == TSB_F64 || dtype == TSB_I64) elem = 8;
+  else if (dtype == TSB_F16 || dtype == TSB_BF16) elem = 2;
+  CsrParams p;
+  p.src = src;
+  p.indptr = rowptr + row_lo;
+  p.out = static_cast<unsigned char *>(out) + (size_t)(row_lo * K) * elem;
+  p.arg_out = arg_out != nullptr ? arg_out + row_lo * K : nullptr;
+  p.count_out = nullptr;
+  p.B = B; p.E = E; p.K = K; p.N = row_hi - row_lo;
+  p.bstride = 0;
+  p.perm = E > 0 ? perm : nullptr;
+  p.skip_outside = slice;
+  p.mode = out_seeded ? kCooSeeded : kCooFresh;
+  p.workspace = workspace;
+  p.workspace_bytes = workspace_bytes;
+  return launch_csr_reduce(p, dtype, reduce, reinterpret_cast<cudaStream_t>(stream));
+}
+

@@ -260,6 +260,10 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
   const int64_t ce = (cs + g.chunk_entries < p.E) ? cs + g.chunk_entries : p.E;
   const int t = (int)(ce - cs);
   const int64_t *ip = p.indptr + b * p.bstride;
+  if (p.skip_outside && (ce <= ip[0] || cs >= ip[p.N])) {  // warp-uniform
+    if (lane == 0) g.head_row[chunk_id] = -1;
+    return;
+  }
 
   // ---- first row that ends after cs: 32-ary search over ends[r] = indptr[r + 1] -----------------
   int64_t r_first = 0;
@@ -581,6 +585,7 @@ int launch_csr_reduce(const CsrParams &p, int dtype, int reduce, cudaStream_t st
   if (p.indptr == nullptr || p.out == nullptr) return TSB_ERR_ARG;
   if ((reduce == TSB_MIN || reduce == TSB_MAX) && p.arg_out == nullptr) return TSB_ERR_ARG;
   if (p.perm != nullptr && p.E >= kRelInf) return TSB_ERR_TOO_LARGE;
+  if (p.skip_outside && p.B != 1) return TSB_ERR_ARG;
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
     switch (reduce) {
       case TSB_SUM: return launch_typed<scalar_t, kSum>(p, stream);

@@ -299,6 +299,54 @@ torch::Tensor scatter_sum_slice(torch::Tensor src, torch::Tensor index, torch::T
   return partial;
 }
 
+// Sharded building blocks of the atomics-free path.  scatter_group: entry ids grouped by target row,
+// (rowptr int64 [N+1], perm int32 [E]).  segment_sum_perm: sums src rows through that grouping into the rows
+// [row_lo, row_hi) of `partial` [N, ...] (same dtype as src; 16-bit sources accumulate in fp32 registers and
+// are rounded once).  Not differentiable.
+std::tuple<torch::Tensor, torch::Tensor> scatter_group(torch::Tensor index, int64_t dim_size) {
+  TSB_CHECK_CUDA(index);
+  check_index_dtype(index, "index");
+  TSB_CHECK_INPUT(index.dim() == 1 && dim_size >= 1);
+  c10::cuda::CUDAGuard guard(index.device());
+  index = index.contiguous();
+  const int64_t E = index.numel();
+  auto rowptr = torch::empty({dim_size + 1}, index.options());
+  auto perm = torch::empty({E}, index.options().dtype(torch::kInt32));
+  auto count = torch::empty({dim_size}, index.options().dtype(torch::kInt32));
+  const size_t ws_bytes = tsb_scatter_group_workspace_bytes(E, dim_size);
+  auto workspace = torch::empty({(int64_t)ws_bytes}, index.options().dtype(torch::kUInt8));
+  check_status(tsb_scatter_group(index.data_ptr<int64_t>(), E, dim_size, rowptr.data_ptr<int64_t>(),
+                                 perm.data_ptr<int32_t>(), count.data_ptr<int32_t>(), workspace.data_ptr(), ws_bytes,
+                                 current_stream()),
+               "tsb_scatter_group");
+  return std::make_tuple(rowptr, perm);
+}
+
+torch::Tensor segment_sum_perm(torch::Tensor src, torch::Tensor rowptr, torch::Tensor perm, torch::Tensor partial,
+                               int64_t row_lo, int64_t row_hi) {
+  TSB_CHECK_CUDA(src);
+  TSB_CHECK_CUDA(rowptr);
+  TSB_CHECK_CUDA(perm);
+  TSB_CHECK_CUDA(partial);
+  check_index_dtype(rowptr, "rowptr");
+  TORCH_CHECK(perm.scalar_type() == at::ScalarType::Int, "perm must be int32");
+  c10::cuda::CUDAGuard guard(src.device());
+  TSB_CHECK_INPUT(rowptr.dim() == 1 && perm.dim() == 1 && src.dim() >= 1 && src.size(0) == perm.size(0));
+  TSB_CHECK_INPUT(partial.dim() == src.dim() && partial.is_contiguous() && rowptr.is_contiguous() && perm.is_contiguous());
+  TSB_CHECK_INPUT(partial.size(0) + 1 == rowptr.size(0) && partial.scalar_type() == src.scalar_type());
+  for (int64_t i = 1; i < src.dim(); i++) TSB_CHECK_INPUT(src.size(i) == partial.size(i));
+  src = src.contiguous();
+  const int64_t E = src.size(0), N = partial.size(0);
+  const int64_t K = E > 0 ? src.numel() / E : (N > 0 ? partial.numel() / N : 0);
+  const size_t ws_bytes = tsb_segment_csr_perm_workspace_bytes(1, E, K, N, dtype_enum(src), TSB_SUM);
+  auto workspace = torch::empty({(int64_t)ws_bytes}, src.options().dtype(torch::kUInt8));
+  check_status(tsb_segment_csr_perm(src.data_ptr(), rowptr.data_ptr<int64_t>(), perm.data_ptr<int32_t>(),
+                                    partial.data_ptr(), nullptr, 1, E, K, N, row_lo, row_hi, dtype_enum(src), TSB_SUM, 0,
+                                    workspace.data_ptr(), ws_bytes, current_stream()),
+               "tsb_segment_csr_perm");
+  return partial;
+}
+
 torch::Tensor scatter_sum(torch::Tensor src, torch::Tensor index, int64_t dim,
                           std::optional<torch::Tensor> optional_out, std::optional<int64_t> dim_size) {
   return ScatterSumMean<false>::apply(src, index, dim, optional_out, dim_size)[0];
@@ -336,4 +384,6 @@ TORCH_LIBRARY_FRAGMENT(torch_scatter, m) {
   // not part of upstream's operator set: the index read-back its composites do with Tensor.gather
   m.def("gather_rows", &tsb_ops::gather_rows);
   m.def("scatter_sum_slice", &tsb_ops::scatter_sum_slice);
+  m.def("scatter_group", &tsb_ops::scatter_group);
+  m.def("segment_sum_perm", &tsb_ops::segment_sum_perm);
 }

@@ -140,20 +140,31 @@ def scatter_sum_overlapped(src_local: torch.Tensor, index_local: torch.Tensor, d
     it is reduce-scattered over the ranks on a side stream - all links busy, every rank receiving its share of
     the slice - while the next slice is accumulated.  Ownership is therefore interleaved: within every slice,
     rank ``r`` owns the ``r``-th run of ``sub`` rows (see :func:`overlapped_layout` / :func:`owned_rows`).
-    Returns this rank's ``passes * sub`` rows in accumulation precision (fp32 for 16-bit sources).
+    Returns this rank's ``passes * sub`` rows.  On CUDA the local accumulation is the atomics-free path (entry
+    ids grouped by target row once, every slice a row range of one segmented reduction through that permutation)
+    and partials travel in the source dtype; with an injected ``slice_reduce`` they are held in accumulation
+    precision (fp32 for 16-bit sources).
 
     ``slice_reduce(src, index, partial, row_lo, row_hi)`` fills the slice; it defaults to this package's
     ``scatter_sum_slice`` operator (CPU tests inject a reference).
     """
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     feat = tuple(src_local.shape[1:])
-    acc_dtype = torch.float32 if src_local.dtype in (torch.float16, torch.bfloat16) else src_local.dtype
+    grouped = slice_reduce is None and src_local.is_cuda and 0 < src_local.size(0) < (1 << 30)
+    acc_dtype = torch.float32 if src_local.dtype in (torch.float16, torch.bfloat16) and not grouped else src_local.dtype
     row_bytes = max(1, int(torch.tensor(feat).prod()) if feat else 1) * torch.empty((), dtype=acc_dtype).element_size()
     passes, sub = overlapped_layout(dim_size, world, row_bytes, pass_bytes)
     rows_per_pass = sub * world
     partial = torch.empty((passes * rows_per_pass,) + feat, dtype=acc_dtype, device=src_local.device)
     mine = torch.empty((passes * sub,) + feat, dtype=acc_dtype, device=src_local.device)
-    if slice_reduce is None:
+    if grouped:
+        # group this rank's entry ids by target row once, then every slice is a row range of one
+        # atomics-free segmented reduction through that permutation
+        rowptr, perm = torch.ops.torch_scatter.scatter_group(index_local, passes * rows_per_pass)
+
+        def slice_reduce(src, index, partial, row_lo, row_hi):
+            return torch.ops.torch_scatter.segment_sum_perm(src, rowptr, perm, partial, row_lo, row_hi)
+    elif slice_reduce is None:
         slice_reduce = torch.ops.torch_scatter.scatter_sum_slice
     on_gpu = src_local.is_cuda
     nccl = dist.get_backend(group) == 'nccl'

@@ -412,3 +412,44 @@ def test_scatter_sum_slice():
         before = partial.clone()
         torch.ops.torch_scatter.scatter_sum_slice(src.cuda(), index.cuda(), partial, 10, 20)
         assert torch.equal(partial[:10], before[:10]) and torch.equal(partial[20:], before[20:])
+
+
+@pytest.mark.parametrize('sort', ['buckets', 'atomic'])
+def test_scatter_group_and_permuted_row_slices(sort, chunk):
+    """The two halves of the atomics-free scatter as operators: one grouping, then the rows reduced slice by slice
+    (what the sharded scatter does between collectives); rows outside a call's slice stay untouched."""
+    import pytorch_scatter_b200  # noqa: F401  (registers the operators)
+    old = os.environ.get('TSB_SCATTER_GROUPED_SORT')
+    os.environ['TSB_SCATTER_GROUPED_SORT'] = sort
+    try:
+        gen = torch.Generator().manual_seed(56)
+        E, K, N = 20000, 16, 3000
+        index = torch.randint(0, N, (E,), generator=gen)
+        index[100:4100] = 777                      # a row spread over many chunks
+        index[::53] = N + 1                        # names no row
+        keep = (index >= 0) & (index < N)
+        rowptr, perm = torch.ops.torch_scatter.scatter_group(index.cuda(), N)
+        counts = torch.bincount(index[keep], minlength=N)
+        assert torch.equal(rowptr.cpu(), torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)]))
+        got_rows = index[perm[:int(rowptr[-1])].cpu().long()]
+        assert torch.equal(got_rows, torch.repeat_interleave(torch.arange(N), counts))   # grouped by row
+        assert torch.equal(perm[:int(rowptr[-1])].cpu().long().sort().values, torch.nonzero(keep).view(-1))
+        for dtype in (torch.float32, torch.bfloat16, torch.int64):
+            src = rand_src(gen, (E, K), dtype)
+            partial = torch.full((N, K), 7, dtype=dtype).cuda()
+            for lo, hi in ((0, 700), (700, 778), (778, 2999)):
+                torch.ops.torch_scatter.segment_sum_perm(src.cuda(), rowptr, perm, partial, lo, hi)
+            assert torch.all(partial[2999:] == 7)                                       # not in any slice
+            want = oracle.scatter(src[keep].view(1, -1, K), index[keep].view(1, -1, 1), N, 'sum')[0][0]
+            if dtype.is_floating_point:
+                want64 = oracle.scatter(src[keep].double().view(1, -1, K), index[keep].view(1, -1, 1), N, 'sum')[0][0]
+                mass64 = oracle.scatter(src[keep].double().abs().view(1, -1, K), index[keep].view(1, -1, 1), N, 'sum')[0][0]
+                assert_sum_close(partial[:2999], want64[:2999], mass64[:2999], what=f'segment_sum_perm {dtype}')
+            else:
+                assert_close(partial[:2999], want[:2999], what=f'segment_sum_perm {dtype}')
+    finally:
+        if old is None:
+            os.environ.pop('TSB_SCATTER_GROUPED_SORT', None)
+        else:
+            os.environ['TSB_SCATTER_GROUPED_SORT'] = old
+
