@@ -182,7 +182,7 @@ def run_reference(args):
 def run_ours(args):
     import torch.distributed as dist
     import pytorch_scatter_b200 as ts
-    from pytorch_scatter_b200.dist import scatter_sum_overlapped
+    from pytorch_scatter_b200.dist import routed_exchange_available, scatter_sum_overlapped, scatter_sum_routed
 
     world = int(os.environ.get('WORLD_SIZE', '1'))
     rank = int(os.environ.get('RANK', '0'))
@@ -207,12 +207,22 @@ def run_ours(args):
         # partial, then a reduce-scatter leaves each rank with its block of target rows.
         scatter_step(src, shuffled)
 
+    exchange = {'kind': None}   # how the sharded scatter exchanges rows; decided by the first call
+
     def scatter_step(s, ix):
-        # Unsorted scatter shards the edge dimension.  One GPU: the plain operator.  Several: every rank
-        # accumulates slice by slice into a full-length fp32 partial and each finished slice is reduced to
-        # the ranks that own its rows (NCCL, side stream) while the next slice is accumulated.
+        # Unsorted scatter shards the edge dimension.  One GPU: the plain operator.  Several: every rank reduces
+        # its edges for all rows through one grouping and the kernel stores each finished row into its owner's
+        # staging buffer over NVLink (peer stores), then the owners add the slabs.  If symmetric memory cannot be
+        # set up on this box, the per-slice NCCL reduce-scatter variant runs instead.
         if world == 1:
             return ts.scatter(s, ix, dim=0, dim_size=ROWS, reduce='sum')
+        if exchange['kind'] is None:   # decided once, by all ranks together
+            if routed_exchange_available(s, ROWS):
+                exchange['kind'] = 'peer stores from the reduction kernel (symmetric memory), owners add the slabs'
+            else:
+                exchange['kind'] = 'NCCL reduce-scatter per output slice, overlapped with the next slice'
+        if exchange['kind'].startswith('peer'):
+            return scatter_sum_routed(s, ix, ROWS)
         return scatter_sum_overlapped(s, ix, ROWS)
 
     def sync_all():
@@ -331,12 +341,12 @@ def run_ours(args):
             'config': {'workload': f'power-law CSR: {ROWS} rows, {nnz_all[0]} entries per GPU (log-normal row '
                                    f'lengths, mean 16, clip 20000, 8 rows forced to 20000), src fp32 [nnz x {FEAT}], '
                                    'int64 indptr/index; step = segment_csr(sum) + scatter(sum, shuffled index)'
-                                   + (' with each finished output slice reduced to its owner ranks (NCCL) while the next is accumulated' if world > 1 else ''),
+                                   + (f'; exchange: {exchange["kind"]}' if world > 1 else ''),
                        'l2': 'inputs (4.3 GB) larger than L2, no flush needed',
                        'parallelism': f'{world} x independent row shards (csr); edge shards + reduce-scatter (scatter)'},
             'ops': {'segment_csr_sum': {'ms': csr_ms, 'GB/s': csr_gbs, 'frac_of_peak': csr_gbs / peak},
                     'scatter_sum': {'ms': sc_ms, 'GB/s': sc_gbs, 'frac_of_peak': sc_gbs / peak},
-                    'collective': 'inside scatter_sum (overlapped per output slice)' if world > 1 else None},
+                    'collective': f'inside scatter_sum ({exchange["kind"]})' if world > 1 else None},
             'roofline': {'bound': 'hbm', 'kernel': 'csr_stream_kernel<float,sum,VEC=4>', 'achieved': csr_gbs, 'peak': peak,
                          'unit': 'GB/s', 'frac': csr_gbs / peak, 'traffic': CSR_KERNEL_DRAM_TRAFFIC_BYTES,
                          'peak_source': peak_src, 'algorithmic_bytes_per_launch': b[0][0]},
@@ -346,7 +356,7 @@ def run_ours(args):
             # than L2: the grouped path): bucket_hist, bucket_scan, bucket_partition, bucket_finalize, then
             # csr_stream_kernel + csr_fixup_kernel through the permutation.  Several GPUs: the probe plus, per
             # output slice, one range kernel and one runs kernel (the probe's flag makes one of them exit).
-            'gpu_launches': ((2 + 6) if world == 1 else (3 + 2 * scatter_passes)) * args.steps,
+            'gpu_launches': ((2 + 6) if world == 1 or exchange['kind'].startswith('peer') else (3 + 2 * scatter_passes)) * args.steps,
             'clocks': clocks,
         }
         if world == 1 and not args.no_cpu_baseline:

@@ -192,6 +192,17 @@ int tsb_segment_csr_perm(const void *src, const int64_t *rowptr, const int32_t *
                          int dtype, int reduce, int out_seeded,
                          void *workspace, size_t workspace_bytes, tsb_stream_t stream);
 
+/* tsb_segment_csr_perm for a scatter sharded over `world` <= 8 GPUs (SUM or MEAN of this rank's entries, write-only):
+ * GPU q owns the rows [q*rows_per_owner, (q+1)*rows_per_owner) and holds a staging buffer [world, rows_per_owner, K]
+ * at owner_base[q] (a HOST array of `world` device pointers, peers' memory included: anything this GPU may store
+ * to).  Every finished row n is stored into slab `rank` of its owner's buffer, so the partial rows cross NVLink as
+ * plain stores while the reduction is still running; once all ranks have finished (the caller's barrier), every
+ * owner adds its `world` slabs.  rows_per_owner * world >= N.  No counterpart upstream (its scatter is single-GPU). */
+int tsb_segment_csr_perm_routed(const void *src, const int64_t *rowptr, const int32_t *perm,
+                                void *const *owner_base, int world, int rank, int64_t rows_per_owner,
+                                int64_t E, int64_t K, int64_t N, int dtype, int reduce,
+                                void *workspace, size_t workspace_bytes, tsb_stream_t stream);
+
 /* One slice of an unsorted scatter SUM, for sharded use: adds the E edges of this call (src [E,K], 1-D index [E])
  * into the target rows [row_lo, row_hi) of `partial` [N,K], after zeroing exactly those rows; targets outside the
  * slice are ignored.  `partial` is held in accumulation precision: fp32 for fp32/fp16/bf16 sources, the source

@@ -29,6 +29,15 @@ struct CsrParams {
   // lie entirely before indptr[0] or after indptr[N] return at once instead of streaming entries that
   // belong to no row.  Single batch only.
   bool skip_outside = false;
+  // Optional routing of the finished rows to their owners (a sharded scatter over `route_world` GPUs,
+  // SUM/MEAN, single batch): row n belongs to GPU q = n / route_rows and is stored at
+  // route_base[q] + ((route_rank * route_rows + n % route_rows) * K) elements, i.e. into the slab this
+  // rank owns inside q's staging buffer [route_world, route_rows, K].  route_base[q] may be peer memory:
+  // the rows then cross NVLink as plain stores while the reduction is still running.  `out` is unused.
+  static constexpr int kMaxRoute = 8;
+  void *route_base[kMaxRoute] = {nullptr};
+  int route_world = 0, route_rank = 0;
+  int64_t route_rows = 0;
   int mode;
   void *workspace;        // csr_reduce_workspace_bytes(...) bytes, 256-byte aligned
   size_t workspace_bytes;

@@ -524,3 +524,30 @@ extern "C" int tsb_segment_csr_perm(const void *src, const int64_t *rowptr, cons
   return launch_csr_reduce(p, dtype, reduce, reinterpret_cast<cudaStream_t>(stream));
 }
 
+extern "C" int tsb_segment_csr_perm_routed(const void *src, const int64_t *rowptr, const int32_t *perm,
+                                           void *const *owner_base, int world, int rank, int64_t rows_per_owner,
+                                           int64_t E, int64_t K, int64_t N, int dtype, int reduce, void *workspace,
+                                           size_t workspace_bytes, tsb_stream_t stream) {
+  using namespace tsb;
+  if (E < 0 || K < 0 || N < 0 || owner_base == nullptr || world < 1 || world > CsrParams::kMaxRoute) return TSB_ERR_ARG;
+  if (K == 0 || N == 0) return TSB_OK;
+  if (rowptr == nullptr || (E > 0 && (src == nullptr || perm == nullptr))) return TSB_ERR_ARG;
+  CsrParams p;
+  p.src = src;
+  p.indptr = rowptr;
+  p.out = nullptr;
+  p.arg_out = nullptr;
+  p.count_out = nullptr;
+  p.B = 1; p.E = E; p.K = K; p.N = N;
+  p.bstride = 0;
+  p.perm = E > 0 ? perm : nullptr;
+  p.mode = kCooFresh;
+  for (int q = 0; q < world; ++q) p.route_base[q] = owner_base[q];
+  p.route_world = world;
+  p.route_rank = rank;
+  p.route_rows = rows_per_owner;
+  p.workspace = workspace;
+  p.workspace_bytes = workspace_bytes;
+  return launch_csr_reduce(p, dtype, reduce, reinterpret_cast<cudaStream_t>(stream));
+}
+

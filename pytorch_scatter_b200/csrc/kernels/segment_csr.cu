@@ -171,9 +171,18 @@ template <> struct MeanScale<int64_t> {
 };
 
 // Address of element `off` of the output: T everywhere except the LSE table, which is fp32.
-template <typename T, int REDUCE> __device__ __forceinline__ T *row_address(void *out, int64_t off) {
-  if constexpr (REDUCE == kLse) return reinterpret_cast<T *>(static_cast<float *>(out) + off);
-  else return static_cast<T *>(out) + off;
+template <typename T, int REDUCE>
+__device__ __forceinline__ T *row_address(const CsrParams &p, int64_t grow, int64_t col) {
+  if constexpr (REDUCE == kLse) {
+    return reinterpret_cast<T *>(static_cast<float *>(p.out) + grow * p.K + col);
+  } else {
+    if (p.route_world > 0) {  // sharded scatter: the row goes to its owner's staging buffer (maybe over NVLink)
+      const int64_t q = grow / p.route_rows;
+      const int64_t local = grow - q * p.route_rows;
+      return static_cast<T *>(p.route_base[q]) + ((int64_t)p.route_rank * p.route_rows + local) * p.K + col;
+    }
+    return static_cast<T *>(p.out) + grow * p.K + col;
+  }
 }
 
 // Writes one finished row (this lane's VEC columns of it).  `acc` is the reduction over the row's
@@ -350,7 +359,7 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
         } else {
           const int64_t grow = b * p.N + row;
           if (sub == 0 && col_ok) {
-            write_row<T, REDUCE, VEC, int>(tot, row_address<T, REDUCE>(p.out, grow * p.K + c * VEC),
+            write_row<T, REDUCE, VEC, int>(tot, row_address<T, REDUCE>(p, grow, c * VEC),
                                            kArg ? p.arg_out + grow * p.K + c * VEC : nullptr,
                                            (int64_t)(cur_end - cur_start), p.mode, p.E, INDIRECT ? 0 : cs, kRelInf);
           }
@@ -499,7 +508,7 @@ __global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeo
         if (Acc::kPair) oarg[i] = g.carry_arg[at + i];
       }
       acc.merge(oval, oarg);
-      write_row<T, REDUCE, VEC, int64_t>(acc, row_address<T, REDUCE>(p.out, grow * p.K + c * VEC),
+      write_row<T, REDUCE, VEC, int64_t>(acc, row_address<T, REDUCE>(p, grow, c * VEC),
                                          kArg ? p.arg_out + grow * p.K + c * VEC : nullptr, re - rs, p.mode, p.E,
                                          0, p.E);
     }
@@ -556,7 +565,8 @@ int launch_typed(const CsrParams &p, cudaStream_t stream) {
   g.carry_val = ws;
   g.carry_arg = reinterpret_cast<int64_t *>(ws + arg_off);
   g.head_row = reinterpret_cast<int64_t *>(ws + row_off);
-  const bool vec_ok = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.out);
+  bool vec_ok = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.out);
+  for (int q = 0; q < p.route_world; ++q) vec_ok = vec_ok && aligned16(p.route_base[q]);
   return vec_ok ? launch_vec<T, REDUCE, kFull>(p, g, stream) : launch_vec<T, REDUCE, 1>(p, g, stream);
 }
 
@@ -582,7 +592,15 @@ int launch_csr_reduce(const CsrParams &p, int dtype, int reduce, cudaStream_t st
   if (p.B < 0 || p.E < 0 || p.K < 0 || p.N < 0) return TSB_ERR_ARG;
   if (p.B * p.N * p.K == 0) return TSB_OK;
   if (p.src == nullptr && p.E > 0) return TSB_ERR_ARG;
-  if (p.indptr == nullptr || p.out == nullptr) return TSB_ERR_ARG;
+  if (p.indptr == nullptr || (p.out == nullptr && p.route_world == 0)) return TSB_ERR_ARG;
+  if (p.route_world != 0) {
+    if (p.route_world < 0 || p.route_world > CsrParams::kMaxRoute || p.route_rank < 0 || p.route_rank >= p.route_world ||
+        p.route_rows < 1 || p.route_rows * p.route_world < p.N || p.B != 1 || p.mode == kCooSeeded ||
+        (reduce != TSB_SUM && reduce != TSB_MEAN))
+      return TSB_ERR_ARG;
+    for (int q = 0; q < p.route_world; ++q)
+      if (p.route_base[q] == nullptr) return TSB_ERR_ARG;
+  }
   if ((reduce == TSB_MIN || reduce == TSB_MAX) && p.arg_out == nullptr) return TSB_ERR_ARG;
   if (p.perm != nullptr && p.E >= kRelInf) return TSB_ERR_TOO_LARGE;
   if (p.skip_outside && p.B != 1) return TSB_ERR_ARG;

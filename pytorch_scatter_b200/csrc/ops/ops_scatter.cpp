@@ -347,6 +347,34 @@ torch::Tensor segment_sum_perm(torch::Tensor src, torch::Tensor rowptr, torch::T
   return partial;
 }
 
+// The same reduction with every finished row stored straight into its owner's staging buffer
+// (owner_ptrs: device addresses of the `world` buffers [world, rows_per_owner, ...], peers included).
+void segment_sum_perm_routed(torch::Tensor src, torch::Tensor rowptr, torch::Tensor perm, std::vector<int64_t> owner_ptrs,
+                             int64_t rank, int64_t rows_per_owner, int64_t dim_size) {
+  TSB_CHECK_CUDA(src);
+  TSB_CHECK_CUDA(rowptr);
+  TSB_CHECK_CUDA(perm);
+  check_index_dtype(rowptr, "rowptr");
+  TORCH_CHECK(perm.scalar_type() == at::ScalarType::Int, "perm must be int32");
+  c10::cuda::CUDAGuard guard(src.device());
+  TSB_CHECK_INPUT(rowptr.dim() == 1 && perm.dim() == 1 && src.dim() >= 1 && src.size(0) == perm.size(0));
+  TSB_CHECK_INPUT(rowptr.is_contiguous() && perm.is_contiguous() && rowptr.size(0) == dim_size + 1);
+  const int world = (int)owner_ptrs.size();
+  TSB_CHECK_INPUT(world >= 1 && world <= 8 && rank >= 0 && rank < world && rows_per_owner * world >= dim_size);
+  src = src.contiguous();
+  const int64_t E = src.size(0);
+  int64_t K = 1;
+  for (int64_t i = 1; i < src.dim(); i++) K *= src.size(i);
+  std::vector<void *> bases(world);
+  for (int q = 0; q < world; ++q) bases[q] = reinterpret_cast<void *>(owner_ptrs[q]);
+  const size_t ws_bytes = tsb_segment_csr_perm_workspace_bytes(1, E, K, dim_size, dtype_enum(src), TSB_SUM);
+  auto workspace = torch::empty({(int64_t)ws_bytes}, src.options().dtype(torch::kUInt8));
+  check_status(tsb_segment_csr_perm_routed(src.data_ptr(), rowptr.data_ptr<int64_t>(), perm.data_ptr<int32_t>(),
+                                           bases.data(), world, (int)rank, rows_per_owner, E, K, dim_size, dtype_enum(src),
+                                           TSB_SUM, workspace.data_ptr(), ws_bytes, current_stream()),
+               "tsb_segment_csr_perm_routed");
+}
+
 torch::Tensor scatter_sum(torch::Tensor src, torch::Tensor index, int64_t dim,
                           std::optional<torch::Tensor> optional_out, std::optional<int64_t> dim_size) {
   return ScatterSumMean<false>::apply(src, index, dim, optional_out, dim_size)[0];
@@ -386,4 +414,5 @@ TORCH_LIBRARY_FRAGMENT(torch_scatter, m) {
   m.def("scatter_sum_slice", &tsb_ops::scatter_sum_slice);
   m.def("scatter_group", &tsb_ops::scatter_group);
   m.def("segment_sum_perm", &tsb_ops::segment_sum_perm);
+  m.def("segment_sum_perm_routed", &tsb_ops::segment_sum_perm_routed);
 }

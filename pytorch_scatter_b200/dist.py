@@ -192,6 +192,63 @@ def scatter_sum_overlapped(src_local: torch.Tensor, index_local: torch.Tensor, d
     return mine
 
 
+_ROUTED_STAGING = {}
+
+
+def _routed_staging(world: int, rows: int, feat: tuple, dtype: torch.dtype, device: torch.device, group):
+    """Symmetric staging buffer [world, rows, *feat] of this rank plus the device addresses of every rank's
+    buffer; allocated and exchanged once per shape (the rendezvous is a collective)."""
+    import os
+    import torch.distributed._symmetric_memory as symm_mem
+    # plain peer stores are all this path needs: keep the buffers off NVLink multicast objects
+    os.environ.setdefault('TORCH_SYMM_MEM_DISABLE_MULTICAST', '1')
+    key = (id(group), world, rows, feat, dtype, device.index)
+    if key not in _ROUTED_STAGING:
+        buf = symm_mem.empty((world, rows) + feat, dtype=dtype, device=device)
+        handle = symm_mem.rendezvous(buf, group if group is not None else dist.group.WORLD)
+        _ROUTED_STAGING[key] = (buf, handle, [int(p) for p in handle.buffer_ptrs])
+    return _ROUTED_STAGING[key]
+
+
+def routed_exchange_available(src_local: torch.Tensor, dim_size: int, group=None) -> bool:
+    """Sets up the staging buffers :func:`scatter_sum_routed` needs for this shape and says whether that worked on
+    EVERY rank (a collective: all ranks must call it).  False means: use :func:`scatter_sum_overlapped`."""
+    world = dist.get_world_size(group)
+    ok = 1
+    try:
+        _routed_staging(world, -(-dim_size // world), tuple(src_local.shape[1:]), src_local.dtype, src_local.device, group)
+    except Exception as exc:  # noqa: BLE001  (no symmetric memory on this box, whatever the reason)
+        print(f'[pytorch_scatter_b200.dist] routed exchange unavailable: {type(exc).__name__}: {exc}', flush=True)
+        ok = 0
+    flag = torch.tensor([ok], device=src_local.device, dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    return bool(flag.item())
+
+
+def scatter_sum_routed(src_local: torch.Tensor, index_local: torch.Tensor, dim_size: int, group=None) -> torch.Tensor:
+    """Edge-sharded ``scatter(sum)`` along dim 0 with the exchange fused into the reduction kernel.
+
+    Every rank groups its entry ids by target row and reduces all ``dim_size`` rows through that permutation in one
+    launch; the kernel stores each finished row straight into the staging buffer of the rank that owns it (peer
+    memory over NVLink, plain stores), so the transfer runs while the reduction is still going and no collective
+    kernel competes for SMs.  After a barrier every rank adds the ``world`` partial slabs it received.  Rank ``r``
+    owns the contiguous rows ``[r * rows, (r + 1) * rows)`` with ``rows = ceil(dim_size / world)`` and gets them
+    back (zero rows beyond ``dim_size``), in the source dtype.  CUDA + NCCL only.
+    """
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    feat = tuple(src_local.shape[1:])
+    rows = -(-dim_size // world)
+    buf, handle, ptrs = _routed_staging(world, rows, feat, src_local.dtype, src_local.device, group)
+    rowptr, perm = torch.ops.torch_scatter.scatter_group(index_local, dim_size)
+    # bounded waits: a rank that never arrives ends the call with an error instead of hanging the GPUs
+    handle.barrier(channel=0, timeout_ms=60000)   # nobody is still adding up the previous call's slabs
+    torch.ops.torch_scatter.segment_sum_perm_routed(src_local, rowptr, perm, ptrs, rank, rows, dim_size)
+    if rows * world > dim_size and rank == world - 1:   # rows past dim_size exist only as padding: nobody writes them
+        buf[:, dim_size - rank * rows:].zero_()
+    handle.barrier(channel=1, timeout_ms=60000)   # every rank's rows have landed
+    return buf.sum(dim=0)
+
+
 def _cuda_local_reduce(src, index, dim_size, reduce):
     from . import scatter_max, scatter_min, scatter_sum
     if reduce == 'sum':

@@ -453,3 +453,35 @@ def test_scatter_group_and_permuted_row_slices(sort, chunk):
         else:
             os.environ['TSB_SCATTER_GROUPED_SORT'] = old
 
+
+def test_routed_rows_two_ranks_emulated():
+    """The sharded scatter's fused exchange on one GPU: two "ranks" (two edge shards, run one after the other) store
+    their finished rows into the owners' staging buffers; adding each owner's slabs must give the full scatter."""
+    import pytorch_scatter_b200  # noqa: F401  (registers the operators)
+    gen = torch.Generator().manual_seed(57)
+    world, N, K = 2, 1001, 16
+    rows = -(-N // world)
+    for dtype in (torch.float32, torch.bfloat16, torch.int64):
+        staging = [torch.full((world, rows, K), 9, dtype=dtype).cuda() for _ in range(world)]   # owner q's buffer
+        ptrs = [t.data_ptr() for t in staging]
+        shards = []
+        for rank in range(world):
+            E = 7000 + 500 * rank
+            index = torch.randint(0, N, (E,), generator=gen)
+            index[:900] = 500 + rank                    # long rows on both sides of the ownership border
+            src = rand_src(gen, (E, K), dtype)
+            shards.append((src, index))
+            rowptr, perm = torch.ops.torch_scatter.scatter_group(index.cuda(), N)
+            torch.ops.torch_scatter.segment_sum_perm_routed(src.cuda(), rowptr, perm, ptrs, rank, rows, N)
+        got = torch.cat([buf.float().sum(0) if dtype == torch.bfloat16 else buf.sum(0) for buf in staging])[:N]
+        src_all = torch.cat([s for s, _ in shards])
+        index_all = torch.cat([i for _, i in shards])
+        if dtype.is_floating_point:
+            want64 = oracle.scatter(src_all.double().view(1, -1, K), index_all.view(1, -1, 1), N, 'sum')[0][0]
+            mass64 = oracle.scatter(src_all.double().abs().view(1, -1, K), index_all.view(1, -1, 1), N, 'sum')[0][0]
+            assert_sum_close(got.to(dtype), want64, mass64, what=f'routed {dtype}')
+        else:
+            want = oracle.scatter(src_all.view(1, -1, K), index_all.view(1, -1, 1), N, 'sum')[0][0]
+            assert_close(got, want, what=f'routed {dtype}')
+        assert torch.all(staging[1][:, N - rows:] == 9)   # the padding row past N is nobody's
+
