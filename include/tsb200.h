@@ -203,6 +203,10 @@ int tsb_segment_csr_perm_routed(const void *src, const int64_t *rowptr, const in
                                 int64_t E, int64_t K, int64_t N, int dtype, int reduce,
                                 void *workspace, size_t workspace_bytes, tsb_stream_t stream);
 
+/* The owner's last step of the routed scatter: out[i] = sum over q < world of slabs[q * elems + i] (accumulated in fp32
+ * for 16-bit dtypes), one streaming pass. */
+int tsb_sum_slabs(const void *slabs, void *out, int world, int64_t elems, int dtype, tsb_stream_t stream);
+
 /* One slice of an unsorted scatter SUM, for sharded use: adds the E edges of this call (src [E,K], 1-D index [E])
  * into the target rows [row_lo, row_hi) of `partial` [N,K], after zeroing exactly those rows; targets outside the
  * slice are ignored.  `partial` is held in accumulation precision: fp32 for fp32/fp16/bf16 sources, the source

@@ -475,6 +475,29 @@ int run_scatter_grouped(const void *src, const int64_t *index, void *out, int64_
 
 }  // namespace tsb
 
+namespace tsb {
+namespace {
+// out[i] = sum over q of slabs[q * elems + i], accumulated in acc_t<T> (fp32 for 16-bit), 16 bytes per thread.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kThreads) sum_slabs_kernel(const T *__restrict__ slabs, T *__restrict__ out, int world, int64_t elems) {
+  const int64_t i = ((int64_t)blockIdx.x * kThreads + threadIdx.x) * VEC;
+  if (i >= elems) return;
+  acc_t<T> acc[VEC];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) acc[k] = (acc_t<T>)0;
+  for (int q = 0; q < world; ++q) {
+    const Pack<T, VEC> v = ld_stream<T, VEC>(slabs + (int64_t)q * elems + i);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] += to_acc<T>(v.v[k]);
+  }
+  Pack<T, VEC> o;
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) o.v[k] = from_acc<T>(acc[k]);
+  st_stream<T, VEC>(out + i, o);
+}
+}  // namespace
+}  // namespace tsb
+
 extern "C" size_t tsb_scatter_group_workspace_bytes(int64_t E, int64_t N) { return tsb::scatter_group_workspace_bytes(E, N); }
 
 extern "C" int tsb_scatter_group(const int64_t *index, int64_t E, int64_t N, int64_t *rowptr, int32_t *perm,
@@ -549,5 +572,23 @@ extern "C" int tsb_segment_csr_perm_routed(const void *src, const int64_t *rowpt
   p.workspace = workspace;
   p.workspace_bytes = workspace_bytes;
   return launch_csr_reduce(p, dtype, reduce, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tsb_sum_slabs(const void *slabs, void *out, int world, int64_t elems, int dtype, tsb_stream_t stream) {
+  using namespace tsb;
+  if (world < 1 || elems < 0) return TSB_ERR_ARG;
+  if (elems == 0) return TSB_OK;
+  if (slabs == nullptr || out == nullptr) return TSB_ERR_ARG;
+  return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
+    constexpr int kFull = full_vec<scalar_t>();
+    const bool vec_ok = elems % kFull == 0 && aligned16(slabs) && aligned16(out);
+    const int64_t threads = vec_ok ? elems / kFull : elems;
+    const int64_t blocks = (threads + kThreads - 1) / kThreads;
+    if (blocks > 2147483647LL) return TSB_ERR_TOO_LARGE;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (vec_ok) sum_slabs_kernel<scalar_t, kFull><<<(unsigned)blocks, kThreads, 0, st>>>(static_cast<const scalar_t *>(slabs), static_cast<scalar_t *>(out), world, elems);
+    else sum_slabs_kernel<scalar_t, 1><<<(unsigned)blocks, kThreads, 0, st>>>(static_cast<const scalar_t *>(slabs), static_cast<scalar_t *>(out), world, elems);
+    return launch_status();
+  });
 }
 

@@ -262,7 +262,15 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
   const int eps = 32 >> g.l_log2;
   const int64_t Kv = p.K / VEC;
 
-  const int64_t chunk_id = blockIdx.x;
+  int64_t chunk_id = blockIdx.x;
+  if (p.route_world > 1) {
+    // Routed rows: chunks are scheduled roughly in order, so without a rotation every rank would store to owner 0
+    // first, then to owner 1, ... and world-1 senders would share one GPU's NVLink ingress at any time.  Rank r
+    // starts with the chunks that hold the rows of owner r+1: at any moment the ranks target distinct owners.
+    int64_t first_row = (int64_t)((p.route_rank + 1) % p.route_world) * p.route_rows;
+    if (first_row > p.N) first_row = p.N;
+    chunk_id = (chunk_id + clamp64(p.indptr[first_row], 0, p.E) / g.chunk_entries) % g.chunks;  // single batch
+  }
   const int64_t b = chunk_id / g.chunks;
   const int64_t w = chunk_id - b * g.chunks;
   const int64_t cs = w * g.chunk_entries;

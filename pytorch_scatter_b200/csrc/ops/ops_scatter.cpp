@@ -375,6 +375,18 @@ void segment_sum_perm_routed(torch::Tensor src, torch::Tensor rowptr, torch::Ten
                "tsb_segment_csr_perm_routed");
 }
 
+// slabs [world, ...] -> their sum over dim 0 (the owner's last step of the routed scatter)
+torch::Tensor sum_slabs(torch::Tensor slabs) {
+  TSB_CHECK_CUDA(slabs);
+  TSB_CHECK_INPUT(slabs.dim() >= 1 && slabs.is_contiguous());
+  c10::cuda::CUDAGuard guard(slabs.device());
+  auto out = torch::empty(slabs.sizes().slice(1), slabs.options());
+  check_status(tsb_sum_slabs(slabs.data_ptr(), out.data_ptr(), (int)slabs.size(0), out.numel(), dtype_enum(slabs),
+                             current_stream()),
+               "tsb_sum_slabs");
+  return out;
+}
+
 torch::Tensor scatter_sum(torch::Tensor src, torch::Tensor index, int64_t dim,
                           std::optional<torch::Tensor> optional_out, std::optional<int64_t> dim_size) {
   return ScatterSumMean<false>::apply(src, index, dim, optional_out, dim_size)[0];
@@ -415,4 +427,5 @@ TORCH_LIBRARY_FRAGMENT(torch_scatter, m) {
   m.def("scatter_group", &tsb_ops::scatter_group);
   m.def("segment_sum_perm", &tsb_ops::segment_sum_perm);
   m.def("segment_sum_perm_routed", &tsb_ops::segment_sum_perm_routed);
+  m.def("sum_slabs", &tsb_ops::sum_slabs);
 }

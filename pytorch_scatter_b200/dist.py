@@ -246,7 +246,7 @@ def scatter_sum_routed(src_local: torch.Tensor, index_local: torch.Tensor, dim_s
     if rows * world > dim_size and rank == world - 1:   # rows past dim_size exist only as padding: nobody writes them
         buf[:, dim_size - rank * rows:].zero_()
     handle.barrier(channel=1, timeout_ms=60000)   # every rank's rows have landed
-    return buf.sum(dim=0)
+    return torch.ops.torch_scatter.sum_slabs(buf)
 
 
 def _cuda_local_reduce(src, index, dim_size, reduce):
