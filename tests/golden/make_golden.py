@@ -1,7 +1,6 @@
 """Generates the golden fixtures in this directory from the upstream project itself.
 
-Runs only where a checkout of rusty1s/pytorch_scatter is available (``--ref``, default
-``/root/reference``) and its CPU operator libraries have been built by ``make -C oracle ref`` into
+Runs only where a checkout of rusty1s/pytorch_scatter is available (``--ref``) and its CPU operator libraries have been built by ``make -C oracle ref`` into
 ``oracle/_ref/``.  It assembles the upstream Python package in a temporary directory (symlinks to the
 checkout's ``torch_scatter/*.py`` plus the built ``_*_cpu.so``), imports it, and records
 
