@@ -171,12 +171,12 @@ template <> struct MeanScale<int64_t> {
 };
 
 // Address of element `off` of the output: T everywhere except the LSE table, which is fp32.
-template <typename T, int REDUCE>
+template <typename T, int REDUCE, bool EXTRAS>
 __device__ __forceinline__ T *row_address(const CsrParams &p, int64_t grow, int64_t col) {
   if constexpr (REDUCE == kLse) {
     return reinterpret_cast<T *>(static_cast<float *>(p.out) + grow * p.K + col);
   } else {
-    if (p.route_world > 0) {  // sharded scatter: the row goes to its owner's staging buffer (maybe over NVLink)
+    if (EXTRAS && p.route_world > 0) {  // sharded scatter: the row goes to its owner's staging buffer (maybe over NVLink)
       const int64_t q = grow / p.route_rows;
       const int64_t local = grow - q * p.route_rows;
       return static_cast<T *>(p.route_base[q]) + ((int64_t)p.route_rank * p.route_rows + local) * p.K + col;
@@ -248,8 +248,19 @@ __device__ __forceinline__ void write_row(const RowAcc<T, REDUCE, VEC, ArgT> &ac
 }
 
 // Streaming kernel: blockIdx.x = (batch, chunk); one warp.
-template <typename T, int REDUCE, int VEC, bool INDIRECT>
-__global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams p, CsrGeom g) {
+// 16-bit MIN/MAX carry eight fp32 values and eight arg indices per lane: under the 80-register cap they spill, so
+// those variants trade resident warps for registers (16 CTAs = 128 KiB in flight per SM still covers the latency).
+template <typename T, int REDUCE, int VEC> constexpr int stream_ctas_per_sm() {
+  return (sizeof(T) == 2 && VEC > 1 && (REDUCE == kMin || REDUCE == kMax)) ? 16 : kMinCtasPerSm;
+}
+
+// MODE 0: contiguous source.  1: source through CsrParams::perm.  2: perm plus the sharded-scatter features (row
+// slices, rows routed to their owners).  The features are compiled out of the other modes: as run-time branches
+// they cost every variant registers (all of them spilled) and the 16-bit and MIN/MAX variants up to 60 % of their speed.
+template <typename T, int REDUCE, int VEC, int MODE>
+__global__ void __launch_bounds__(32, stream_ctas_per_sm<T, REDUCE, VEC>()) csr_stream_kernel(CsrParams p, CsrGeom g) {
+  constexpr bool INDIRECT = MODE >= 1;
+  constexpr bool EXTRAS = MODE == 2;
   using A = acc_t<T>;
   using Acc = RowAcc<T, REDUCE, VEC, int>;  // arg indices relative to the chunk start inside the stream
   constexpr bool kArg = Acc::kArg;
@@ -263,7 +274,7 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
   const int64_t Kv = p.K / VEC;
 
   int64_t chunk_id = blockIdx.x;
-  if (p.route_world > 1) {
+  if (EXTRAS && p.route_world > 1) {
     // Routed rows: chunks are scheduled roughly in order, so without a rotation every rank would store to owner 0
     // first, then to owner 1, ... and world-1 senders would share one GPU's NVLink ingress at any time.  Rank r
     // starts with the chunks that hold the rows of owner r+1: at any moment the ranks target distinct owners.
@@ -277,7 +288,7 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
   const int64_t ce = (cs + g.chunk_entries < p.E) ? cs + g.chunk_entries : p.E;
   const int t = (int)(ce - cs);
   const int64_t *ip = p.indptr + b * p.bstride;
-  if (p.skip_outside && (ce <= ip[0] || cs >= ip[p.N])) {  // warp-uniform
+  if (EXTRAS && p.skip_outside && (ce <= ip[0] || cs >= ip[p.N])) {  // warp-uniform
     if (lane == 0) g.head_row[chunk_id] = -1;
     return;
   }
@@ -367,7 +378,7 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
         } else {
           const int64_t grow = b * p.N + row;
           if (sub == 0 && col_ok) {
-            write_row<T, REDUCE, VEC, int>(tot, row_address<T, REDUCE>(p, grow, c * VEC),
+            write_row<T, REDUCE, VEC, int>(tot, row_address<T, REDUCE, EXTRAS>(p, grow, c * VEC),
                                            kArg ? p.arg_out + grow * p.K + c * VEC : nullptr,
                                            (int64_t)(cur_end - cur_start), p.mode, p.E, INDIRECT ? 0 : cs, kRelInf);
           }
@@ -463,7 +474,7 @@ __global__ void __launch_bounds__(32, kMinCtasPerSm) csr_stream_kernel(CsrParams
 // Fix-up kernel: one warp per chunk.  If the chunk closed a row that began in an earlier chunk,
 // fold the TAIL partials of the chunks the row ran through and this chunk's HEAD partial, in a
 // fixed order, and write the row.
-template <typename T, int REDUCE, int VEC>
+template <typename T, int REDUCE, int VEC, bool EXTRAS>
 __global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeom g) {
   using A = acc_t<T>;
   using Acc = RowAcc<T, REDUCE, VEC>;
@@ -516,7 +527,7 @@ __global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeo
         if (Acc::kPair) oarg[i] = g.carry_arg[at + i];
       }
       acc.merge(oval, oarg);
-      write_row<T, REDUCE, VEC, int64_t>(acc, row_address<T, REDUCE>(p, grow, c * VEC),
+      write_row<T, REDUCE, VEC, int64_t>(acc, row_address<T, REDUCE, EXTRAS>(p, grow, c * VEC),
                                          kArg ? p.arg_out + grow * p.K + c * VEC : nullptr, re - rs, p.mode, p.E,
                                          0, p.E);
     }
@@ -542,15 +553,23 @@ int launch_vec(const CsrParams &p, CsrGeom g, cudaStream_t stream) {
   g.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
   const int64_t total_chunks = p.B * g.chunks;
   if (total_chunks > 2147483647LL) return TSB_ERR_TOO_LARGE;
-  if (p.perm != nullptr) {
-    if constexpr (REDUCE == kLse) return TSB_ERR_REDUCE;
-    else csr_stream_kernel<T, REDUCE, VEC, true><<<(unsigned)total_chunks, 32, 0, stream>>>(p, g);
+  const bool extras = p.skip_outside || p.route_world > 0;
+  const int64_t blocks = (total_chunks + (kThreads / 32) - 1) / (kThreads / 32);
+  if (p.perm != nullptr || extras) {
+    if constexpr (REDUCE == kLse) {
+      return TSB_ERR_REDUCE;
+    } else {
+      if (p.perm == nullptr && p.E > 0) return TSB_ERR_ARG;  // the sharded-scatter features come with a permutation
+      if (extras) csr_stream_kernel<T, REDUCE, VEC, 2><<<(unsigned)total_chunks, 32, 0, stream>>>(p, g);
+      else csr_stream_kernel<T, REDUCE, VEC, 1><<<(unsigned)total_chunks, 32, 0, stream>>>(p, g);
+      if (g.chunks > 1) {  // a single chunk per batch cannot split a row
+        if (extras) csr_fixup_kernel<T, REDUCE, VEC, true><<<(unsigned)blocks, kThreads, 0, stream>>>(p, g);
+        else csr_fixup_kernel<T, REDUCE, VEC, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, g);
+      }
+    }
   } else {
-    csr_stream_kernel<T, REDUCE, VEC, false><<<(unsigned)total_chunks, 32, 0, stream>>>(p, g);
-  }
-  if (g.chunks > 1) {  // a single chunk per batch cannot split a row
-    const int64_t blocks = (total_chunks + (kThreads / 32) - 1) / (kThreads / 32);
-    csr_fixup_kernel<T, REDUCE, VEC><<<(unsigned)blocks, kThreads, 0, stream>>>(p, g);
+    csr_stream_kernel<T, REDUCE, VEC, 0><<<(unsigned)total_chunks, 32, 0, stream>>>(p, g);
+    if (g.chunks > 1) csr_fixup_kernel<T, REDUCE, VEC, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, g);
   }
   return launch_status();
 }
