@@ -69,7 +69,10 @@ template <typename T, int REDUCE> __host__ __device__ __forceinline__ acc_t<T> r
   if (REDUCE == kMin) return (acc_t<T>)Limits<T>::max();
   if (REDUCE == kMax) return (acc_t<T>)Limits<T>::lowest();
   if (REDUCE == kMul) return (acc_t<T>)1;
-  if (REDUCE == kLse) return (acc_t<T>)(-3.402823466e+38f);  // running maximum of the online log-sum-exp
+  if (REDUCE == kLse) {  // running maximum of the online log-sum-exp (floating accumulators only)
+    if constexpr (std::is_floating_point<acc_t<T>>::value) return (acc_t<T>)(-3.402823466e+38f);
+    else return (acc_t<T>)0;
+  }
   return (acc_t<T>)0;
 }
 

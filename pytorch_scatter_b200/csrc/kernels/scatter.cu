@@ -152,48 +152,68 @@ struct ScatterParams {
   int l_log2;
   int fresh;
   int replicas;        // copies of the output the updates are spread over (1: none)
-  const int *clustered;  // device flag written by scatter_probe_kernel: 1 = neighbouring entries share targets
+  const int *clustered;  // device flags written by scatter_probe_kernel: [0] 1 = neighbouring entries share targets,
+                         // [1] 1 = entries far apart often share targets (a skewed index)
+  int use_skew;          // the cached kernel was launched next to the direct one: flag [1] picks between them
 };
 
 // One CTA looks at four windows of 256 consecutive index entries and counts neighbours that name the
 // same target.  An index where that is common (an edge list sorted or clustered by destination) is
 // handed to the run-combining kernel, any other to the direct kernels; the verdict is a device-side
 // flag, so choosing the variant costs no host synchronisation.
-__global__ void __launch_bounds__(kThreads) scatter_probe_kernel(ScatterParams p, int *clustered, int forced) {
-  if (forced >= 0) {  // test hook: the caller dictates the verdict
-    if (threadIdx.x == 0) *clustered = forced;
-    return;
-  }
-  __shared__ int s_equal, s_pairs;
-  if (threadIdx.x == 0) { s_equal = 0; s_pairs = 0; }
+__global__ void __launch_bounds__(kThreads) scatter_probe_kernel(ScatterParams p, int *clustered, int forced, int forced_skew) {
+  __shared__ int s_equal, s_pairs, s_far_equal, s_far_pairs;
+  if (threadIdx.x == 0) { s_equal = 0; s_pairs = 0; s_far_equal = 0; s_far_pairs = 0; }
   __syncthreads();
   const int64_t M = p.B * p.E;
-  // four windows of 256 neighbouring pairs; all eight loads of a thread are independent
-  int64_t x[4], y[4];
-  bool ok[4];
+  // four windows of 256 neighbouring pairs, and for each first entry a partner 1021 entries further on;
+  // all twelve loads of a thread are independent
+  int64_t x[4], y[4], z[4];
+  bool ok[4], far_ok[4];
 #pragma unroll
   for (int w = 0; w < 4; ++w) {
     const int64_t i = (M / 4) * w + threadIdx.x;
     ok[w] = i + 1 < M;
+    far_ok[w] = i + 1021 < M;
+    x[w] = y[w] = z[w] = 0;
     if (ok[w]) {
       const int64_t b0 = (p.B == 1) ? 0 : i / p.E, b1 = (p.B == 1) ? 0 : (i + 1) / p.E;
       x[w] = p.index[b0 * p.sb + (i - b0 * p.E) * p.se];
       y[w] = p.index[b1 * p.sb + (i + 1 - b1 * p.E) * p.se];
       ok[w] = b0 == b1;
+      if (far_ok[w]) {
+        const int64_t b2 = (p.B == 1) ? 0 : (i + 1021) / p.E;
+        z[w] = p.index[b2 * p.sb + (i + 1021 - b2 * p.E) * p.se];
+        far_ok[w] = b0 == b2;
+      }
+    } else {
+      far_ok[w] = false;
     }
   }
-  int equal = 0, pairs = 0;
+  int equal = 0, pairs = 0, far_equal = 0, far_pairs = 0;
 #pragma unroll
   for (int w = 0; w < 4; ++w) {
     if (ok[w]) {
       pairs += 1;
       equal += (x[w] == y[w]) ? 1 : 0;
     }
+    if (far_ok[w]) {
+      far_pairs += 1;
+      far_equal += (x[w] == z[w]) ? 1 : 0;
+    }
   }
   atomicAdd(&s_equal, equal);
   atomicAdd(&s_pairs, pairs);
+  atomicAdd(&s_far_equal, far_equal);
+  atomicAdd(&s_far_pairs, far_pairs);
   __syncthreads();
-  if (threadIdx.x == 0) *clustered = (s_pairs > 0 && s_equal * 8 >= s_pairs) ? 1 : 0;
+  if (threadIdx.x == 0) {
+    // test hooks: the caller may dictate either verdict
+    clustered[0] = forced >= 0 ? forced : ((s_pairs > 0 && s_equal * 8 >= s_pairs) ? 1 : 0);
+    // two entries far apart name the same row with probability sum p_k^2: about 5 % for Zipf(1.2) over 100,000 rows,
+    // 0.0015 % for a uniform index over 65,536; the cache pays from about 1 %
+    clustered[1] = forced_skew >= 0 ? forced_skew : ((s_far_pairs >= 64 && s_far_equal * 100 >= s_far_pairs) ? 1 : 0);
+  }
 }
 
 // ---- direct row kernels: one update per entry ---------------------------------------------------
@@ -206,7 +226,8 @@ template <typename T, int OP, int VEC>
 __global__ void __launch_bounds__(kThreads) scatter_rows_direct_kernel(ScatterParams p) {
   using U = acc_t<T>;
   const T *__restrict__ src = static_cast<const T *>(p.src);
-  if (*p.clustered != 0) return;  // the run-combining kernel takes clustered indices
+  if (p.clustered[0] != 0) return;                       // the run-combining kernel takes clustered indices
+  if (p.use_skew != 0 && p.clustered[1] != 0) return;    // the cached kernel takes skewed ones
   U *target = static_cast<U *>(p.target);
   if (p.replicas > 1) target += (blockIdx.x % p.replicas) * (p.B * p.N * p.K);
   const int L = 1 << p.l_log2;
@@ -222,6 +243,107 @@ __global__ void __launch_bounds__(kThreads) scatter_rows_direct_kernel(ScatterPa
   for (int64_t c = col; c < Kv; c += L) apply_pack<OP, T, VEC>(trow + c * VEC, ld_stream<T, VEC>(srow + c * VEC));
   // one count per row of the index itself: a batch-broadcast index is counted for b == 0 only
   if (p.count != nullptr && col == 0 && (p.sb != 0 || b == 0)) atomicAdd(p.count + (p.sb ? b : 0) * p.N + idx, 1);
+}
+
+// Small, contended outputs under a skewed index (a few rows take most of the entries): what bounds the direct kernel
+// is same-address atomic throughput in L2.  Here a CTA accumulates a tile of entries through a direct-mapped cache of
+// `slots` rows in shared memory: the first row that hashes to a free slot claims it (hot rows come early and often, so
+// they get theirs), later entries of that row are added with shared-memory atomics, all other entries go to global
+// memory as before; at the end every claimed slot is flushed with one global update per element.  The cache is used
+// when the probe's second flag says the index is skewed (duplicates among sampled, non-adjacent entries), otherwise
+// the kernel sends every entry to global memory like the direct kernel; fp32 accumulation, SUM only.  (A variant that
+// reserved a slot on the first sighting and cached only from the second on, to spare rows seen once the flush, was
+// slower on both the skewed and the uniform case.)
+constexpr int kCacheBytesMax = 96 * 1024;
+
+template <typename T, int VEC, bool USE_CACHE>
+__device__ __forceinline__ void cached_tile(const ScatterParams &p, int tile_entries, int slots_log2, float *s_val,
+                                            int *s_tag, int *s_cnt) {
+  using U = acc_t<T>;
+  const int slots = 1 << slots_log2;
+  const T *__restrict__ src = static_cast<const T *>(p.src);
+  U *target = static_cast<U *>(p.target);
+  if (p.replicas > 1) target += (blockIdx.x % p.replicas) * (p.B * p.N * p.K);
+  if (USE_CACHE) {
+    for (int i = threadIdx.x; i < slots * (int)p.K; i += kThreads) s_val[i] = 0.0f;
+    for (int i = threadIdx.x; i < slots; i += kThreads) { s_tag[i] = -1; s_cnt[i] = 0; }
+    __syncthreads();
+  }
+  const int L = 1 << p.l_log2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = lane & (L - 1);
+  const int sub = lane >> p.l_log2;
+  const int eps = 32 >> p.l_log2;
+  const int64_t Kv = p.K / VEC;
+  const int64_t M = p.B * p.E;
+  const int64_t tile0 = (int64_t)blockIdx.x * tile_entries;
+  const int per_round = (kThreads / 32) * eps;
+  for (int it = 0; it < tile_entries; it += per_round) {  // CTA-uniform trip count: the shuffle below needs every lane
+    const int64_t entry = tile0 + it + warp * eps + sub;
+    const bool in_tile = it + warp * eps + sub < tile_entries && entry < M;
+    int64_t grow = -1;
+    int64_t b = 0;
+    if (in_tile) {
+      b = entry / p.E;
+      const int64_t idx = p.index[b * p.sb + (entry - b * p.E) * p.se];
+      if (idx >= 0 && idx < p.N) grow = b * p.N + idx;
+    }
+    const bool valid = grow >= 0;
+    bool hit = false;
+    int slot = 0;
+    if (USE_CACHE) {
+      slot = valid ? (int)(((unsigned)grow * 2654435761u) >> (32 - slots_log2)) : 0;
+      int seen = valid ? *reinterpret_cast<volatile int *>(s_tag + slot) : -2;
+      const bool claim = valid && seen == -1;
+      if (claim && col == 0) seen = atomicCAS(s_tag + slot, -1, (int)grow);
+      seen = __shfl_sync(kFullMask, seen, lane - col);  // the lane group's first lane decides for the group
+      hit = valid && (seen == (int)grow || (claim && seen == -1));
+    }
+    if (!valid) continue;
+    const T *srow = src + entry * p.K;
+    if (USE_CACHE && hit) {
+      float *crow = s_val + (size_t)slot * p.K;
+      for (int64_t c = col; c < Kv; c += L) {
+        const Pack<T, VEC> v = ld_stream<T, VEC>(srow + c * VEC);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) atomicAdd(crow + c * VEC + i, to_acc<T>(v.v[i]));
+      }
+      if (p.count != nullptr && col == 0 && (p.sb != 0 || b == 0)) atomicAdd(s_cnt + slot, 1);
+    } else {
+      U *trow = target + grow * p.K;
+      for (int64_t c = col; c < Kv; c += L) apply_pack<kSum, T, VEC>(trow + c * VEC, ld_stream<T, VEC>(srow + c * VEC));
+      if (p.count != nullptr && col == 0 && (p.sb != 0 || b == 0))
+        atomicAdd(p.count + (p.sb ? b : 0) * p.N + (grow - b * p.N), 1);
+    }
+  }
+  if (!USE_CACHE) return;
+  __syncthreads();
+  // flush: one warp per claimed slot at a time
+  for (int slot = warp; slot < slots; slot += kThreads / 32) {
+    const int grow = s_tag[slot];
+    if (grow < 0) continue;  // warp-uniform
+    const float *crow = s_val + (size_t)slot * p.K;
+    U *trow = target + (int64_t)grow * p.K;
+    for (int k = lane; k < (int)p.K; k += 32) atom_add(trow + k, crow[k]);
+    if (p.count != nullptr && lane == 0 && s_cnt[slot] != 0) {
+      const int64_t b = grow / p.N;
+      atomicAdd(p.count + (p.sb ? b : 0) * p.N + (grow - b * p.N), s_cnt[slot]);
+    }
+  }
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kThreads) scatter_rows_cached_kernel(ScatterParams p, int tile_entries, int slots_log2) {
+  static_assert(std::is_same<acc_t<T>, float>::value, "fp32 accumulation only");
+  extern __shared__ float s_cache[];
+  const int slots = 1 << slots_log2;
+  float *s_val = s_cache;                                         // [slots][K]
+  int *s_tag = reinterpret_cast<int *>(s_cache + (size_t)slots * p.K);  // [slots] target row over all batches, -1: free
+  int *s_cnt = s_tag + slots;                                     // [slots] entries seen (MEAN's count)
+  if (p.clustered[0] != 0) return;  // clustered: the run-combining kernel
+  // skewed: through the cache; otherwise every entry goes straight to global memory (CTA-uniform choice)
+  if (p.clustered[1] != 0) cached_tile<T, VEC, true>(p, tile_entries, slots_log2, s_val, s_tag, s_cnt);
+  else cached_tile<T, VEC, false>(p, tile_entries, slots_log2, s_val, s_tag, s_cnt);
 }
 
 constexpr int kRangeBatches = 4;  // 32-entry batches per group: a group is 128 consecutive entries
@@ -883,7 +1005,10 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
       // run-combining kernel are both launched and the one the flag does not select exits at once.
       const char *force_env = std::getenv("TSB_SCATTER_CLUSTERED");  // test hook: "0" / "1"
       const int forced = (force_env != nullptr && (*force_env == '0' || *force_env == '1')) ? (*force_env - '0') : -1;
-      scatter_probe_kernel<<<1, kThreads, 0, stream>>>(p, flag, forced);
+      const char *cache_env = std::getenv("TSB_SCATTER_CACHED");  // test / tuning hook: "0" / "1" dictate the skew verdict
+      const int forced_skew = (cache_env != nullptr && (*cache_env == '0' || *cache_env == '1')) ? (*cache_env - '0') : -1;
+      scatter_probe_kernel<<<1, kThreads, 0, stream>>>(p, flag, forced, forced_skew);
+      p.use_skew = 0;
       unsigned blocks_direct = 0, blocks_batched = 0, blocks_range = 0;
       if (!grid_for((p.B * p.E + kRangeBatches * kRangeGroups - 1) / (kRangeBatches * kRangeGroups), &blocks_range)) return TSB_ERR_TOO_LARGE;  // 1024 entries per warp
       if (!grid_for((p.B * p.E) << p.l_log2, &blocks_direct)) return TSB_ERR_TOO_LARGE;                    // L lanes per entry
@@ -896,7 +1021,38 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
         if (zero_slices && cudaMemsetAsync(static_cast<U *>(p.target) + lo * p.K, 0,
                                            (size_t)((hi - lo) * p.K) * sizeof(U), stream) != cudaSuccess)
           return TSB_ERR_LAUNCH;
-        if (vec_ok) {
+        bool cached = false;
+        if constexpr (OP == kSum && std::is_same<U, float>::value) {
+          // small, replicated (= possibly contended) output with short rows: accumulate through the shared-memory cache
+          const bool want = forced_skew == 1 || (forced_skew != 0 && replicas > 1);
+          const int64_t row_bytes = p.K * (int64_t)sizeof(float);
+          if (want && vec_ok && !sliced && row_bytes <= 256 && all_rows < (1ll << 31)) {
+            int64_t tile = (p.B * p.E) / (148 * 8);
+            const int64_t tile_max = env_bytes("TSB_SCATTER_CACHE_TILE", 8192);  // tuning hooks
+            tile = tile < 1024 ? 1024 : (tile > tile_max ? tile_max : tile);
+            int64_t cache_bytes = env_bytes("TSB_SCATTER_CACHE_BYTES", 32 * 1024);
+            if (cache_bytes > kCacheBytesMax) cache_bytes = kCacheBytesMax;
+            int slots_log2 = 0;
+            while ((2ll << slots_log2) * (row_bytes + 8) <= cache_bytes && (2ll << slots_log2) <= tile / 4) ++slots_log2;
+            const int64_t tiles = (p.B * p.E + tile - 1) / tile;
+            if (tiles <= 2147483647LL && slots_log2 >= 4) {
+              const size_t smem = ((size_t)1 << slots_log2) * (size_t)(row_bytes + 8);
+              static bool allowed[64] = {false};
+              int dev = 0;
+              if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !allowed[dev]) {
+                if (cudaFuncSetAttribute(scatter_rows_cached_kernel<T, kFull>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kCacheBytesMax) != cudaSuccess)
+                  return TSB_ERR_LAUNCH;
+                allowed[dev] = true;
+              }
+              scatter_rows_cached_kernel<T, kFull><<<(unsigned)tiles, kThreads, smem, stream>>>(p, (int)tile, slots_log2);
+              cached = true;
+            }
+          }
+        }
+        if (cached) {  // it covers the skewed and the plain case; clustered indices still go to the runs kernel
+          scatter_rows_runs_kernel<T, OP, kFull><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi, replicas);
+        } else if (vec_ok) {
           if (sliced) scatter_rows_range_kernel<T, OP, kFull><<<blocks_range, kThreads, 0, stream>>>(p, lo, hi);
           else scatter_rows_direct_kernel<T, OP, kFull><<<blocks_direct, kThreads, 0, stream>>>(p);
           scatter_rows_runs_kernel<T, OP, kFull><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi, replicas);
@@ -1029,6 +1185,7 @@ extern "C" int tsb_scatter(const void *src, const int64_t *index, void *out, int
   p.fresh = out_seeded ? 0 : 1;
   p.replicas = 1;
   p.clustered = nullptr;
+  p.use_skew = 0;
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
     switch (reduce) {
       case TSB_SUM:
@@ -1061,7 +1218,7 @@ int run_scatter_sum_slice(ScatterParams p, int64_t row_lo, int64_t row_hi, int *
   unsigned blocks = 0, blocks_range = 0;
   if (!grid_for((p.E + kBatches - 1) / kBatches, &blocks)) return TSB_ERR_TOO_LARGE;
   if (!grid_for((p.E + kRangeBatches * kRangeGroups - 1) / (kRangeBatches * kRangeGroups), &blocks_range)) return TSB_ERR_TOO_LARGE;
-  scatter_probe_kernel<<<1, kThreads, 0, stream>>>(p, flag, -1);
+  scatter_probe_kernel<<<1, kThreads, 0, stream>>>(p, flag, -1, -1);
   if (vec_ok) {
     scatter_rows_range_kernel<T, kSum, kFull><<<blocks_range, kThreads, 0, stream>>>(p, row_lo, row_hi);
     scatter_rows_runs_kernel<T, kSum, kFull><<<blocks, kThreads, 0, stream>>>(p, row_lo, row_hi, 1);
@@ -1087,7 +1244,7 @@ extern "C" int tsb_scatter_sum_slice(const void *src, const int64_t *index, void
   p.arg_out = nullptr; p.count = nullptr;
   p.B = 1; p.E = E; p.K = K; p.N = N;
   p.sb = 0; p.se = 1; p.sk = 0;
-  p.l_log2 = 0; p.fresh = 1; p.replicas = 1; p.clustered = nullptr;
+  p.l_log2 = 0; p.fresh = 1; p.replicas = 1; p.clustered = nullptr; p.use_skew = 0;
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
     return run_scatter_sum_slice<scalar_t>(p, row_lo, row_hi, static_cast<int *>(workspace),
                                            reinterpret_cast<cudaStream_t>(stream));

@@ -413,6 +413,8 @@ __global__ void __launch_bounds__(32, stream_ctas_per_sm<T, REDUCE, VEC>()) csr_
     // INDIRECT: the permutation is read 32 positions at a time (lane j holds position 32 w + j of the
     // chunk), two windows ahead of the one the copies are issued from, and handed out by shuffle.
     int pw0 = 0, pw1 = 0, pw2 = 0;
+    const int row_elems = (int)p.K;                 // K < 2^31 with a permutation (checked by the launcher)
+    const T *perm_col = bsrc + c * VEC;             // this lane's columns of source entry 0
     auto load_perm_window = [&](int first) -> int {
       const int q = first + lane;
       int v = (q < t) ? p.perm[cs + q] : 0;
@@ -426,7 +428,7 @@ __global__ void __launch_bounds__(32, stream_ctas_per_sm<T, REDUCE, VEC>()) csr_
         if (step_first > 0 && (step_first & 31) == 0) { pw0 = pw1; pw1 = pw2; pw2 = load_perm_window(step_first + 64); }
         const int id = __shfl_sync(kFullMask, pw0, (step_first & 31) + sub);
         if (col_ok && next_rel < t) {
-          async_copy_pack<T, VEC>(&s_ring[into][lane], bsrc + (int64_t)id * p.K + c * VEC);
+          async_copy_pack<T, VEC>(&s_ring[into][lane], perm_col + (int64_t)id * row_elems);  // one 32x32->64 multiply-add
           if (kArg) s_id[into][lane] = id;
         }
       } else {
@@ -629,7 +631,7 @@ int launch_csr_reduce(const CsrParams &p, int dtype, int reduce, cudaStream_t st
       if (p.route_base[q] == nullptr) return TSB_ERR_ARG;
   }
   if ((reduce == TSB_MIN || reduce == TSB_MAX) && p.arg_out == nullptr) return TSB_ERR_ARG;
-  if (p.perm != nullptr && p.E >= kRelInf) return TSB_ERR_TOO_LARGE;
+  if (p.perm != nullptr && (p.E >= kRelInf || p.K >= (1ll << 31))) return TSB_ERR_TOO_LARGE;
   if (p.skip_outside && p.B != 1) return TSB_ERR_ARG;
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
     switch (reduce) {

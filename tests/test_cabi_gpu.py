@@ -208,7 +208,7 @@ def test_gathers(K):
 
 
 @pytest.fixture(params=['one-pass', 'sliced', 'replicated', 'runs', 'runs-sliced', 'direct', 'grouped', 'grouped-chunk32',
-                        'grouped-atomic'])
+                        'grouped-atomic', 'cached', 'cached-replicated'])
 def scatter_slices(request):
     """Forces the variants the launcher normally picks by size or by probing the index: sliced multi-pass
     accumulation (outputs larger than L2), accumulation into several copies of the output (small,
@@ -216,7 +216,7 @@ def scatter_slices(request):
     entries by target row and reduces rows through the permutation (also with 32-entry chunks, so that rows
     straddle many chunk borders)."""
     names = ('TSB_SCATTER_SLICE_BYTES', 'TSB_SCATTER_REPLICAS', 'TSB_SCATTER_CLUSTERED', 'TSB_SCATTER_GROUPED',
-             'TSB_CSR_CHUNK_ENTRIES', 'TSB_SCATTER_GROUPED_SORT')
+             'TSB_CSR_CHUNK_ENTRIES', 'TSB_SCATTER_GROUPED_SORT', 'TSB_SCATTER_CACHED')
     old = {k: os.environ.get(k) for k in names}
     for k in names:
         os.environ.pop(k, None)
@@ -231,6 +231,11 @@ def scatter_slices(request):
     os.environ['TSB_SCATTER_GROUPED'] = '1' if request.param.startswith('grouped') else '0'
     if request.param == 'grouped-chunk32':
         os.environ['TSB_CSR_CHUNK_ENTRIES'] = '32'
+    if request.param.startswith('cached'):  # fp32 sums through the shared-memory row cache (skewed indices)
+        os.environ['TSB_SCATTER_CACHED'] = '1'
+        os.environ['TSB_SCATTER_CLUSTERED'] = '0'
+        if request.param == 'cached-replicated':
+            os.environ['TSB_SCATTER_REPLICAS'] = '4'
     if request.param == 'grouped-atomic':  # the grouping by one global atomic per entry (huge row counts)
         os.environ['TSB_SCATTER_GROUPED_SORT'] = 'atomic'
     yield request.param
