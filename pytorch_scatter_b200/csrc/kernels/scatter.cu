@@ -154,7 +154,6 @@ struct ScatterParams {
   int replicas;        // copies of the output the updates are spread over (1: none)
   const int *clustered;  // device flags written by scatter_probe_kernel: [0] 1 = neighbouring entries share targets,
                          // [1] 1 = entries far apart often share targets (a skewed index)
-  int use_skew;          // the cached kernel was launched next to the direct one: flag [1] picks between them
 };
 
 // One CTA looks at four windows of 256 consecutive index entries and counts neighbours that name the
@@ -227,7 +226,6 @@ __global__ void __launch_bounds__(kThreads) scatter_rows_direct_kernel(ScatterPa
   using U = acc_t<T>;
   const T *__restrict__ src = static_cast<const T *>(p.src);
   if (p.clustered[0] != 0) return;                       // the run-combining kernel takes clustered indices
-  if (p.use_skew != 0 && p.clustered[1] != 0) return;    // the cached kernel takes skewed ones
   U *target = static_cast<U *>(p.target);
   if (p.replicas > 1) target += (blockIdx.x % p.replicas) * (p.B * p.N * p.K);
   const int L = 1 << p.l_log2;
@@ -251,7 +249,9 @@ __global__ void __launch_bounds__(kThreads) scatter_rows_direct_kernel(ScatterPa
 // they get theirs), later entries of that row are added with shared-memory atomics, all other entries go to global
 // memory as before; at the end every claimed slot is flushed with one global update per element.  The cache is used
 // when the probe's second flag says the index is skewed (duplicates among sampled, non-adjacent entries), otherwise
-// the kernel sends every entry to global memory like the direct kernel; fp32 accumulation, SUM only.  (A variant that
+// the kernel sends every entry to global memory like the direct kernel; fp32 accumulation, SUM only.  (For MIN/MAX
+// the cache was measured and loses, 2.65 -> 3.27 ms on the same index: their global updates are already filtered by a
+// plain load, and a hot row stops updating once it holds a large value.)  (A variant that
 // reserved a slot on the first sighting and cached only from the second on, to spare rows seen once the flush, was
 // slower on both the skewed and the uniform case.)
 constexpr int kCacheBytesMax = 96 * 1024;
@@ -1008,7 +1008,6 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
       const char *cache_env = std::getenv("TSB_SCATTER_CACHED");  // test / tuning hook: "0" / "1" dictate the skew verdict
       const int forced_skew = (cache_env != nullptr && (*cache_env == '0' || *cache_env == '1')) ? (*cache_env - '0') : -1;
       scatter_probe_kernel<<<1, kThreads, 0, stream>>>(p, flag, forced, forced_skew);
-      p.use_skew = 0;
       unsigned blocks_direct = 0, blocks_batched = 0, blocks_range = 0;
       if (!grid_for((p.B * p.E + kRangeBatches * kRangeGroups - 1) / (kRangeBatches * kRangeGroups), &blocks_range)) return TSB_ERR_TOO_LARGE;  // 1024 entries per warp
       if (!grid_for((p.B * p.E) << p.l_log2, &blocks_direct)) return TSB_ERR_TOO_LARGE;                    // L lanes per entry
@@ -1185,7 +1184,6 @@ extern "C" int tsb_scatter(const void *src, const int64_t *index, void *out, int
   p.fresh = out_seeded ? 0 : 1;
   p.replicas = 1;
   p.clustered = nullptr;
-  p.use_skew = 0;
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
     switch (reduce) {
       case TSB_SUM:
@@ -1244,7 +1242,7 @@ extern "C" int tsb_scatter_sum_slice(const void *src, const int64_t *index, void
   p.arg_out = nullptr; p.count = nullptr;
   p.B = 1; p.E = E; p.K = K; p.N = N;
   p.sb = 0; p.se = 1; p.sk = 0;
-  p.l_log2 = 0; p.fresh = 1; p.replicas = 1; p.clustered = nullptr; p.use_skew = 0;
+  p.l_log2 = 0; p.fresh = 1; p.replicas = 1; p.clustered = nullptr;
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
     return run_scatter_sum_slice<scalar_t>(p, row_lo, row_hi, static_cast<int *>(workspace),
                                            reinterpret_cast<cudaStream_t>(stream));
