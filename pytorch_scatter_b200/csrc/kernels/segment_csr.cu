@@ -39,6 +39,9 @@ constexpr int kRingDepth = 16;
 constexpr int kWindowRows = 31;          // lane j holds row pointer j of the window, so rows+1 <= 32
 constexpr int kRelInf = 0x3fffffff;      // "never ends inside this chunk"
 constexpr int64_t kChunkBytes = 128 * 1024;
+constexpr int64_t kFlatTileBytes = 32 * 1024;  // K == 1: a chunk is staged whole in shared memory (csr_flat_kernel)
+constexpr int kFlatThreads = 128;
+constexpr int kFlatLongRow = 64;               // entries inside the chunk from which a warp, not a thread, reduces a row
 
 struct CsrGeom {
   int l_log2;            // lanes per entry
@@ -54,8 +57,9 @@ struct CsrGeom {
 // Chunk length: a power of two holding about kChunkBytes of source, shortened (down to one full
 // warp step) when the whole reduced dimension would otherwise give too few chunks to occupy the GPU.
 inline int chunk_entries_for(int64_t K, size_t elem, int64_t E) {
-  int64_t c = kChunkBytes / (K * (int64_t)elem);
-  const int64_t want_chunks = 16384;  // ~7 single-warp CTAs per resident slot of a 148-SM part
+  int64_t c = (K == 1 ? kFlatTileBytes : kChunkBytes) / (K * (int64_t)elem);
+  // ~7 single-warp CTAs per resident slot of a 148-SM part; K == 1: 128-thread CTAs that pay two row searches each
+  const int64_t want_chunks = (K == 1) ? 4096 : 16384;
   if (E / want_chunks < c) c = E / want_chunks;
   if (const char *forced = std::getenv("TSB_CSR_CHUNK_ENTRIES")) {  // test hook: force short chunks
     const long long v = std::atoll(forced);
@@ -473,6 +477,150 @@ __global__ void __launch_bounds__(32, stream_ctas_per_sm<T, REDUCE, VEC>()) csr_
   }
 }
 
+// First row whose end (indptr[r + 1]) lies after `pos`, by a cooperative 32-ary search of one warp; N if none.
+__device__ __forceinline__ int64_t first_row_ending_after(const int64_t *ip, int64_t N, int64_t pos, int lane) {
+  int64_t lo = 0, hi = N;  // answer in [lo, hi]; hi == N means "no such row"
+  while (hi - lo > 32) {
+    const int64_t step = (hi - lo + 31) / 32;
+    int64_t probe = lo + (lane + 1) * step - 1;
+    if (probe > hi - 1) probe = hi - 1;
+    const unsigned gt = __ballot_sync(kFullMask, ip[probe + 1] > pos);
+    if (gt == 0) { lo = hi; break; }
+    const int f = __ffs((int)gt) - 1;
+    const int64_t new_hi = lo + (int64_t)(f + 1) * step - 1;
+    lo = lo + (int64_t)f * step;
+    hi = new_hi < hi - 1 ? new_hi : hi - 1;  // ends[hi] > pos is known: the answer is <= hi
+    if (hi < lo) hi = lo;
+  }
+  if (lo >= N) return N;
+  const bool in = lo + lane <= hi && lo + lane < N;
+  const unsigned gt = __ballot_sync(kFullMask, in && ip[lo + lane + 1] > pos);
+  return gt ? lo + (__ffs((int)gt) - 1) : hi;
+}
+
+// K == 1 (a 1-D source): the streaming kernel would spend a whole warp step on 32 scalars.  Here a CTA stages its
+// chunk (at most 32 KiB of entries) in shared memory with coalesced loads, finds the rows that end inside the chunk
+// with two cooperative searches, and then every thread reduces whole rows out of shared memory; rows with more than
+// kFlatLongRow entries inside the chunk are queued and reduced by a warp each.  Rows that straddle chunk borders use
+// the same HEAD / TAIL partials and the same fix-up kernel as the streaming kernel.
+template <typename T, int REDUCE>
+__global__ void __launch_bounds__(kFlatThreads) csr_flat_kernel(CsrParams p, CsrGeom g) {
+  using A = acc_t<T>;
+  using Acc = RowAcc<T, REDUCE, 1, int64_t>;  // arg: absolute position, p.E = none
+  constexpr bool kArg = Acc::kArg;
+  extern __shared__ __align__(16) unsigned char s_flat_raw[];
+  T *s_src = reinterpret_cast<T *>(s_flat_raw);
+  __shared__ int64_t s_rows[2];          // r_lo, r_hi
+  __shared__ int s_nlong;
+  __shared__ int64_t s_long[kFlatThreads];  // queued rows (at most one per thread and sweep)
+  const T *__restrict__ src = static_cast<const T *>(p.src);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t chunk_id = blockIdx.x;
+  const int64_t b = chunk_id / g.chunks;
+  const int64_t w = chunk_id - b * g.chunks;
+  const int64_t cs = w * g.chunk_entries;
+  const int64_t ce = (cs + g.chunk_entries < p.E) ? cs + g.chunk_entries : p.E;
+  const int t = (int)(ce - cs);
+  const int64_t *ip = p.indptr + b * p.bstride;
+  const T *csrc = src + b * p.E + cs;
+
+  // ---- stage the chunk ---------------------------------------------------------------------------
+  constexpr int kPer16 = 16 / (int)sizeof(T);
+  if ((reinterpret_cast<uintptr_t>(csrc) & 15u) == 0) {
+    const int full = t / kPer16;
+    for (int i = tid; i < full; i += kFlatThreads)
+      reinterpret_cast<int4 *>(s_src)[i] = __ldcs(reinterpret_cast<const int4 *>(csrc) + i);
+    for (int i = full * kPer16 + tid; i < t; i += kFlatThreads) s_src[i] = csrc[i];
+  } else {
+    for (int i = tid; i < t; i += kFlatThreads) s_src[i] = csrc[i];
+  }
+  // ---- the rows that end inside (cs, ce] (chunk 0: also those that end at 0) ----------------------
+  if (warp == 0) {
+    const int64_t r_lo = w > 0 ? first_row_ending_after(ip, p.N, cs, lane) : 0;
+    const int64_t r_hi = first_row_ending_after(ip, p.N, ce, lane);
+    if (lane == 0) {
+      s_rows[0] = r_lo;
+      s_rows[1] = r_hi < r_lo ? r_lo : r_hi;
+      s_nlong = 0;
+      g.head_row[chunk_id] = -1;
+    }
+  }
+  __syncthreads();
+  const int64_t r_lo = s_rows[0], r_hi = s_rows[1];
+  A *carry = static_cast<A *>(g.carry_val) + chunk_id * 2;          // [HEAD, TAIL], K == 1
+  int64_t *carry_arg = Acc::kPair ? g.carry_arg + chunk_id * 2 : nullptr;
+
+  // Finishes row r, whose part inside the chunk has been reduced into `acc`.
+  auto finish = [&](int64_t r, int64_t rs, int64_t re, const Acc &acc) {
+    if (r == r_lo && w > 0 && rs < cs) {  // began in an earlier chunk: the fix-up kernel adds the other pieces
+      carry[0] = acc.val[0];
+      if (kArg) carry_arg[0] = acc.arg[0];
+      if (Acc::kLseAcc) carry_arg[0] = acc.arg[0];
+      g.head_row[chunk_id] = r;
+      return;
+    }
+    const int64_t grow = b * p.N + r;
+    write_row<T, REDUCE, 1, int64_t>(acc, row_address<T, REDUCE, false>(p, grow, 0), kArg ? p.arg_out + grow : nullptr,
+                                     re - rs, p.mode, p.E, 0, p.E);
+    if (p.count_out != nullptr) static_cast<T *>(p.count_out)[grow] = from_acc<T>((A)(re - rs > 0 ? re - rs : 1));
+  };
+  // Reduces the entries [lo, hi) of the staged chunk that this lane (of `lanes`) owns.
+  auto reduce_part = [&](Acc &acc, int lo, int hi, int first, int lanes) {
+    for (int i = lo + first; i < hi; i += lanes) {
+      Pack<T, 1> v;
+      v.v[0] = s_src[i];
+      acc.update(v, cs + i);
+    }
+  };
+
+  for (int64_t base = r_lo; base < r_hi; base += kFlatThreads) {  // CTA-uniform trip count
+    const int64_t r = base + tid;
+    if (r < r_hi) {
+      const int64_t re = clamp64(ip[r + 1], 0, ce);   // bad pointers stay harmless: 0 <= rs <= re <= ce
+      const int64_t rs = clamp64(ip[r], 0, re);
+      const int lo = (int)((rs > cs ? rs : cs) - cs), hi = (int)(re - cs);
+      if (hi - lo > kFlatLongRow) {
+        s_long[atomicAdd(&s_nlong, 1)] = r;
+      } else {
+        Acc acc;
+        acc.init(p.E);
+        reduce_part(acc, lo, hi, 0, 1);
+        finish(r, rs, re, acc);
+      }
+    }
+    __syncthreads();
+    const int nlong = s_nlong;
+    for (int q = warp; q < nlong; q += kFlatThreads / 32) {  // warp-uniform
+      const int64_t rr = s_long[q];
+      const int64_t re = clamp64(ip[rr + 1], 0, ce);
+      const int64_t rs = clamp64(ip[rr], 0, re);
+      Acc acc;
+      acc.init(p.E);
+      reduce_part(acc, (int)((rs > cs ? rs : cs) - cs), (int)(re - cs), lane, 32);
+      acc.butterfly(1, 32);
+      if (lane == 0) finish(rr, rs, re, acc);
+    }
+    __syncthreads();
+    if (tid == 0) s_nlong = 0;
+    __syncthreads();
+  }
+  // ---- the row still open at the chunk's end: its part inside the chunk is this chunk's TAIL partial ----
+  if (warp == 0 && r_hi < p.N) {
+    const int64_t rs = clamp64(ip[r_hi], 0, p.E);
+    if (rs < ce) {
+      Acc acc;
+      acc.init(p.E);
+      reduce_part(acc, (int)((rs > cs ? rs : cs) - cs), t, lane, 32);
+      acc.butterfly(1, 32);
+      if (lane == 0) {
+        carry[1] = acc.val[0];
+        if (kArg) carry_arg[1] = acc.arg[0];
+        if (Acc::kLseAcc) carry_arg[1] = acc.arg[0];
+      }
+    }
+  }
+}
+
 // Fix-up kernel: one warp per chunk.  If the chunk closed a row that began in an earlier chunk,
 // fold the TAIL partials of the chunks the row ran through and this chunk's HEAD partial, in a
 // fixed order, and write the row.
@@ -594,6 +742,17 @@ int launch_typed(const CsrParams &p, cudaStream_t stream) {
   g.carry_val = ws;
   g.carry_arg = reinterpret_cast<int64_t *>(ws + arg_off);
   g.head_row = reinterpret_cast<int64_t *>(ws + row_off);
+  if (p.K == 1 && p.perm == nullptr && !p.skip_outside && p.route_world == 0 &&
+      (size_t)g.chunk_entries * sizeof(T) <= (size_t)kFlatTileBytes) {
+    const int64_t total_chunks = p.B * g.chunks;
+    if (total_chunks > 2147483647LL) return TSB_ERR_TOO_LARGE;
+    csr_flat_kernel<T, REDUCE><<<(unsigned)total_chunks, kFlatThreads, (size_t)g.chunk_entries * sizeof(T), stream>>>(p, g);
+    if (g.chunks > 1) {
+      const int64_t blocks = (total_chunks + (kThreads / 32) - 1) / (kThreads / 32);
+      csr_fixup_kernel<T, REDUCE, 1, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, g);
+    }
+    return launch_status();
+  }
   bool vec_ok = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.out);
   for (int q = 0; q < p.route_world; ++q) vec_ok = vec_ok && aligned16(p.route_base[q]);
   return vec_ok ? launch_vec<T, REDUCE, kFull>(p, g, stream) : launch_vec<T, REDUCE, 1>(p, g, stream);
