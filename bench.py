@@ -354,9 +354,10 @@ def run_ours(args):
                     'steps': e2e_steps, 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h},
             # per step, segment_csr: csr_stream_kernel + csr_fixup_kernel.  scatter on one GPU (output larger
             # than L2: the grouped path): bucket_hist, bucket_scan, bucket_partition, bucket_finalize, then
-            # csr_stream_kernel + csr_fixup_kernel through the permutation.  Several GPUs: the probe plus, per
-            # output slice, one range kernel and one runs kernel (the probe's flag makes one of them exit).
-            'gpu_launches': ((2 + 6) if world == 1 or exchange['kind'].startswith('peer') else (3 + 2 * scatter_passes)) * args.steps,
+            # csr_stream_kernel + csr_fixup_kernel through the permutation.  Several GPUs with the routed exchange:
+            # the same plus sum_slabs_kernel; with the NCCL variant: the grouping once plus stream + fix-up per slice.
+            'gpu_launches': ((2 + 6) if world == 1 else (2 + 6 + 1) if exchange['kind'].startswith('peer')
+                             else (3 + 2 * scatter_passes)) * args.steps,
             'clocks': clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
