@@ -357,7 +357,7 @@ def run_ours(args):
             # csr_stream_kernel + csr_fixup_kernel through the permutation.  Several GPUs with the routed exchange:
             # the same plus sum_slabs_kernel; with the NCCL variant: the grouping once plus stream + fix-up per slice.
             'gpu_launches': ((2 + 6) if world == 1 else (2 + 6 + 1) if exchange['kind'].startswith('peer')
-                             else (3 + 2 * scatter_passes)) * args.steps,
+                             else (2 + 4 + 2 * scatter_passes)) * args.steps,
             'clocks': clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
