@@ -41,6 +41,9 @@ constexpr int kRelInf = 0x3fffffff;      // "never ends inside this chunk"
 constexpr int64_t kChunkBytes = 128 * 1024;
 constexpr int64_t kFlatTileBytes = 32 * 1024;  // K == 1: a chunk is staged whole in shared memory (csr_flat_kernel)
 constexpr int kFlatThreads = 128;
+constexpr int64_t kFlatRowBytes = 0;           // widest entry (besides K == 1) that goes through csr_flat_kernel: none.
+                                               // Measured at 64 / 128 / 256 bytes per entry: 0.45 vs 0.26 ms (fp32 F=16),
+                                               // 1.07 vs 0.55 ms (bf16 F=64), 1.54 vs 0.73 ms (fp32 F=64) against the stream.
 constexpr int kFlatLongRow = 64;               // entries inside the chunk from which a warp, not a thread, reduces a row
 
 struct CsrGeom {
@@ -56,10 +59,18 @@ struct CsrGeom {
 
 // Chunk length: a power of two holding about kChunkBytes of source, shortened (down to one full
 // warp step) when the whole reduced dimension would otherwise give too few chunks to occupy the GPU.
+// Entries narrow enough for csr_flat_kernel (K == 1 always; tuning hook TSB_CSR_FLAT_ROW_BYTES).
+inline bool flat_rows(int64_t K, size_t elem) {
+  int64_t limit = kFlatRowBytes;
+  if (const char *v = std::getenv("TSB_CSR_FLAT_ROW_BYTES")) limit = std::atoll(v);
+  return K == 1 || K * (int64_t)elem <= limit;
+}
+
 inline int chunk_entries_for(int64_t K, size_t elem, int64_t E) {
-  int64_t c = (K == 1 ? kFlatTileBytes : kChunkBytes) / (K * (int64_t)elem);
-  // ~7 single-warp CTAs per resident slot of a 148-SM part; K == 1: 128-thread CTAs that pay two row searches each
-  const int64_t want_chunks = (K == 1) ? 4096 : 16384;
+  const bool flat = flat_rows(K, elem);
+  int64_t c = (flat ? kFlatTileBytes : kChunkBytes) / (K * (int64_t)elem);
+  // ~7 single-warp CTAs per resident slot of a 148-SM part; flat kernel: 128-thread CTAs that pay two row searches each
+  const int64_t want_chunks = flat ? 4096 : 16384;
   if (E / want_chunks < c) c = E / want_chunks;
   if (const char *forced = std::getenv("TSB_CSR_CHUNK_ENTRIES")) {  // test hook: force short chunks
     const long long v = std::atoll(forced);
@@ -498,23 +509,33 @@ __device__ __forceinline__ int64_t first_row_ending_after(const int64_t *ip, int
   return gt ? lo + (__ffs((int)gt) - 1) : hi;
 }
 
-// K == 1 (a 1-D source): the streaming kernel would spend a whole warp step on 32 scalars.  Here a CTA stages its
-// chunk (at most 32 KiB of entries) in shared memory with coalesced loads, finds the rows that end inside the chunk
-// with two cooperative searches, and then every thread reduces whole rows out of shared memory; rows with more than
-// kFlatLongRow entries inside the chunk are queued and reduced by a warp each.  Rows that straddle chunk borders use
-// the same HEAD / TAIL partials and the same fix-up kernel as the streaming kernel.
-template <typename T, int REDUCE>
+// K == 1 (a 1-D source; wider entries only through the tuning hook, where it loses): the streaming kernel would
+// spend a whole warp step (about 70 instructions plus the row-close path) on 32 scalars.  Here a CTA stages
+// its chunk (at most 32 KiB of entries) in shared memory with coalesced loads, finds the rows that end inside the
+// chunk with two cooperative searches, and then a group of L lanes (one 16-byte pack of the entry each) reduces a
+// whole row out of shared memory: a load, VEC adds and a loop counter per entry.  Rows with more than kFlatLongRow
+// entries inside the chunk are queued and reduced by a warp each.  Rows that straddle chunk borders use the same
+// HEAD / TAIL partials and the same fix-up kernel as the streaming kernel.
+template <typename T, int REDUCE, int VEC>
 __global__ void __launch_bounds__(kFlatThreads) csr_flat_kernel(CsrParams p, CsrGeom g) {
   using A = acc_t<T>;
-  using Acc = RowAcc<T, REDUCE, 1, int64_t>;  // arg: absolute position, p.E = none
+  using Acc = RowAcc<T, REDUCE, VEC, int64_t>;  // arg: absolute position, p.E = none
   constexpr bool kArg = Acc::kArg;
   extern __shared__ __align__(16) unsigned char s_flat_raw[];
   T *s_src = reinterpret_cast<T *>(s_flat_raw);
   __shared__ int64_t s_rows[2];          // r_lo, r_hi
   __shared__ int s_nlong;
-  __shared__ int64_t s_long[kFlatThreads];  // queued rows (at most one per thread and sweep)
+  __shared__ int64_t s_long[kFlatThreads];  // queued rows (at most one per lane group and sweep)
   const T *__restrict__ src = static_cast<const T *>(p.src);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int L = 1 << g.l_log2;             // lanes per entry
+  const int col = lane & (L - 1);
+  const int sub = lane >> g.l_log2;        // lane group inside the warp
+  const int eps = 32 >> g.l_log2;          // lane groups per warp
+  const int groups = kFlatThreads >> g.l_log2;
+  const int group = tid >> g.l_log2;
+  const int64_t Kv = p.K / VEC;
+  const bool col_ok = col < Kv;
   const int64_t chunk_id = blockIdx.x;
   const int64_t b = chunk_id / g.chunks;
   const int64_t w = chunk_id - b * g.chunks;
@@ -522,17 +543,18 @@ __global__ void __launch_bounds__(kFlatThreads) csr_flat_kernel(CsrParams p, Csr
   const int64_t ce = (cs + g.chunk_entries < p.E) ? cs + g.chunk_entries : p.E;
   const int t = (int)(ce - cs);
   const int64_t *ip = p.indptr + b * p.bstride;
-  const T *csrc = src + b * p.E + cs;
+  const T *csrc = src + (b * p.E + cs) * p.K;
 
   // ---- stage the chunk ---------------------------------------------------------------------------
   constexpr int kPer16 = 16 / (int)sizeof(T);
+  const int elems = t * (int)p.K;
   if ((reinterpret_cast<uintptr_t>(csrc) & 15u) == 0) {
-    const int full = t / kPer16;
+    const int full = elems / kPer16;
     for (int i = tid; i < full; i += kFlatThreads)
       reinterpret_cast<int4 *>(s_src)[i] = __ldcs(reinterpret_cast<const int4 *>(csrc) + i);
-    for (int i = full * kPer16 + tid; i < t; i += kFlatThreads) s_src[i] = csrc[i];
+    for (int i = full * kPer16 + tid; i < elems; i += kFlatThreads) s_src[i] = csrc[i];
   } else {
-    for (int i = tid; i < t; i += kFlatThreads) s_src[i] = csrc[i];
+    for (int i = tid; i < elems; i += kFlatThreads) s_src[i] = csrc[i];
   }
   // ---- the rows that end inside (cs, ce] (chunk 0: also those that end at 0) ----------------------
   if (warp == 0) {
@@ -547,40 +569,45 @@ __global__ void __launch_bounds__(kFlatThreads) csr_flat_kernel(CsrParams p, Csr
   }
   __syncthreads();
   const int64_t r_lo = s_rows[0], r_hi = s_rows[1];
-  A *carry = static_cast<A *>(g.carry_val) + chunk_id * 2;          // [HEAD, TAIL], K == 1
-  int64_t *carry_arg = Acc::kPair ? g.carry_arg + chunk_id * 2 : nullptr;
+  A *carry = static_cast<A *>(g.carry_val) + chunk_id * 2 * p.K;          // [HEAD, TAIL] of K values
+  int64_t *carry_arg = Acc::kPair ? g.carry_arg + chunk_id * 2 * p.K : nullptr;
 
-  // Finishes row r, whose part inside the chunk has been reduced into `acc`.
+  // Finishes row r (this lane's VEC columns of it), whose part inside the chunk has been reduced into `acc`.
   auto finish = [&](int64_t r, int64_t rs, int64_t re, const Acc &acc) {
     if (r == r_lo && w > 0 && rs < cs) {  // began in an earlier chunk: the fix-up kernel adds the other pieces
-      carry[0] = acc.val[0];
-      if (kArg) carry_arg[0] = acc.arg[0];
-      if (Acc::kLseAcc) carry_arg[0] = acc.arg[0];
-      g.head_row[chunk_id] = r;
+      if (col_ok) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          carry[col * VEC + i] = acc.val[i];
+          if (kArg) carry_arg[col * VEC + i] = acc.arg[i];
+          if (Acc::kLseAcc) carry_arg[col * VEC + i] = acc.arg[i];
+        }
+      }
+      if (col == 0) g.head_row[chunk_id] = r;
       return;
     }
     const int64_t grow = b * p.N + r;
-    write_row<T, REDUCE, 1, int64_t>(acc, row_address<T, REDUCE, false>(p, grow, 0), kArg ? p.arg_out + grow : nullptr,
-                                     re - rs, p.mode, p.E, 0, p.E);
-    if (p.count_out != nullptr) static_cast<T *>(p.count_out)[grow] = from_acc<T>((A)(re - rs > 0 ? re - rs : 1));
+    if (col_ok)
+      write_row<T, REDUCE, VEC, int64_t>(acc, row_address<T, REDUCE, false>(p, grow, col * VEC),
+                                         kArg ? p.arg_out + grow * p.K + col * VEC : nullptr, re - rs, p.mode, p.E, 0, p.E);
+    if (col == 0 && p.count_out != nullptr) static_cast<T *>(p.count_out)[grow] = from_acc<T>((A)(re - rs > 0 ? re - rs : 1));
   };
-  // Reduces the entries [lo, hi) of the staged chunk that this lane (of `lanes`) owns.
-  auto reduce_part = [&](Acc &acc, int lo, int hi, int first, int lanes) {
-    for (int i = lo + first; i < hi; i += lanes) {
-      Pack<T, 1> v;
-      v.v[0] = s_src[i];
-      acc.update(v, cs + i);
-    }
+  // Reduces this lane's columns of the staged entries lo + first, lo + first + stride, ... below hi.
+  auto reduce_part = [&](Acc &acc, int lo, int hi, int first, int stride) {
+    if (!col_ok) return;
+    const T *base = s_src + col * VEC;
+    for (int i = lo + first; i < hi; i += stride)
+      acc.update(*reinterpret_cast<const Pack<T, VEC> *>(base + (size_t)i * p.K), cs + i);
   };
 
-  for (int64_t base = r_lo; base < r_hi; base += kFlatThreads) {  // CTA-uniform trip count
-    const int64_t r = base + tid;
+  for (int64_t first_row = r_lo; first_row < r_hi; first_row += groups) {  // CTA-uniform trip count
+    const int64_t r = first_row + group;
     if (r < r_hi) {
       const int64_t re = clamp64(ip[r + 1], 0, ce);   // bad pointers stay harmless: 0 <= rs <= re <= ce
       const int64_t rs = clamp64(ip[r], 0, re);
       const int lo = (int)((rs > cs ? rs : cs) - cs), hi = (int)(re - cs);
       if (hi - lo > kFlatLongRow) {
-        s_long[atomicAdd(&s_nlong, 1)] = r;
+        if (col == 0) s_long[atomicAdd(&s_nlong, 1)] = r;
       } else {
         Acc acc;
         acc.init(p.E);
@@ -596,9 +623,9 @@ __global__ void __launch_bounds__(kFlatThreads) csr_flat_kernel(CsrParams p, Csr
       const int64_t rs = clamp64(ip[rr], 0, re);
       Acc acc;
       acc.init(p.E);
-      reduce_part(acc, (int)((rs > cs ? rs : cs) - cs), (int)(re - cs), lane, 32);
-      acc.butterfly(1, 32);
-      if (lane == 0) finish(rr, rs, re, acc);
+      reduce_part(acc, (int)((rs > cs ? rs : cs) - cs), (int)(re - cs), sub, eps);
+      acc.butterfly(L, 32);
+      if (sub == 0) finish(rr, rs, re, acc);
     }
     __syncthreads();
     if (tid == 0) s_nlong = 0;
@@ -610,12 +637,15 @@ __global__ void __launch_bounds__(kFlatThreads) csr_flat_kernel(CsrParams p, Csr
     if (rs < ce) {
       Acc acc;
       acc.init(p.E);
-      reduce_part(acc, (int)((rs > cs ? rs : cs) - cs), t, lane, 32);
-      acc.butterfly(1, 32);
-      if (lane == 0) {
-        carry[1] = acc.val[0];
-        if (kArg) carry_arg[1] = acc.arg[0];
-        if (Acc::kLseAcc) carry_arg[1] = acc.arg[0];
+      reduce_part(acc, (int)((rs > cs ? rs : cs) - cs), t, sub, eps);
+      acc.butterfly(L, 32);
+      if (sub == 0 && col_ok) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          carry[p.K + col * VEC + i] = acc.val[i];
+          if (kArg) carry_arg[p.K + col * VEC + i] = acc.arg[i];
+          if (Acc::kLseAcc) carry_arg[p.K + col * VEC + i] = acc.arg[i];
+        }
       }
     }
   }
@@ -742,16 +772,25 @@ int launch_typed(const CsrParams &p, cudaStream_t stream) {
   g.carry_val = ws;
   g.carry_arg = reinterpret_cast<int64_t *>(ws + arg_off);
   g.head_row = reinterpret_cast<int64_t *>(ws + row_off);
-  if (p.K == 1 && p.perm == nullptr && !p.skip_outside && p.route_world == 0 &&
-      (size_t)g.chunk_entries * sizeof(T) <= (size_t)kFlatTileBytes) {
+  if (flat_rows(p.K, sizeof(T)) && p.perm == nullptr && !p.skip_outside && p.route_world == 0 &&
+      (size_t)g.chunk_entries * (size_t)p.K * sizeof(T) <= (size_t)kFlatTileBytes) {
     const int64_t total_chunks = p.B * g.chunks;
     if (total_chunks > 2147483647LL) return TSB_ERR_TOO_LARGE;
-    csr_flat_kernel<T, REDUCE><<<(unsigned)total_chunks, kFlatThreads, (size_t)g.chunk_entries * sizeof(T), stream>>>(p, g);
-    if (g.chunks > 1) {
+    const bool vec = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.out);
+    const int64_t Kv = p.K / (vec ? kFull : 1);
+    if (Kv <= 32) {
+      g.l_log2 = ilog2_ceil(Kv);
+      const size_t smem = (size_t)g.chunk_entries * (size_t)p.K * sizeof(T);
       const int64_t blocks = (total_chunks + (kThreads / 32) - 1) / (kThreads / 32);
-      csr_fixup_kernel<T, REDUCE, 1, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, g);
+      if (vec) {
+        csr_flat_kernel<T, REDUCE, kFull><<<(unsigned)total_chunks, kFlatThreads, smem, stream>>>(p, g);
+        if (g.chunks > 1) csr_fixup_kernel<T, REDUCE, kFull, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, g);
+      } else {
+        csr_flat_kernel<T, REDUCE, 1><<<(unsigned)total_chunks, kFlatThreads, smem, stream>>>(p, g);
+        if (g.chunks > 1) csr_fixup_kernel<T, REDUCE, 1, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, g);
+      }
+      return launch_status();
     }
-    return launch_status();
   }
   bool vec_ok = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.out);
   for (int q = 0; q < p.route_world; ++q) vec_ok = vec_ok && aligned16(p.route_base[q]);

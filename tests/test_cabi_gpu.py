@@ -42,18 +42,25 @@ def row_lengths(gen, rows, kind):
     return lens
 
 
-@pytest.fixture(params=[None, 32, 64], ids=['chunk-default', 'chunk-32', 'chunk-64'])
+@pytest.fixture(params=[None, 32, 64, 'staged'], ids=['chunk-default', 'chunk-32', 'chunk-64', 'staged-rows'])
 def chunk(request):
-    old = os.environ.get('TSB_CSR_CHUNK_ENTRIES')
-    if request.param is None:
-        os.environ.pop('TSB_CSR_CHUNK_ENTRIES', None)
-    else:
+    """Chunk lengths of the row-pointer reduction (short chunks make rows straddle many chunk borders), and the kernel
+    that stages chunks in shared memory (the default for K == 1 only) forced for every entry of up to 64 bytes."""
+    names = ('TSB_CSR_CHUNK_ENTRIES', 'TSB_CSR_FLAT_ROW_BYTES')
+    old = {k: os.environ.get(k) for k in names}
+    for k in names:
+        os.environ.pop(k, None)
+    if request.param == 'staged':
+        os.environ['TSB_CSR_FLAT_ROW_BYTES'] = '64'
+        os.environ['TSB_CSR_CHUNK_ENTRIES'] = '64'
+    elif request.param is not None:
         os.environ['TSB_CSR_CHUNK_ENTRIES'] = str(request.param)
     yield request.param
-    if old is None:
-        os.environ.pop('TSB_CSR_CHUNK_ENTRIES', None)
-    else:
-        os.environ['TSB_CSR_CHUNK_ENTRIES'] = old
+    for k, v in old.items():
+        if v is None:
+            os.environ.pop(k, None)
+        else:
+            os.environ[k] = v
 
 
 @pytest.mark.parametrize('kind', ['lognormal', 'uniform', 'giant', 'empty_ends'])
