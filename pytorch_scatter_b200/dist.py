@@ -243,8 +243,9 @@ def scatter_sum_routed(src_local: torch.Tensor, index_local: torch.Tensor, dim_s
     # bounded waits: a rank that never arrives ends the call with an error instead of hanging the GPUs
     handle.barrier(channel=0, timeout_ms=60000)   # nobody is still adding up the previous call's slabs
     torch.ops.torch_scatter.segment_sum_perm_routed(src_local, rowptr, perm, ptrs, rank, rows, dim_size)
-    if rows * world > dim_size and rank == world - 1:   # rows past dim_size exist only as padding: nobody writes them
-        buf[:, dim_size - rank * rows:].zero_()
+    valid = min(max(dim_size - rank * rows, 0), rows)   # rows of this rank's block that exist; the rest is padding
+    if valid < rows:                                    # nobody writes padding rows: keep them zero
+        buf[:, valid:].zero_()
     handle.barrier(channel=1, timeout_ms=60000)   # every rank's rows have landed
     return torch.ops.torch_scatter.sum_slabs(buf)
 
