@@ -492,6 +492,8 @@ def run_suite(args):
                 nb = nnz * F * s + nnz * 8 + ROWS * F * s
                 ms, gbs = timeit(lambda: ts.scatter_logsumexp(src, index, 0, dim_size=ROWS), nb, False)
                 emit('C3', 'scatter_logsumexp fp32 F=64 (composite)', ms, gbs)
+                ms, gbs = timeit(lambda: ts.scatter_std(src, index, 0, dim_size=ROWS), nb, False)
+                emit('C3', 'scatter_std fp32 F=64 (composite)', ms, gbs)
             del src, table, out
         del index, indptr
 

@@ -138,6 +138,12 @@ int tsb_gather_coo(const void *src, const int64_t *index, void *out, const void 
 int tsb_gather_coo_apply(const void *x, const void *table, const int64_t *index, void *out,
                          int64_t B, int64_t E, int64_t K, int64_t N, int64_t index_batch_stride,
                          int dtype, int op, tsb_stream_t stream);
+/* The same with op 3 = (x - row)^2 as well and an optional second FP32 table `scale` [B,N,K] (NULL: none) whose
+ * gathered row multiplies the result: with table = the group means these are the second pass of upstream's
+ * scatter_std (torch_scatter/composite/std.py:31-33, op 3) and its backward (op 2 with scale = grad / (count * std)). */
+int tsb_gather_coo_apply2(const void *x, const void *table, const void *scale, const int64_t *index, void *out,
+                          int64_t B, int64_t E, int64_t K, int64_t N, int64_t index_batch_stride,
+                          int dtype, int op, tsb_stream_t stream);
 
 /* Sets *unsorted_flag (a device int) to 1 if the n index entries are not ascending, else to 0.  Lets a caller
  * pick the sorted-index kernels for an index of unknown order (upstream asserts sortedness instead,

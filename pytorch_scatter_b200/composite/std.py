@@ -2,7 +2,7 @@
 
 Same signature and two-pass arithmetic as ``torch_scatter/composite/std.py:8-39`` upstream: group
 means first, then the sum of squared deviations, divided by ``max(count - 1, 1) + 1e-6`` when
-``unbiased``.
+``unbiased``.  fp32 data over an ascending 1-D index takes a fused three-pass form of the same arithmetic.
 """
 from typing import Optional
 
@@ -10,7 +10,7 @@ import torch
 
 from ..scatter import scatter_sum
 from ..utils import broadcast
-from .softmax import _read_back
+from .softmax import _fused_ok, _read_back
 
 
 def scatter_std(src: torch.Tensor, index: torch.Tensor, dim: int = -1,
@@ -21,6 +21,9 @@ def scatter_std(src: torch.Tensor, index: torch.Tensor, dim: int = -1,
         dim_size = out.size(dim)
     if dim < 0:
         dim = src.dim() + dim
+    if out is None and src.dtype == torch.float32 and _fused_ok(src, index):
+        # ascending 1-D index: three passes (means, squared deviations fused into the read-back, their sums)
+        return torch.ops.torch_scatter.std_sorted(src, index, dim, dim_size, unbiased)
 
     # group sizes, counted over the index as given (before broadcasting)
     index_dim = dim if index.dim() > dim else index.dim() - 1

@@ -131,7 +131,8 @@ struct GatherCooParams {
   void *out;
   const void *count;
   const void *x;  // optional per-entry operand [B,E,K]: out = op(x, gathered row)
-  int op;         // 1: exp(x - row), 2: x - row (the second passes of softmax / log_softmax)
+  int op;         // 1: exp(x - row), 2: x - row (the second passes of softmax / log_softmax), 3: (x - row)^2
+  const float *scale;  // optional second fp32 table [B,N,K]: the result is multiplied by its gathered row
   int64_t B, E, K, N, bstride;
   int l_log2;
 };
@@ -222,9 +223,14 @@ __global__ void __launch_bounds__(kThreads) gather_coo_kernel(GatherCooParams p)
             if constexpr (APPLY) {
               Pack<T, VEC> o;
 #pragma unroll
+              FloatRow<VEC> w;
+              if (p.scale != nullptr) w = ld_float_row<VEC>(p.scale + r[u] * p.K + c * VEC);  // row just fetched: L1/L2
+#pragma unroll
               for (int k = 0; k < VEC; ++k) {
                 const float d = (float)to_acc<T>(xv[u].v[k]) - v[u].v[k];
-                o.v[k] = from_acc<T>((acc_t<T>)(p.op == 1 ? __expf(d) : d));
+                float y = p.op == 1 ? __expf(d) : (p.op == 3 ? d * d : d);
+                if (p.scale != nullptr) y *= w.v[k];
+                o.v[k] = from_acc<T>((acc_t<T>)y);
               }
               st_stream<T, VEC>(out + at, o);
             } else {
@@ -247,7 +253,8 @@ int launch_gather_coo(GatherCooParams p, cudaStream_t stream) {
   constexpr int kFull = full_vec<T>();
   const int64_t entries = p.B * p.E;
   if (entries == 0 || p.K == 0 || p.N == 0) return TSB_OK;
-  const bool vec_ok = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.out) && (p.x == nullptr || aligned16(p.x));
+  const bool vec_ok = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.out) && (p.x == nullptr || aligned16(p.x)) &&
+                      (p.scale == nullptr || aligned16(p.scale));
   const int64_t Kv = p.K / (vec_ok ? kFull : 1);
   p.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
   const int64_t per_cta = (int64_t)(kThreads / 32) * 32 * kGatherBatches;
@@ -303,7 +310,7 @@ extern "C" int tsb_gather_coo(const void *src, const int64_t *index, void *out, 
   if (count != nullptr && (dtype == TSB_I32 || dtype == TSB_I64)) return TSB_ERR_DTYPE;
   GatherCooParams p;
   p.src = src; p.index = index; p.out = out; p.count = count;
-  p.x = nullptr; p.op = 0;
+  p.x = nullptr; p.op = 0; p.scale = nullptr;
   p.B = B; p.E = E; p.K = K; p.N = N; p.bstride = index_batch_stride; p.l_log2 = 0;
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
     return launch_gather_coo<scalar_t, false>(p, reinterpret_cast<cudaStream_t>(stream));
@@ -313,15 +320,21 @@ extern "C" int tsb_gather_coo(const void *src, const int64_t *index, void *out, 
 extern "C" int tsb_gather_coo_apply(const void *x, const void *table, const int64_t *index, void *out, int64_t B,
                                     int64_t E, int64_t K, int64_t N, int64_t index_batch_stride, int dtype, int op,
                                     tsb_stream_t stream) {
+  return tsb_gather_coo_apply2(x, table, nullptr, index, out, B, E, K, N, index_batch_stride, dtype, op, stream);
+}
+
+extern "C" int tsb_gather_coo_apply2(const void *x, const void *table, const void *scale, const int64_t *index, void *out,
+                                     int64_t B, int64_t E, int64_t K, int64_t N, int64_t index_batch_stride, int dtype,
+                                     int op, tsb_stream_t stream) {
   using namespace tsb;
   if (B < 0 || E < 0 || K < 0 || N < 0) return TSB_ERR_ARG;
   if (B * E * K == 0 || N == 0) return TSB_OK;
   if (x == nullptr || table == nullptr || index == nullptr || out == nullptr) return TSB_ERR_ARG;
-  if (op != 1 && op != 2) return TSB_ERR_REDUCE;
+  if (op < 1 || op > 3) return TSB_ERR_REDUCE;
   if (dtype != TSB_F32 && dtype != TSB_F16 && dtype != TSB_BF16) return TSB_ERR_DTYPE;  // computed in fp32
   GatherCooParams p;
   p.src = table; p.index = index; p.out = out; p.count = nullptr;
-  p.x = x; p.op = op;
+  p.x = x; p.op = op; p.scale = static_cast<const float *>(scale);
   p.B = B; p.E = E; p.K = K; p.N = N; p.bstride = index_batch_stride; p.l_log2 = 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == TSB_F32) return launch_gather_coo<float, true>(p, s);

@@ -49,19 +49,23 @@ torch::Tensor segment_lse(const torch::Tensor &src_, const torch::Tensor &index,
   return table;
 }
 
-// out = op(x, table[.., index, ..]) along dim, table fp32; op 1: exp(x - row), 2: x - row
+// out = op(x, table[.., index, ..]) [* scale[.., index, ..]] along dim, tables fp32;
+// op 1: exp(x - row), 2: x - row, 3: (x - row)^2
 torch::Tensor gather_apply(const torch::Tensor &x_, const torch::Tensor &table_, const torch::Tensor &index, int64_t dim,
-                           int op) {
+                           int op, const std::optional<torch::Tensor> &scale_ = std::nullopt) {
   c10::cuda::CUDAGuard guard(x_.device());
   auto x = x_.contiguous();
   auto table = table_.contiguous();
+  torch::Tensor scale;
+  if (scale_.has_value()) scale = scale_.value().contiguous();
   auto out = torch::empty_like(x);
   if (x.numel() == 0) return out;
   const Flat f = flat_dims(x, dim);
   auto idx = index.contiguous();
-  check_status(tsb_gather_coo_apply(x.data_ptr(), table.data_ptr<float>(), idx.data_ptr<int64_t>(), out.data_ptr(), f.B,
-                                    f.E, f.K, table.size(dim), 0, dtype_enum(x), op, current_stream()),
-               "tsb_gather_coo_apply");
+  check_status(tsb_gather_coo_apply2(x.data_ptr(), table.data_ptr<float>(), scale.defined() ? scale.data_ptr<float>() : nullptr,
+                                     idx.data_ptr<int64_t>(), out.data_ptr(), f.B, f.E, f.K, table.size(dim), 0,
+                                     dtype_enum(x), op, current_stream()),
+               "tsb_gather_coo_apply2");
   return out;
 }
 
@@ -142,6 +146,44 @@ public:
   }
 };
 
+// Grouped standard deviation of fp32 data over an ascending 1-D index in three passes (upstream composes seven,
+// torch_scatter/composite/std.py:8-39): group means (and counts), the squared deviations through the gather with
+// (x - mean)^2 fused in, their group sums.  out = sqrt(S / (c + 1e-6)) with c = max(count - 1, 1) when unbiased.
+// backward: gx = g[group] * (x - mean[group]) / ((c + 1e-6) * out)[group]  (the mean's own derivative sums to zero).
+class StdSorted : public torch::autograd::Function<StdSorted> {
+public:
+  static variable_list forward(AutogradContext *ctx, Variable src, Variable index, int64_t dim,
+                               std::optional<int64_t> dim_size, bool unbiased) {
+    dim = dim < 0 ? src.dim() + dim : dim;
+    const int64_t N = groups_of(index, dim_size);
+    auto iv = index_view(index, src, dim);
+    auto mean_count = segment_coo_fw(src, iv, std::nullopt, N, "mean");
+    auto mean = std::get<0>(mean_count);
+    auto count = std::get<1>(mean_count).value();  // clamped to >= 1, shaped like the index view with N along dim
+    auto squares = gather_apply(src, mean, index, dim, 3);
+    auto total = std::get<0>(segment_coo_fw(squares, iv, std::nullopt, N, "sum"));
+    while (count.dim() < total.dim()) count = count.unsqueeze(-1);
+    if (unbiased) count = count.sub(1).clamp_min(1);
+    auto denom = count + 1e-6;
+    auto out = total.div(denom).sqrt();
+    ctx->saved_data["dim"] = dim;
+    ctx->save_for_backward({src, index, mean, denom, out});
+    return {out};
+  }
+  static variable_list backward(AutogradContext *ctx, variable_list grad_outs) {
+    auto saved = ctx->get_saved_variables();
+    auto src = saved[0], index = saved[1], mean = saved[2], denom = saved[3], out = saved[4];
+    const int64_t dim = ctx->saved_data["dim"].toInt();
+    auto scale = grad_outs[0].div(denom * out).expand_as(out).contiguous();
+    auto grad_in = gather_apply(src, mean, index, dim, 2, scale);
+    return {grad_in, Variable(), Variable(), Variable(), Variable()};
+  }
+};
+
+torch::Tensor std_sorted(torch::Tensor src, torch::Tensor index, int64_t dim, std::optional<int64_t> dim_size, bool unbiased) {
+  return StdSorted::apply(src, index, dim, dim_size, unbiased)[0];
+}
+
 torch::Tensor softmax_sorted(torch::Tensor src, torch::Tensor index, int64_t dim, std::optional<int64_t> dim_size,
                              bool log) {
   return SoftmaxSorted::apply(src, index, dim, dim_size, log)[0];
@@ -157,4 +199,5 @@ TORCH_LIBRARY_FRAGMENT(torch_scatter, m) {
   m.def("index_is_sorted", &tsb_ops::index_is_sorted);
   m.def("softmax_sorted", &tsb_ops::softmax_sorted);
   m.def("logsumexp_sorted", &tsb_ops::logsumexp_sorted);
+  m.def("std_sorted", &tsb_ops::std_sorted);
 }

@@ -96,7 +96,7 @@ def gather_coo(src, index, count=None):
 
 
 def gather_coo_apply(x, table, index, op):
-    """x [B,E,K], table fp32 [B,N,K], index [Bi,E]; op 1: exp(x - table[index]), 2: x - table[index]."""
+    """x [B,E,K], table fp32 [B,N,K], index [Bi,E]; op 1: exp(x - table[index]), 2: x - table[index], 3: its square."""
     assert table.dtype == torch.float32
     B, E, K = x.shape
     bstride = 0 if index.size(0) == 1 else E

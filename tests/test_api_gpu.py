@@ -240,6 +240,31 @@ def test_fused_sorted_softmax_family(ts, dtype):
         assert torch.equal(torch.jit.script(ts.scatter_softmax)(src, index, dim), ts.scatter_softmax(src, index, dim))
 
 
+@pytest.mark.parametrize('unbiased', [True, False])
+def test_fused_sorted_std(ts, unbiased):
+    """fp32 data over an ascending 1-D index takes the three-pass form; judge: the composed operators in float64 on
+    the same groups in permuted order."""
+    torch.manual_seed(5)
+    E, N = 4000, 150
+    index = torch.randint(0, N - 10, (E,), device=DEV).sort()[0]
+    perm = torch.randperm(E, device=DEV)
+    for shape, dim in (((E,), 0), ((E, 5), 0), ((3, E, 8), 1), ((2, E), -1)):
+        src = 3 * torch.randn(shape, device=DEV)
+        a = src.clone().requires_grad_()
+        b = src.double().index_select(dim, perm).requires_grad_()
+        out_a = ts.scatter_std(a, index, dim=dim, dim_size=N, unbiased=unbiased)
+        out_b = ts.scatter_std(b, index[perm], dim=dim, dim_size=N, unbiased=unbiased)
+        assert out_a.dtype == torch.float32 and out_a.shape == out_b.shape
+        assert torch.allclose(out_a.double(), out_b, rtol=1e-5, atol=1e-6), shape
+        g = torch.randn_like(out_a)
+        out_a.backward(g)
+        out_b.backward(g.double())
+        want_grad = torch.empty_like(b.grad).index_copy_(dim, perm, b.grad)
+        assert torch.allclose(a.grad.double(), want_grad, rtol=1e-4, atol=1e-5, equal_nan=True), (shape, 'grad')
+        assert torch.equal(torch.jit.script(ts.scatter_std)(src, index, dim, None, N, unbiased),
+                           ts.scatter_std(src, index, dim, None, N, unbiased))
+
+
 def test_fused_sorted_softmax_gradcheck(ts):
     """float64 does not take the fused path, so check its analytic backward numerically in fp32 against the composed one."""
     torch.manual_seed(4)

@@ -168,7 +168,7 @@ def test_gather_coo_apply_and_sortedness():
             x = torch.randn(2, E, K, generator=gen).to(dtype)
             table = torch.randn(2, N, K, generator=gen)
             rows = table[:, index[0]]
-            for op, want in ((1, (x.float() - rows).exp()), (2, x.float() - rows)):
+            for op, want in ((1, (x.float() - rows).exp()), (2, x.float() - rows), (3, (x.float() - rows) ** 2)):
                 got = cabi.gather_coo_apply(x.cuda(), table.cuda(), index.cuda(), op).cpu().float()
                 assert torch.allclose(got, want, rtol=tol, atol=tol), f'apply op={op} {dtype} K={K}'
     asc = torch.arange(100000).cuda() // 3
