@@ -188,7 +188,7 @@ int tsb_scatter(const void *src, const int64_t *index, void *out, int64_t *arg_o
  *   tsb_segment_csr_perm  out[b, n, :] = reduce over q in [rowptr[n], rowptr[n+1]) of src[b, perm[q], :] for the rows
  *                         row_lo <= n < row_hi (other rows of out are not touched; a proper slice needs B == 1),
  *                         with scatter's write rules (out_seeded as in tsb_scatter; MIN/MAX args are entry ids,
- *                         ties towards the smaller id).  SUM, MEAN, MIN or MAX. */
+ *                         ties towards the smaller id).  SUM, MEAN, MIN, MAX, or (whole problem only) MUL. */
 size_t tsb_scatter_group_workspace_bytes(int64_t E, int64_t N);
 int tsb_scatter_group(const int64_t *index, int64_t E, int64_t N, int64_t *rowptr, int32_t *perm, int32_t *count,
                       void *workspace, size_t workspace_bytes, tsb_stream_t stream);

@@ -1052,12 +1052,18 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
         if (cached) {  // it covers the skewed and the plain case; clustered indices still go to the runs kernel
           scatter_rows_runs_kernel<T, OP, kFull><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi, replicas);
         } else if (vec_ok) {
-          if (sliced) scatter_rows_range_kernel<T, OP, kFull><<<blocks_range, kThreads, 0, stream>>>(p, lo, hi);
-          else scatter_rows_direct_kernel<T, OP, kFull><<<blocks_direct, kThreads, 0, stream>>>(p);
+          bool ranged = false;
+          if constexpr (OP == kSum) {  // only sums are ever sliced
+            if (sliced) { scatter_rows_range_kernel<T, OP, kFull><<<blocks_range, kThreads, 0, stream>>>(p, lo, hi); ranged = true; }
+          }
+          if (!ranged) scatter_rows_direct_kernel<T, OP, kFull><<<blocks_direct, kThreads, 0, stream>>>(p);
           scatter_rows_runs_kernel<T, OP, kFull><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi, replicas);
         } else {
-          if (sliced) scatter_rows_range_kernel<T, OP, 1><<<blocks_range, kThreads, 0, stream>>>(p, lo, hi);
-          else scatter_rows_direct_kernel<T, OP, 1><<<blocks_direct, kThreads, 0, stream>>>(p);
+          bool ranged = false;
+          if constexpr (OP == kSum) {
+            if (sliced) { scatter_rows_range_kernel<T, OP, 1><<<blocks_range, kThreads, 0, stream>>>(p, lo, hi); ranged = true; }
+          }
+          if (!ranged) scatter_rows_direct_kernel<T, OP, 1><<<blocks_direct, kThreads, 0, stream>>>(p);
           scatter_rows_runs_kernel<T, OP, 1><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi, replicas);
         }
       }
@@ -1121,10 +1127,11 @@ namespace {
 // it wins once the accumulation target no longer stays in L2 (the reductions then re-fetch output
 // lines or re-read the index per slice), for MIN/MAX earlier because value+arg targets are twice as big.
 bool prefer_grouped(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce) {
-  (void)E;
   const int64_t acc = (dtype == TSB_F64 || dtype == TSB_I64) ? 8 : 4;
   const int64_t elem = (dtype == TSB_F64 || dtype == TSB_I64) ? 8 : (dtype == TSB_F16 || dtype == TSB_BF16) ? 2 : 4;
   const int64_t target_bytes = B * N * K * acc;
+  // products have no native atomic (compare-and-swap loops): grouping wins as soon as there is work to speak of
+  if (reduce == TSB_MUL) return B * E * K >= (1ll << 18) && E < (1ll << 30);
   if (K * elem < 32) return false;
   const bool minmax = reduce == TSB_MIN || reduce == TSB_MAX;
   return target_bytes > (minmax ? (48ll << 20) : (192ll << 20));

@@ -361,7 +361,7 @@ GroupedLayout layout_for(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, 
 
 bool scatter_grouped_possible(int64_t B, int64_t E, int64_t K, int64_t N, int64_t sb, int64_t se, int64_t sk,
                               int dtype, int reduce) {
-  if (reduce != TSB_SUM && reduce != TSB_MEAN && reduce != TSB_MIN && reduce != TSB_MAX) return false;
+  if (reduce != TSB_SUM && reduce != TSB_MEAN && reduce != TSB_MIN && reduce != TSB_MAX && reduce != TSB_MUL) return false;
   // the CSR mean truncates integers, upstream's scatter_mean floors them (torch_scatter/scatter.py:65)
   if (reduce == TSB_MEAN && (dtype == TSB_I32 || dtype == TSB_I64)) return false;
   if (sk != 0 || (E > 1 && se != 1) || (B > 1 && sb != 0)) return false;  // one index entry per source row, shared by the batches

@@ -7,7 +7,7 @@
 namespace tsb {
 
 // Structural conditions: one index entry per source row (stride 0 along the features, unit stride
-// along the entries), shared by all batches; SUM / MEAN (floats) / MIN / MAX; E < 2^30.
+// along the entries), shared by all batches; SUM / MEAN (floats) / MIN / MAX / MUL; E < 2^30.
 bool scatter_grouped_possible(int64_t B, int64_t E, int64_t K, int64_t N, int64_t sb, int64_t se, int64_t sk,
                               int dtype, int reduce);
 

@@ -114,6 +114,8 @@ template <typename T, int REDUCE, int VEC, typename ArgT = int64_t> struct RowAc
       const A x = to_acc<T>(v.v[i]);
       if (REDUCE == kSum || REDUCE == kMean) {
         val[i] += x;
+      } else if (REDUCE == kMul) {
+        val[i] *= x;
       } else if (REDUCE == kMin) {
         if (x < val[i] || (TIES && x == val[i] && e < arg[i] && arg[i] != none)) { val[i] = x; arg[i] = e; }
       } else if (REDUCE == kMax) {
@@ -138,6 +140,8 @@ template <typename T, int REDUCE, int VEC, typename ArgT = int64_t> struct RowAc
     for (int i = 0; i < VEC; ++i) {
       if (REDUCE == kSum || REDUCE == kMean) {
         val[i] += oval[i];
+      } else if (REDUCE == kMul) {
+        val[i] *= oval[i];
       } else if (kArg) {
         const bool better = (REDUCE == kMin) ? (oval[i] < val[i]) : (oval[i] > val[i]);
         if (better || (oval[i] == val[i] && oarg[i] < arg[i])) { val[i] = oval[i]; arg[i] = oarg[i]; }
@@ -242,7 +246,7 @@ __device__ __forceinline__ void write_row(const RowAcc<T, REDUCE, VEC, ArgT> &ac
   for (int i = 0; i < VEC; ++i) {
     A v = acc.val[i];
     if (!kArg) {
-      if (mode == kCooSeeded) v += to_acc<T>(seed.v[i]);
+      if (mode == kCooSeeded) v = (REDUCE == kMul) ? v * to_acc<T>(seed.v[i]) : v + to_acc<T>(seed.v[i]);
       o.v[i] = (REDUCE == kMean) ? scale.apply(v) : from_acc<T>(v);
     } else {
       int64_t a = (acc.arg[i] == arg_none) ? sentinel : arg_base + (int64_t)acc.arg[i];
@@ -735,7 +739,12 @@ int launch_vec(const CsrParams &p, CsrGeom g, cudaStream_t stream) {
   if (total_chunks > 2147483647LL) return TSB_ERR_TOO_LARGE;
   const bool extras = p.skip_outside || p.route_world > 0;
   const int64_t blocks = (total_chunks + (kThreads / 32) - 1) / (kThreads / 32);
-  if (p.perm != nullptr || extras) {
+  if constexpr (REDUCE == kMul) {  // the product exists for scatter only: through the permutation, whole problem
+    if (p.perm == nullptr || extras) return TSB_ERR_REDUCE;
+    csr_stream_kernel<T, REDUCE, VEC, 1><<<(unsigned)total_chunks, 32, 0, stream>>>(p, g);
+    if (g.chunks > 1) csr_fixup_kernel<T, REDUCE, VEC, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, g);
+    return launch_status();
+  } else if (p.perm != nullptr || extras) {
     if constexpr (REDUCE == kLse) {
       return TSB_ERR_REDUCE;
     } else {
@@ -772,6 +781,7 @@ int launch_typed(const CsrParams &p, cudaStream_t stream) {
   g.carry_val = ws;
   g.carry_arg = reinterpret_cast<int64_t *>(ws + arg_off);
   g.head_row = reinterpret_cast<int64_t *>(ws + row_off);
+  if constexpr (REDUCE != kMul) {
   if (flat_rows(p.K, sizeof(T)) && p.perm == nullptr && !p.skip_outside && p.route_world == 0 &&
       (size_t)g.chunk_entries * (size_t)p.K * sizeof(T) <= (size_t)kFlatTileBytes) {
     const int64_t total_chunks = p.B * g.chunks;
@@ -791,6 +801,7 @@ int launch_typed(const CsrParams &p, cudaStream_t stream) {
       }
       return launch_status();
     }
+  }
   }
   bool vec_ok = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.out);
   for (int q = 0; q < p.route_world; ++q) vec_ok = vec_ok && aligned16(p.route_base[q]);
@@ -837,6 +848,7 @@ int launch_csr_reduce(const CsrParams &p, int dtype, int reduce, cudaStream_t st
       case TSB_MEAN: return launch_typed<scalar_t, kMean>(p, stream);
       case TSB_MIN: return launch_typed<scalar_t, kMin>(p, stream);
       case TSB_MAX: return launch_typed<scalar_t, kMax>(p, stream);
+      case TSB_MUL: return launch_typed<scalar_t, kMul>(p, stream);
       case TSB_LSE:
         if constexpr (std::is_same<acc_t<scalar_t>, float>::value) return launch_typed<scalar_t, kLse>(p, stream);
         else return TSB_ERR_DTYPE;

@@ -365,6 +365,24 @@ def test_scatter_grouped_many_buckets(sort):
                 os.environ[k] = v
 
 
+def test_scatter_rows_mul(scatter_slices):
+    """Products over a broadcast 1-D index: compare-and-swap atomics, or (grouped variants) the atomics-free path."""
+    gen = torch.Generator().manual_seed(78)
+    B, E, K, N = 2, 3000, 8, 40
+    index = torch.randint(0, N, (1, E, 1), generator=gen)
+    for dtype in (torch.float32, torch.float64, torch.int32, torch.int64):
+        src = rand_src(gen, (B, E, K), dtype)
+        # mostly ones, a few factors in [-2, 2]: products stay finite and exact enough for the tolerance
+        s = torch.where(torch.rand(src.shape, generator=gen) < 0.02, src.double().clamp(-2, 2).to(dtype), torch.ones_like(src))
+        base = rand_src(gen, (B, N, K), dtype)
+        want, _ = oracle.scatter(s, index, N, 'mul')
+        got, _, _ = cabi.scatter(s.cuda(), index.cuda(), N, 'mul', (0, 1, 0))
+        assert_close(got, want, what=f'scatter mul {dtype}')
+        want, _ = oracle.scatter(s, index, N, 'mul', base)
+        got, _, _ = cabi.scatter(s.cuda(), index.cuda(), N, 'mul', (0, 1, 0), out=base.clone().cuda())
+        assert_close(got, want, what=f'scatter mul seeded {dtype}')
+
+
 def test_scatter_seeded_and_out_of_range(scatter_slices):
     gen = torch.Generator().manual_seed(21)
     E, K, N = 500, 8, 20
