@@ -513,7 +513,7 @@ def run_suite(args):
     def c5():
         # One GPU's share of the 8-GPU job: 1/8 of the 200M edges (bf16 [25M x 128]); segment_csr over the
         # shard's own row range (1.25M rows), scatter over all 10M destination rows (the full-length partial
-        # that the reduce-scatter would consume).  Row lengths: the log-normal recipe with mean 20.
+        # that the exchange would consume).  Row lengths: the log-normal recipe with mean 20.
         rows_csr, n_all, F = 1_250_000, 10_000_000, 128
         lens = row_lengths(rows_csr, SEED + 5, mean=20.0, force_long=8)
         indptr = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)]).to(dev)
@@ -523,12 +523,24 @@ def run_suite(args):
             nb = E * F * 2 + (rows_csr + 1) * 8 + rows_csr * F * 2
             ms, gbs = timeit(lambda: ts.segment_csr(src, indptr, reduce=reduce), nb, False)
             emit('C5', f'segment_csr {reduce} bf16 F=128, {rows_csr} rows / {E} edges (1/8 shard)', ms, gbs)
-        idx = torch.randint(0, n_all, (E,), device=dev, generator=g)
+        del indptr
+        # the shard's edges: every edge of the power-law graph (in-degree log-normal, mean 20, clip 20,000) lands on
+        # this GPU with probability 1/8, in random order
+        lens_all = row_lengths(n_all, SEED + 6, mean=20.0, force_long=8).to(dev)
+        lens_here = torch.binomial(lens_all.float(), torch.full((n_all,), 0.125, device=dev), generator=g).long()
+        idx = torch.repeat_interleave(torch.arange(n_all, device=dev), lens_here)
+        idx = idx[torch.randperm(idx.numel(), device=dev, generator=g)]
+        Es = idx.numel()
+        del lens_all, lens_here
+        if Es > E:
+            idx = idx[:E]
+            Es = E
+        src = src[:Es]
         for reduce in ('sum', 'max'):
-            nb = E * F * 2 + E * 8 + n_all * F * 2 + (n_all * F * 8 if reduce == 'max' else 0)
+            nb = Es * F * 2 + Es * 8 + n_all * F * 2 + (n_all * F * 8 if reduce == 'max' else 0)
             fn = getattr(ts, f'scatter_{reduce}')
             ms, gbs = timeit(lambda: fn(src, idx, 0, None, n_all), nb, False)
-            emit('C5', f'scatter {reduce} bf16 F=128, {E} edges -> {n_all} rows (1/8 shard, full-length partial)', ms, gbs)
+            emit('C5', f'scatter {reduce} bf16 F=128, {Es} edges -> {n_all} rows (1/8 shard of a power-law graph, full-length partial)', ms, gbs)
 
     if not only or 'C1' in only:
         c1()
