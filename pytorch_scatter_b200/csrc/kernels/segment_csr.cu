@@ -379,8 +379,10 @@ __global__ void __launch_bounds__(32, stream_ctas_per_sm<T, REDUCE, VEC>()) csr_
     auto close_rows = [&](const Pack<T, VEC> &v, int e, int id, int step_end) {
       while (cur_end <= step_end) {
         Acc tot = acc;
-        if (e >= cur_start && e < cur_end) tot.template update<INDIRECT>(v, id, kRelInf);
-        tot.butterfly(L, 32);
+        if (cur_end != cur_start) {  // warp-uniform; an empty row's accumulators are still the identity
+          if (e >= cur_start && e < cur_end) tot.template update<INDIRECT>(v, id, kRelInf);
+          tot.butterfly(L, 32);
+        }
         const int64_t row = r_win + cur;
         if (head_pending) {
           // the row started in an earlier chunk: leave its last piece for the fix-up kernel
