@@ -159,9 +159,13 @@ template <int VEC> __device__ __forceinline__ FloatRow<VEC> ld_float_row(const f
   return r;
 }
 
-// APPLY: src is an fp32 table and out[e] = op(x[e], src[index[e]]) (op 1: exp(x - row), 2: x - row).
-template <typename T, int VEC, bool APPLY>
+// MODE 0: plain gather.  1: src is an fp32 table and out[e] = op(x[e], src[index[e]]) (op 1: exp(x - row),
+// 2: x - row, 3: (x - row)^2).  2: the same times the gathered row of a second fp32 table (`scale`); a mode of its
+// own because as a run-time branch it cost the softmax passes a fifth of their speed.
+template <typename T, int VEC, int MODE>
 __global__ void __launch_bounds__(kThreads) gather_coo_kernel(GatherCooParams p) {
+  constexpr bool APPLY = MODE >= 1;
+  constexpr bool SCALED = MODE == 2;
   using Row = typename std::conditional<APPLY, FloatRow<VEC>, Pack<T, VEC>>::type;
   const T *__restrict__ src = static_cast<const T *>(p.src);
   const float *__restrict__ table = static_cast<const float *>(p.src);
@@ -224,12 +228,12 @@ __global__ void __launch_bounds__(kThreads) gather_coo_kernel(GatherCooParams p)
               Pack<T, VEC> o;
 #pragma unroll
               FloatRow<VEC> w;
-              if (p.scale != nullptr) w = ld_float_row<VEC>(p.scale + r[u] * p.K + c * VEC);  // row just fetched: L1/L2
+              if constexpr (SCALED) w = ld_float_row<VEC>(p.scale + r[u] * p.K + c * VEC);  // the table row's neighbour in time: L1/L2
 #pragma unroll
               for (int k = 0; k < VEC; ++k) {
                 const float d = (float)to_acc<T>(xv[u].v[k]) - v[u].v[k];
                 float y = p.op == 1 ? __expf(d) : (p.op == 3 ? d * d : d);
-                if (p.scale != nullptr) y *= w.v[k];
+                if constexpr (SCALED) y *= w.v[k];
                 o.v[k] = from_acc<T>((acc_t<T>)y);
               }
               st_stream<T, VEC>(out + at, o);
@@ -248,7 +252,7 @@ __global__ void __launch_bounds__(kThreads) gather_coo_kernel(GatherCooParams p)
   }
 }
 
-template <typename T, bool APPLY>
+template <typename T, int MODE>
 int launch_gather_coo(GatherCooParams p, cudaStream_t stream) {
   constexpr int kFull = full_vec<T>();
   const int64_t entries = p.B * p.E;
@@ -260,8 +264,8 @@ int launch_gather_coo(GatherCooParams p, cudaStream_t stream) {
   const int64_t per_cta = (int64_t)(kThreads / 32) * 32 * kGatherBatches;
   const int64_t blocks = (entries + per_cta - 1) / per_cta;
   if (blocks > 2147483647LL) return TSB_ERR_TOO_LARGE;
-  if (vec_ok) gather_coo_kernel<T, kFull, APPLY><<<(unsigned)blocks, kThreads, 0, stream>>>(p);
-  else gather_coo_kernel<T, 1, APPLY><<<(unsigned)blocks, kThreads, 0, stream>>>(p);
+  if (vec_ok) gather_coo_kernel<T, kFull, MODE><<<(unsigned)blocks, kThreads, 0, stream>>>(p);
+  else gather_coo_kernel<T, 1, MODE><<<(unsigned)blocks, kThreads, 0, stream>>>(p);
   return launch_status();
 }
 
@@ -313,7 +317,7 @@ extern "C" int tsb_gather_coo(const void *src, const int64_t *index, void *out, 
   p.x = nullptr; p.op = 0; p.scale = nullptr;
   p.B = B; p.E = E; p.K = K; p.N = N; p.bstride = index_batch_stride; p.l_log2 = 0;
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
-    return launch_gather_coo<scalar_t, false>(p, reinterpret_cast<cudaStream_t>(stream));
+    return launch_gather_coo<scalar_t, 0>(p, reinterpret_cast<cudaStream_t>(stream));
   });
 }
 
@@ -337,9 +341,14 @@ extern "C" int tsb_gather_coo_apply2(const void *x, const void *table, const voi
   p.x = x; p.op = op; p.scale = static_cast<const float *>(scale);
   p.B = B; p.E = E; p.K = K; p.N = N; p.bstride = index_batch_stride; p.l_log2 = 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (dtype == TSB_F32) return launch_gather_coo<float, true>(p, s);
-  if (dtype == TSB_F16) return launch_gather_coo<__half, true>(p, s);
-  return launch_gather_coo<__nv_bfloat16, true>(p, s);
+  if (scale != nullptr) {
+    if (dtype == TSB_F32) return launch_gather_coo<float, 2>(p, s);
+    if (dtype == TSB_F16) return launch_gather_coo<__half, 2>(p, s);
+    return launch_gather_coo<__nv_bfloat16, 2>(p, s);
+  }
+  if (dtype == TSB_F32) return launch_gather_coo<float, 1>(p, s);
+  if (dtype == TSB_F16) return launch_gather_coo<__half, 1>(p, s);
+  return launch_gather_coo<__nv_bfloat16, 1>(p, s);
 }
 
 extern "C" int tsb_arg_backward(const void *grad_out, const int64_t *arg, void *grad_in, int64_t B,

@@ -16,24 +16,37 @@ namespace tsb {
 namespace {
 
 // rowptr[r] = first position e with index[e] >= r, for r in [0, N]; equals E when no such e.
+// A thread looks at kRowptrItems consecutive entries of one batch (and the entry before them).
+constexpr int kRowptrItems = 4;
+
 __global__ void __launch_bounds__(kThreads)
 coo_rowptr_kernel(const int64_t *__restrict__ index, int64_t *__restrict__ rowptr, int64_t B, int64_t E,
                   int64_t N, int64_t bstride) {
-  const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-  if (i >= B * E) return;
-  const int64_t b = i / E, e = i - b * E;
+  const int64_t per_batch = (E + kRowptrItems - 1) / kRowptrItems;  // threads per batch
+  const int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (t >= B * per_batch) return;
+  const int64_t b = (B == 1) ? 0 : t / per_batch;
+  const int64_t e0 = (t - b * per_batch) * kRowptrItems;
   const int64_t *ix = index + b * bstride;
   int64_t *rp = rowptr + b * (N + 1);
-  const int64_t cur = ix[e];
-  const int64_t prev = e > 0 ? ix[e - 1] : -1;
-  if (cur > prev) {
-    const int64_t lo = prev + 1 > 0 ? prev + 1 : 0;
-    const int64_t hi = cur < N ? cur : N;
-    for (int64_t r = lo; r <= hi; ++r) rp[r] = e;
-  }
-  if (e == E - 1) {
-    const int64_t lo = cur + 1 > 0 ? cur + 1 : 0;
-    for (int64_t r = lo; r <= N; ++r) rp[r] = E;
+  int64_t v[kRowptrItems + 1];
+  v[0] = e0 > 0 ? ix[e0 - 1] : -1;
+#pragma unroll
+  for (int j = 0; j < kRowptrItems; ++j) v[j + 1] = e0 + j < E ? ix[e0 + j] : v[j];  // past the end: no new run
+#pragma unroll
+  for (int j = 0; j < kRowptrItems; ++j) {
+    const int64_t e = e0 + j;
+    if (e >= E) break;
+    const int64_t cur = v[j + 1], prev = v[j];
+    if (cur > prev) {
+      const int64_t lo = prev + 1 > 0 ? prev + 1 : 0;
+      const int64_t hi = cur < N ? cur : N;
+      for (int64_t r = lo; r <= hi; ++r) rp[r] = e;
+    }
+    if (e == E - 1) {
+      const int64_t lo = cur + 1 > 0 ? cur + 1 : 0;
+      for (int64_t r = lo; r <= N; ++r) rp[r] = E;
+    }
   }
 }
 
@@ -74,7 +87,7 @@ extern "C" int tsb_segment_coo(const void *src, const int64_t *index, void *out,
   if (E == 0) {
     if (cudaMemsetAsync(rowptr, 0, rowptr_bytes(B, N), stream) != cudaSuccess) return TSB_ERR_LAUNCH;
   } else {
-    const int64_t blocks = (B * E + kThreads - 1) / kThreads;
+    const int64_t blocks = (B * ((E + kRowptrItems - 1) / kRowptrItems) + kThreads - 1) / kThreads;
     if (blocks > 2147483647LL) return TSB_ERR_TOO_LARGE;
     coo_rowptr_kernel<<<(unsigned)blocks, kThreads, 0, stream>>>(index, rowptr, B, E, N, index_batch_stride);
     if (launch_status() != TSB_OK) return TSB_ERR_LAUNCH;
