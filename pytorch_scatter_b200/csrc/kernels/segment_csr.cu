@@ -379,7 +379,8 @@ __global__ void __launch_bounds__(32, stream_ctas_per_sm<T, REDUCE, VEC>()) csr_
     auto close_rows = [&](const Pack<T, VEC> &v, int e, int id, int step_end) {
       while (cur_end <= step_end) {
         Acc tot = acc;
-        if (cur_end != cur_start) {  // warp-uniform; an empty row's accumulators are still the identity
+        if (kArg || cur_end != cur_start) {  // warp-uniform; an empty row's accumulators are still the identity
+                                               // (MIN/MAX keep the plain path: the extra branch cost them 3-8 %)
           if (e >= cur_start && e < cur_end) tot.template update<INDIRECT>(v, id, kRelInf);
           tot.butterfly(L, 32);
         }
