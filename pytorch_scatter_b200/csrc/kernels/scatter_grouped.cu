@@ -149,12 +149,16 @@ bucket_hist_kernel(const int64_t *__restrict__ index, int64_t E, int64_t N, int 
   for (int b = threadIdx.x; b < P; b += kThreads) s_hist[b] = 0;
   __syncthreads();
   const int64_t first = (int64_t)blockIdx.x * (kThreads * 64);
-  for (int j = 0; j < 64; ++j) {
-    const int64_t e = first + (int64_t)j * kThreads + threadIdx.x;
-    if (e < E) {
-      const int64_t t = __ldcs(index + e);
-      if (t >= 0 && t < N) atomicAdd(&s_hist[(int)(t >> shift)], 1);
+  for (int j0 = 0; j0 < 64; j0 += 8) {  // eight independent loads in flight, then their eight updates
+    int64_t t[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int64_t e = first + (int64_t)(j0 + j) * kThreads + threadIdx.x;
+      t[j] = e < E ? __ldcs(index + e) : -1;
     }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (t[j] >= 0 && t[j] < N) atomicAdd(&s_hist[(int)(t[j] >> shift)], 1);
   }
   __syncthreads();
   for (int b = threadIdx.x; b < P; b += kThreads)
