@@ -31,10 +31,6 @@ FEAT = 64
 SEED = 20240602
 METRIC = 'segment_csr+scatter sum effective HBM bandwidth (F=64, fp32, power-law CSR)'
 UNIT = 'GB/s'
-# Per-launch DRAM traffic of csr_stream_kernel on the full workload (dram__bytes_read.sum 4341.2 MB +
-# dram__bytes_write.sum 270.5 MB, 1-pass ncu capture summarised in
-# profiles/bench_launch_list_csr_scatter_F64_fp32.md); the algorithmic bytes are 4603.0 MB.
-CSR_KERNEL_DRAM_TRAFFIC_BYTES = 4_611_700_000
 
 
 def row_lengths(rows, seed, force_long=8, mean=16.0):
@@ -67,6 +63,22 @@ def algorithmic_bytes(rows, nnz, feat=FEAT, s=4):
     csr = nnz * feat * s + (rows + 1) * 8 + rows * feat * s
     scatter = nnz * feat * s + nnz * 8 + rows * feat * s
     return csr, scatter
+
+
+def profiled_dram_bytes(name):
+    """DRAM bytes per launch of one kernel as ncu counted them (dram__bytes_read.sum + dram__bytes_write.sum), from the
+    line `dram_bytes_per_launch <name> <bytes> <entries>` of the committed launch-list summary, together with the
+    entry count of the captured launch (traffic grows in proportion to it).  (None, None) if there is no such line."""
+    path = osp.join(ROOT, 'profiles', 'bench_launch_list_csr_scatter_F64_fp32.md')
+    try:
+        with open(path) as f:
+            for ln in f:
+                parts = ln.split()
+                if len(parts) >= 4 and parts[0] == 'dram_bytes_per_launch' and parts[1] == name:
+                    return int(parts[2]), int(parts[3])
+    except OSError:
+        pass
+    return None, None
 
 
 class ClockSampler:
@@ -179,10 +191,201 @@ def run_reference(args):
 
 
 # -------------------------------------------------------------------------------------------------
+def sharded_workload(world, rank, dev):
+    """This rank's shard of ONE global problem, materialised on its device only.
+
+    Global problem: world x 1,048,576 CSR rows whose lengths come from a single seed (at world == 1 exactly the
+    single-GPU workload).  segment_csr: the rows are cut into `world` contiguous ranges holding about the same number of
+    entries (`balanced_row_cuts`); rank r reduces range r, no collective.  scatter: the same entries as an unsorted edge
+    list into 1,048,576 target rows (target = global row id modulo 1,048,576, so every rank's edges cover all targets
+    with the single-GPU degree distribution; globally a graph whose mean in-degree grows with `world`); rank r holds the
+    edges of its CSR range in shuffled order, reduces them for ALL target rows and the exchange leaves it with its
+    block of 1,048,576 / world rows."""
+    from pytorch_scatter_b200.dist import balanced_row_cuts
+    lens = row_lengths(world * ROWS, SEED, force_long=8 * world)
+    indptr_g = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)])
+    cuts = balanced_row_cuts(indptr_g, world)
+    lo, hi = int(cuts[rank]), int(cuts[rank + 1])
+    e_lo, e_hi = int(indptr_g[lo]), int(indptr_g[hi])
+    nnz_all = [int(indptr_g[cuts[r + 1]] - indptr_g[cuts[r]]) for r in range(world)]
+    indptr = (indptr_g[lo:hi + 1] - e_lo).to(dev)
+    g = torch.Generator(device=dev).manual_seed(SEED + 1 + rank)
+    sorted_index = torch.repeat_interleave(torch.arange(lo, hi, device=dev), lens[lo:hi].to(dev))
+    targets = sorted_index % ROWS
+    shuffled = targets[torch.randperm(e_hi - e_lo, device=dev, generator=g)]
+    src = torch.randn(e_hi - e_lo, FEAT, device=dev, generator=g)
+    return {'indptr': indptr, 'sorted_local': sorted_index - lo, 'shuffled': shuffled, 'src': src, 'rows': hi - lo,
+            'nnz': e_hi - e_lo, 'nnz_all': nnz_all, 'rows_all': [int(cuts[r + 1] - cuts[r]) for r in range(world)]}
+
+
+def check_results(ts, w, world, rank, dev, scatter_step):
+    """After the timed region: both operators once more, compared with float64 results computed by ATen on the device
+    (`index_add_`).  segment_csr: this rank's rows.  scatter: this rank's block of target rows against the same block
+    of an NCCL reduce-scatter of the ranks' float64 partials.  Tolerance: |error| <= 1e-5 x the sum of |terms| behind
+    an output (an fp32 sum in any order stays inside it).  Returns (csr worst error / bound, scatter worst, ok)."""
+    import torch.distributed as dist
+    src, rows = w['src'], w['rows']
+    s64 = src.double()
+    want = torch.zeros(rows, FEAT, dtype=torch.float64, device=dev).index_add_(0, w['sorted_local'], s64)
+    mass = torch.zeros(rows, FEAT, dtype=torch.float64, device=dev).index_add_(0, w['sorted_local'], s64.abs())
+    got = ts.segment_csr(src, w['indptr'], reduce='sum')
+    csr_ratio = float(((got.double() - want).abs() / (1e-5 * mass + 1e-30)).max())
+    del want, mass, got
+    per = -(-ROWS // world)
+    want = torch.zeros(per * world, FEAT, dtype=torch.float64, device=dev).index_add_(0, w['shuffled'], s64)
+    mass = torch.zeros(per * world, FEAT, dtype=torch.float64, device=dev).index_add_(0, w['shuffled'], s64.abs_())
+    del s64
+    if world > 1:
+        want_b, mass_b = torch.empty(per, FEAT, dtype=torch.float64, device=dev), torch.empty(per, FEAT, dtype=torch.float64, device=dev)
+        dist.reduce_scatter_tensor(want_b, want)
+        dist.reduce_scatter_tensor(mass_b, mass)
+        want, mass = want_b, mass_b
+    got = scatter_step(src, w['shuffled'])
+    valid = min(max(ROWS - rank * per, 0), per)
+    sc_ratio = float(((got[:valid].double() - want[:valid]).abs() / (1e-5 * mass[:valid] + 1e-30)).max())
+    if got.size(0) > valid:   # padding rows of the last block stay zero
+        sc_ratio = max(sc_ratio, float('inf') if bool((got[valid:] != 0).any()) else 0.0)
+    worst = torch.tensor([csr_ratio, sc_ratio], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    csr_ratio, sc_ratio = float(worst[0]), float(worst[1])
+    return csr_ratio, sc_ratio, bool(csr_ratio <= 1.0 and sc_ratio <= 1.0)
+
+
+C5_NODES, C5_EDGES, C5_FEAT = 10_000_000, 200_000_000, 128
+
+
+def c5_lengths(nodes=C5_NODES, edges=C5_EDGES, seed=SEED + 5):
+    """In-degrees of the GNN-scale graph: the log-normal recipe with mean 20 (clip 20,000), rescaled to exactly
+    `edges` edges."""
+    lens = row_lengths(nodes, seed, mean=20.0, force_long=8)
+    lens = (lens.double() * (edges / int(lens.sum()))).floor().long().clamp_(max=20000)
+    diff = edges - int(lens.sum())
+    if diff > 0:
+        lens[torch.nonzero(lens < 20000).view(-1)[:diff]] += 1
+    elif diff < 0:
+        lens[torch.nonzero(lens > 0).view(-1)[:-diff]] -= 1
+    assert int(lens.sum()) == edges
+    return lens
+
+
+def run_c5(ts, world, rank, dev, steps):
+    """GNN-scale aggregation, ONE global problem at every GPU count (strong scaling): 10 M destination nodes, 200 M
+    edges, bf16 messages [200 M x 128].  segment_csr sum / mean over nnz-balanced contiguous row ranges (no collective);
+    scatter sum of the shuffled edge list, edge-sharded, with the exchange of the benchmark's scatter.  Messages are
+    generated on the device, shard by shard (51 GB do not pass through the host).  Returns the `c5` block of the line."""
+    import torch.distributed as dist
+    from pytorch_scatter_b200.dist import balanced_row_cuts, routed_exchange_available, scatter_sum_overlapped, scatter_sum_routed
+    nodes, E, F = C5_NODES, C5_EDGES, C5_FEAT
+    lens = c5_lengths()
+    indptr_g = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)])
+    cuts = balanced_row_cuts(indptr_g, world)
+    lo, hi = int(cuts[rank]), int(cuts[rank + 1])
+    e_lo, e_hi = int(indptr_g[lo]), int(indptr_g[hi])
+    nnz_all = [int(indptr_g[cuts[r + 1]] - indptr_g[cuts[r]]) for r in range(world)]
+    n_here = e_hi - e_lo
+    g = torch.Generator(device=dev).manual_seed(SEED + 50 + rank)
+    src = torch.empty(n_here, F, dtype=torch.bfloat16, device=dev)
+    for c0 in range(0, n_here, 1 << 23):   # fp32 noise in pieces: no 100 GB temporary
+        c1 = min(n_here, c0 + (1 << 23))
+        src[c0:c1] = torch.randn(c1 - c0, F, device=dev, generator=g)
+    indptr = (indptr_g[lo:hi + 1] - e_lo).to(dev)
+    # the unsorted edge list: destinations of all edges in one global shuffled order (same seed on every rank),
+    # rank r holding the slice that matches its messages
+    g_all = torch.Generator(device=dev).manual_seed(SEED + 49)
+    dst = torch.repeat_interleave(torch.arange(nodes, device=dev), lens.to(dev))
+    order = torch.randperm(E, device=dev, generator=g_all)
+    index = dst[order[e_lo:e_hi]].clone()
+    sorted_local = (dst[e_lo:e_hi] - lo).clone()
+    del dst, order
+    torch.cuda.empty_cache()
+
+    routed = world > 1 and routed_exchange_available(src, nodes)
+
+    def scatter_op():
+        if world == 1:
+            return ts.scatter(src, index, dim=0, dim_size=nodes, reduce='sum')
+        if routed:
+            return scatter_sum_routed(src, index, nodes)
+        return scatter_sum_overlapped(src, index, nodes)
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    ms = {'segment_csr_sum': timed(lambda: ts.segment_csr(src, indptr, reduce='sum')),
+          'segment_csr_mean': timed(lambda: ts.segment_csr(src, indptr, reduce='mean')),
+          'scatter_sum': timed(scatter_op)}
+
+    # ---- checks on samples (bf16 bar: |error| <= 1e-2 |result| + 1e-2), float64 by ATen
+    def worst(got, want):
+        return float(((got.double() - want).abs() / (1e-2 * want.abs() + 1e-2)).max()) if got.numel() else 0.0
+
+    r0 = (hi - lo) // 3
+    r1 = min(hi - lo, r0 + 20000)
+    a, b = int(indptr[r0]), int(indptr[r1])
+    want = torch.zeros(r1 - r0, F, dtype=torch.float64, device=dev).index_add_(0, sorted_local[a:b] - r0, src[a:b].double())
+    csr_ratio = worst(ts.segment_csr(src, indptr, reduce='sum')[r0:r1], want)
+    cnt = (indptr[r0 + 1:r1 + 1] - indptr[r0:r1]).clamp(min=1).double().view(-1, 1)
+    mean_ratio = worst(ts.segment_csr(src, indptr, reduce='mean')[r0:r1], want / cnt)
+    sample = torch.randperm(nodes, generator=torch.Generator().manual_seed(SEED + 51))[:50000].sort().values.to(dev)
+    lut = torch.full((nodes,), -1, dtype=torch.long, device=dev)
+    lut[sample] = torch.arange(sample.numel(), device=dev)
+    local = lut[index]
+    keep = torch.nonzero(local >= 0).view(-1)
+    want = torch.zeros(sample.numel(), F, dtype=torch.float64, device=dev).index_add_(0, local[keep], src[keep].double())
+    if world > 1:
+        dist.all_reduce(want)
+    got = scatter_op()
+    per = -(-nodes // world) if world > 1 else nodes
+    mine = (sample >= rank * per) & (sample < rank * per + got.size(0)) if world > 1 else torch.ones_like(sample, dtype=torch.bool)
+    sc_ratio = worst(got[sample[mine] - (rank * per if world > 1 else 0)], want[mine])
+    ratios = torch.tensor([csr_ratio, mean_ratio, sc_ratio], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ratios, op=dist.ReduceOp.MAX)
+    del src, index, got, want, lut
+    torch.cuda.empty_cache()
+
+    peaks_path = osp.join(ROOT, 'MEASURED_PEAKS.json')
+    peak = float(json.load(open(peaks_path))['hbm_gbs']) if osp.exists(peaks_path) else 6650.0
+    b_csr = E * F * 2 + (nodes + 1) * 8 + nodes * F * 2
+    b_sc = E * (F * 2 + 8) + nodes * F * 2
+
+    def entry(name, nbytes):
+        gbs = nbytes / (ms[name] * 1e-3) / 1e9
+        return {'ms': ms[name], 'GB/s': gbs, 'frac_of_peak_per_gpu': gbs / world / peak,
+                'elements_per_s': E * F / (ms[name] * 1e-3)}
+
+    return {'workload': f'{nodes} nodes / {E} edges (log-normal in-degree, mean 20, clip 20000), bf16 messages [{E} x {F}], '
+                        'one global problem at every GPU count (strong scaling)', 'n_gpus': world, 'steps': steps,
+            'shard_entries': nnz_all, 'nnz_imbalance_max_over_mean': max(nnz_all) / (E / world),
+            'exchange': ('peer stores from the reduction kernel' if routed else 'NCCL reduce-scatter per slice') if world > 1 else None,
+            'segment_csr_sum': entry('segment_csr_sum', b_csr), 'segment_csr_mean': entry('segment_csr_mean', b_csr),
+            'scatter_sum': entry('scatter_sum', b_sc),
+            'check': {'segment_csr_sum': float(ratios[0]), 'segment_csr_mean': float(ratios[1]), 'scatter_sum': float(ratios[2]),
+                      'what': 'worst |error| / (1e-2 |result| + 1e-2) over 20,000 rows per rank (csr) and 50,000 sampled '
+                              'target rows (scatter), against float64 index_add_', 'ok': bool((ratios <= 1.0).all())}}
+
+
 def run_ours(args):
     import torch.distributed as dist
     import pytorch_scatter_b200 as ts
-    from pytorch_scatter_b200.dist import routed_exchange_available, scatter_sum_overlapped, scatter_sum_routed
+    from pytorch_scatter_b200.dist import (ROUTED_PHASES, routed_exchange_available, scatter_sum_overlapped,
+                                            scatter_sum_routed)
 
     world = int(os.environ.get('WORLD_SIZE', '1'))
     rank = int(os.environ.get('RANK', '0'))
@@ -193,23 +396,19 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group('nccl', device_id=dev)
 
-    # weak scaling: every rank holds its own workload-sized shard (its own seed)
-    indptr_h, _, shuffled_h, src_h = make_workload(ROWS, SEED + 17 * rank)
-    nnz = src_h.size(0)
-    src_p, indptr_p, shuffled_p = src_h.pin_memory(), indptr_h.pin_memory(), shuffled_h.pin_memory()
-    src, indptr, shuffled = src_p.to(dev), indptr_p.to(dev), shuffled_p.to(dev)
-    out_csr = torch.empty(ROWS, FEAT, device=dev)
-
-    def step():
-        # CSR rows are independent: each rank reduces its own row range, no collective.
-        ts.segment_csr(src, indptr, out=out_csr, reduce='sum')
-        # Unsorted scatter shards the edge dimension: every rank reduces its edges into a full-length
-        # partial, then a reduce-scatter leaves each rank with its block of target rows.
-        scatter_step(src, shuffled)
+    w = sharded_workload(world, rank, dev)
+    src, indptr, shuffled, rows_here = w['src'], w['indptr'], w['shuffled'], w['rows']
+    nnz_all, rows_all = w['nnz_all'], w['rows_all']
+    src_p = torch.empty(src.shape, dtype=src.dtype).pin_memory()
+    indptr_p = torch.empty(indptr.shape, dtype=indptr.dtype).pin_memory()
+    shuffled_p = torch.empty(shuffled.shape, dtype=shuffled.dtype).pin_memory()
+    src_p.copy_(src), indptr_p.copy_(indptr), shuffled_p.copy_(shuffled)
+    out_csr = torch.empty(rows_here, FEAT, device=dev)
 
     exchange = {'kind': None}   # how the sharded scatter exchanges rows; decided by the first call
+    timeline = []               # CUDA events at the phase borders of the routed exchange (timed steps only)
 
-    def scatter_step(s, ix):
+    def scatter_step(s, ix, record=False):
         # Unsorted scatter shards the edge dimension.  One GPU: the plain operator.  Several: every rank reduces
         # its edges for all rows through one grouping and the kernel stores each finished row into its owner's
         # staging buffer over NVLink (peer stores), then the owners add the slabs.  If symmetric memory cannot be
@@ -222,7 +421,7 @@ def run_ours(args):
             else:
                 exchange['kind'] = 'NCCL reduce-scatter per output slice, overlapped with the next slice'
         if exchange['kind'].startswith('peer'):
-            return scatter_sum_routed(s, ix, ROWS)
+            return scatter_sum_routed(s, ix, ROWS, timeline=timeline if record else None)
         return scatter_sum_overlapped(s, ix, ROWS)
 
     def sync_all():
@@ -232,36 +431,45 @@ def run_ours(args):
             torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        step()
+        ts.segment_csr(src, indptr, out=out_csr, reduce='sum')
+        scatter_step(src, shuffled)
     sync_all()
 
     sampler = ClockSampler(dev)
     if rank == 0:
         sampler.start()
     stream = torch.cuda.current_stream()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3 * args.steps + 1)]
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
     ev[0].record(stream)
     for i in range(args.steps):
+        # CSR rows are independent: each rank reduces its own row range, no collective.
         ts.segment_csr(src, indptr, out=out_csr, reduce='sum')
-        ev[3 * i + 1].record(stream)
-        scatter_step(src, shuffled)
-        ev[3 * i + 2].record(stream)
-        ev[3 * i + 3].record(stream)
+        ev[2 * i + 1].record(stream)
+        scatter_step(src, shuffled, record=True)
+        ev[2 * i + 2].record(stream)
     sync_all()
     clocks = sampler.stop() if rank == 0 else None
 
     total_ms = ev[0].elapsed_time(ev[-1])
-    csr_ms = sum(ev[3 * i].elapsed_time(ev[3 * i + 1]) for i in range(args.steps)) / args.steps
-    sc_ms = sum(ev[3 * i + 1].elapsed_time(ev[3 * i + 2]) for i in range(args.steps)) / args.steps
-    coll_ms = sum(ev[3 * i + 2].elapsed_time(ev[3 * i + 3]) for i in range(args.steps)) / args.steps
+    csr_ms = sum(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(args.steps)) / args.steps
+    sc_ms = sum(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps)) / args.steps
+    n_ph = len(ROUTED_PHASES)
+    phase_ms = [0.0] * n_ph
+    if timeline:
+        per_call = n_ph + 1
+        calls = len(timeline) // per_call
+        for c in range(calls):
+            for k in range(n_ph):
+                phase_ms[k] += timeline[c * per_call + k].elapsed_time(timeline[c * per_call + k + 1]) / calls
 
     # ---- end to end through the public API with host buffers: every step copies its inputs from pinned
     # host memory, runs both operators and copies both results back to pinned host memory, all inside
     # the timed region.  The three stages run on three streams with two sets of device input buffers,
     # so step i's read-back and step i+1's upload share the PCIe link's two directions.
     e2e_steps = max(1, min(args.steps, 5))
-    out_csr_h = torch.empty(ROWS, FEAT).pin_memory()
-    out_sc_h = torch.empty(ROWS, FEAT).pin_memory()
+    per = -(-ROWS // world)
+    out_csr_h = torch.empty(rows_here, FEAT).pin_memory()
+    out_sc_h = [None]         # pinned landing buffer of the scatter result, sized by the first (untimed) step
     in_bufs = [(torch.empty_like(src), torch.empty_like(indptr), torch.empty_like(shuffled)) for _ in range(2)]
     up_s, down_s = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     consumed = [None, None]   # per buffer set: the step that last read it has finished computing
@@ -284,7 +492,9 @@ def run_ours(args):
         consumed[i % 2].record(stream)
         with torch.cuda.stream(down_s):
             down_s.wait_event(consumed[i % 2])
-            out_sc_h[:o2.size(0)].copy_(o2, non_blocking=True)
+            if out_sc_h[0] is None:
+                out_sc_h[0] = torch.empty(o2.shape, dtype=o2.dtype).pin_memory()
+            out_sc_h[0].copy_(o2, non_blocking=True)
             out_csr_h.copy_(o1, non_blocking=True)
             o1.record_stream(down_s)
             o2.record_stream(down_s)
@@ -308,21 +518,30 @@ def run_ours(args):
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
     del in_bufs
 
-    # ---- max over ranks
-    times = torch.tensor([total_ms, csr_ms, sc_ms, coll_ms, e2e_ms, float(nnz)], device=dev, dtype=torch.float64)
+    # ---- what was timed is also checked (untimed)
+    csr_ratio, sc_ratio, ok = check_results(ts, w, world, rank, dev, scatter_step)
+
+    # ---- the GNN-scale configuration (bf16 F=128, 10 M nodes / 200 M edges) at this GPU count, untimed by the metric
+    del src, indptr, shuffled, out_csr
+    w.clear()
+    torch.cuda.empty_cache()
+    c5 = None if args.no_c5 else run_c5(ts, world, rank, dev, max(3, min(args.steps, 10)))
+
+    # ---- max (and mean) over ranks
+    times = torch.tensor([total_ms, csr_ms, sc_ms, e2e_ms] + phase_ms, device=dev, dtype=torch.float64)
     if world > 1:
         gathered = [torch.empty_like(times) for _ in range(world)]
         dist.all_gather(gathered, times)
         allt = torch.stack(gathered)
     else:
         allt = times.unsqueeze(0)
-    total_ms, csr_ms, sc_ms, coll_ms, e2e_ms = [float(allt[:, i].max()) for i in range(5)]
-    nnz_all = [int(x) for x in allt[:, 5].tolist()]
+    total_ms, csr_ms, sc_ms, e2e_ms = [float(allt[:, i].max()) for i in range(4)]
 
     if rank == 0:
-        scatter_passes = -(-(ROWS * FEAT * 4) // (128 << 20))  # 128 MiB output slices
-        b = [algorithmic_bytes(ROWS, n) for n in nnz_all]
-        b_csr, b_sc = sum(x[0] for x in b), sum(x[1] for x in b)
+        nnz_total = sum(nnz_all)
+        # the global problem's bytes: every tensor counted once (the scatter's output exists once, on its owners)
+        b_csr = nnz_total * FEAT * 4 + (sum(rows_all) + 1) * 8 + sum(rows_all) * FEAT * 4
+        b_sc = nnz_total * (FEAT * 4 + 8) + ROWS * FEAT * 4
         ms_per_step = total_ms / args.steps
         value = (b_csr + b_sc) / (ms_per_step * 1e-3) / 1e9
         peaks_path = osp.join(ROOT, 'MEASURED_PEAKS.json')
@@ -330,41 +549,75 @@ def run_ours(args):
             peak, peak_src = float(json.load(open(peaks_path))['hbm_gbs']), 'measured (MEASURED_PEAKS.json hbm_gbs)'
         else:
             peak, peak_src = 6650.0, 'fallback'
-        csr_gbs = b[0][0] / (csr_ms * 1e-3) / 1e9          # rank-0-sized launch over the slowest rank's time
-        sc_gbs = b[0][1] / (sc_ms * 1e-3) / 1e9
-        h2d = src_h.numel() * 4 + indptr_h.numel() * 8 + shuffled_h.numel() * 8
-        d2h = ROWS * FEAT * 4 + -(-ROWS // world) * FEAT * 4
+        # per-GPU figures: the largest shard's own bytes over the slowest rank's time
+        big = max(range(world), key=lambda r: nnz_all[r])
+        b0_csr, b0_sc = algorithmic_bytes(rows_all[big], nnz_all[big])
+        b0_sc = nnz_all[big] * (FEAT * 4 + 8) + per * FEAT * 4 if world > 1 else b0_sc
+        csr_gbs = b0_csr / (csr_ms * 1e-3) / 1e9
+        sc_gbs = b0_sc / (sc_ms * 1e-3) / 1e9
+        h2d = nnz_all[0] * FEAT * 4 + (rows_all[0] + 1) * 8 + nnz_all[0] * 8
+        d2h = rows_all[0] * FEAT * 4 + (per if world > 1 else ROWS) * FEAT * 4
+        routed = world > 1 and exchange['kind'].startswith('peer')
+        scatter_passes = -(-(ROWS * FEAT * 4) // (128 << 20))  # 128 MiB output slices (NCCL variant)
+
+        def traffic_of(kernel, entries):
+            t, e = profiled_dram_bytes(kernel)
+            return None if t is None else int(round(t * entries / e))
+
         line = {
             'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
             'warmup': args.warmup, 'ms_per_step': ms_per_step, 'higher_is_better': True, 'scaling': 'weak',
             'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
-            'config': {'workload': f'power-law CSR: {ROWS} rows, {nnz_all[0]} entries per GPU (log-normal row '
-                                   f'lengths, mean 16, clip 20000, 8 rows forced to 20000), src fp32 [nnz x {FEAT}], '
-                                   'int64 indptr/index; step = segment_csr(sum) + scatter(sum, shuffled index)'
+            'elements_per_s': 2 * nnz_total * FEAT / (ms_per_step * 1e-3),
+            'config': {'workload': f'power-law CSR: ONE problem of {world} x {ROWS} rows / {nnz_total} entries (log-normal row '
+                                   f'lengths, mean 16, clip 20000, {8 * world} rows forced to 20000), src fp32 [nnz x {FEAT}], '
+                                   'int64 indptr/index; step = segment_csr(sum) over nnz-balanced contiguous row ranges + '
+                                   f'scatter(sum) of the same entries (shuffled) into {ROWS} target rows'
                                    + (f'; exchange: {exchange["kind"]}' if world > 1 else ''),
-                       'l2': 'inputs (4.3 GB) larger than L2, no flush needed',
-                       'parallelism': f'{world} x independent row shards (csr); edge shards + reduce-scatter (scatter)'},
-            'ops': {'segment_csr_sum': {'ms': csr_ms, 'GB/s': csr_gbs, 'frac_of_peak': csr_gbs / peak},
-                    'scatter_sum': {'ms': sc_ms, 'GB/s': sc_gbs, 'frac_of_peak': sc_gbs / peak},
+                       'l2': 'inputs (4.3 GB per GPU) larger than L2, no flush needed',
+                       'parallelism': f'{world} x nnz-balanced row ranges, no collective (csr); edge shards + exchange (scatter)',
+                       'shard_entries': nnz_all, 'shard_rows': rows_all,
+                       'nnz_imbalance_max_over_mean': max(nnz_all) / (nnz_total / world)},
+            'ops': {'segment_csr_sum': {'ms': csr_ms, 'GB/s': csr_gbs, 'frac_of_peak': csr_gbs / peak,
+                                        'elements_per_s': nnz_all[big] * FEAT / (csr_ms * 1e-3)},
+                    'scatter_sum': {'ms': sc_ms, 'GB/s': sc_gbs, 'frac_of_peak': sc_gbs / peak,
+                                    'elements_per_s': nnz_all[big] * FEAT / (sc_ms * 1e-3)},
                     'collective': f'inside scatter_sum ({exchange["kind"]})' if world > 1 else None},
-            'roofline': {'bound': 'hbm', 'kernel': 'csr_stream_kernel<float,sum,VEC=4>', 'achieved': csr_gbs, 'peak': peak,
-                         'unit': 'GB/s', 'frac': csr_gbs / peak, 'traffic': CSR_KERNEL_DRAM_TRAFFIC_BYTES,
-                         'peak_source': peak_src, 'algorithmic_bytes_per_launch': b[0][0]},
+            'roofline': {'bound': 'hbm', 'kernel': 'csr_stream_kernel<float,sum,VEC=4> (+ csr_fixup_kernel), segment_csr',
+                         'achieved': csr_gbs, 'peak': peak, 'unit': 'GB/s', 'frac': csr_gbs / peak,
+                         'traffic': traffic_of('csr_stream_kernel_contiguous', nnz_all[big]),
+                         'peak_source': peak_src, 'algorithmic_bytes_per_launch': b0_csr},
+            'roofline_scatter': {'bound': 'hbm', 'kernel': 'scatter(sum): bucket_hist/scan/partition/finalize + '
+                                                           'csr_stream_kernel<float,sum,VEC=4,perm> + csr_fixup_kernel'
+                                                           + (' + sum_slabs_kernel' if routed else ''),
+                                 'achieved': sc_gbs, 'peak': peak, 'unit': 'GB/s', 'frac': sc_gbs / peak,
+                                 'traffic': traffic_of('scatter_all_kernels', nnz_all[big]),
+                                 'peak_source': peak_src, 'algorithmic_bytes_per_launch': b0_sc},
             'e2e': {'value': (b_csr + b_sc) / (e2e_ms * 1e-3) / 1e9, 'unit': UNIT, 'ms_per_step': e2e_ms,
                     'steps': e2e_steps, 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h},
+            'check': {'csr_max_err_over_bound': csr_ratio, 'scatter_max_err_over_bound': sc_ratio,
+                      'bound': '1e-5 x sum|terms| per output, against float64 index_add_ (N>1: reduce-scatter of the '
+                               'float64 partials)', 'ok': ok},
             # per step, segment_csr: csr_stream_kernel + csr_fixup_kernel.  scatter on one GPU (output larger
             # than L2: the grouped path): bucket_hist, bucket_scan, bucket_partition, bucket_finalize, then
             # csr_stream_kernel + csr_fixup_kernel through the permutation.  Several GPUs with the routed exchange:
             # the same plus sum_slabs_kernel; with the NCCL variant: the grouping once plus stream + fix-up per slice.
-            'gpu_launches': ((2 + 6) if world == 1 else (2 + 6 + 1) if exchange['kind'].startswith('peer')
-                             else (2 + 4 + 2 * scatter_passes)) * args.steps,
+            'gpu_launches': ((2 + 6) if world == 1 else (2 + 6 + 1) if routed else (2 + 4 + 2 * scatter_passes)) * args.steps,
             'clocks': clocks,
         }
+        if routed:
+            line['ops']['scatter_phases_ms'] = {
+                name: {'max': float(allt[:, 4 + k].max()), 'mean': float(allt[:, 4 + k].mean())}
+                for k, name in enumerate(ROUTED_PHASES)}
+        if c5 is not None:
+            line['c5'] = c5
         if world == 1 and not args.no_cpu_baseline:
             line['cpu_baseline'] = cpu_baseline(args)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if not ok or (c5 is not None and not c5['check']['ok']):
+        sys.exit(3)
 
 
 def cpu_baseline(args):
@@ -560,6 +813,7 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--ref-fraction', type=int, default=4, help='reference arm runs on 1/this of the rows')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-c5', action='store_true', help='skip the GNN-scale block (bf16 F=128, 10 M nodes / 200 M edges)')
     ap.add_argument('--suite', action='store_true', help='per-operator table over the other configurations')
     ap.add_argument('--suite-only', default='', help='comma-separated configs to run, e.g. C3,C4')
     ap.add_argument('--profile-op', choices=['csr', 'scatter'], default=None)

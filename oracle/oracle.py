@@ -27,7 +27,7 @@ def build():
     """Compile liboracle.so with gcc if it is missing or older than its source."""
     src = osp.join(_HERE, 'scatter_oracle.c')
     if not osp.exists(_LIB_PATH) or osp.getmtime(_LIB_PATH) < osp.getmtime(src):
-        subprocess.run([os.environ.get('CC', 'gcc'), '-O2', '-std=c11', '-fPIC', '-shared', '-o', _LIB_PATH, src, '-lm'],
+        subprocess.run([os.environ.get('CC', 'gcc'), '-O3', '-std=c11', '-fPIC', '-shared', '-o', _LIB_PATH, src, '-lm'],
                        check=True)
     return _LIB_PATH
 

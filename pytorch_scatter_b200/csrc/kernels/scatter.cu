@@ -21,6 +21,7 @@
 // Replaces scatter_kernel / scatter_arg_kernel of the upstream project
 // (csrc/cuda/scatter_cuda.cu:13-56): one atomic per element, CAS loops for float MIN/MAX and all
 // 16-bit types, K redundant index loads per row and a racy arg pass.
+#include <atomic>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -711,16 +712,18 @@ __global__ void __launch_bounds__(kThreads) fill_i64_kernel(int64_t *p, int64_t 
 // ---- MIN / MAX with arg in ONE pass for 4-byte accumulation types --------------------------------
 // For fp32 / int32 values (fp16 / bf16 compare as fp32) the value's order-preserving 32-bit key and the
 // element's position are packed into one 64-bit word, so a single native 64-bit atomicMax / atomicMin
-// settles value and arg together: MAX keeps (key << 32 | ~pos), MIN keeps (key << 32 | pos), which on
-// equal values prefers the smaller position - the first-occurrence rule of the CPU loop
-// (csrc/cpu/reducer.h:63-67).  The int64 arg_out tensor itself holds the packed words until the
-// finalize kernel splits them, so the source is read once and no extra memory is needed.  Requires
-// E < 2^32 - 1; 8-byte types keep the two-pass scheme further down.
+// settles value and arg together.  The low word holds the position plus one ("slot"; 0 = no element):
+// MAX keeps (key << 32 | ~slot), MIN keeps (key << 32 | slot).  On equal values the smaller slot wins,
+// and slot 0 - the value `out` held before the call, or the identity - beats every element: the rule of
+// the CPU loop, whose strict comparison keeps what it already has (csrc/cpu/reducer.h:63-67), so a
+// source value equal to the one already in `out` leaves the arg at "none".  The int64 arg_out tensor
+// itself holds the packed words until the finalize kernel splits them, so the source is read once and
+// no extra memory is needed.  Requires E < 2^32 - 1; 8-byte types keep the two-pass scheme further down.
 constexpr uint64_t kNoPos = 0xffffffffull;
 
-template <int OP> __device__ __forceinline__ uint64_t pack_minmax(int32_t key, uint64_t pos) {
+template <int OP> __device__ __forceinline__ uint64_t pack_minmax(int32_t key, uint64_t slot) {
   const uint64_t ukey = (uint32_t)key ^ 0x80000000u;  // signed order -> unsigned order
-  return (ukey << 32) | (OP == kMax ? (kNoPos - pos) : pos);
+  return (ukey << 32) | (OP == kMax ? (kNoPos - slot) : slot);
 }
 template <int OP> __device__ __forceinline__ void atom_packed(uint64_t *addr, uint64_t v) {
   const uint64_t cur = *reinterpret_cast<volatile uint64_t *>(addr);  // filters updates that cannot win
@@ -737,17 +740,18 @@ __global__ void __launch_bounds__(kThreads) packed_init_kernel(const T *out, uin
   const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
   if (i >= total) return;
   const U v = fresh ? reduce_identity<T, OP>() : to_acc<T>(out[i]);
-  packed[i] = pack_minmax<OP>(enc_key(v), kNoPos);  // position "none"
+  packed[i] = pack_minmax<OP>(enc_key(v), 0);  // slot 0: no element
 }
 
-// One element: NaN never wins; on a write-only output a value equal to the identity never wins either
-// (the CPU loop compares strictly against the identity it started from).
+// One element: NaN never wins; a value equal to the identity (fresh output) or to the value already in
+// `out` never wins either, because slot 0 beats its slot on the equal key.
 template <typename T, int OP>
 __device__ __forceinline__ void packed_update(uint64_t *addr, T x, int64_t e, int fresh) {
   using U = acc_t<T>;
+  (void)fresh;
   const U v = to_acc<T>(x);
-  if (is_nan(v) || (fresh && v == reduce_identity<T, OP>())) return;
-  atom_packed<OP>(addr, pack_minmax<OP>(enc_key(v), (uint64_t)e));
+  if (is_nan(v)) return;
+  atom_packed<OP>(addr, pack_minmax<OP>(enc_key(v), (uint64_t)e + 1));
 }
 
 template <typename T, int OP, int VEC>
@@ -792,16 +796,49 @@ packed_finalize_kernel(T *out, int64_t *arg_out, int64_t total, int64_t E, int f
   const uint64_t w = reinterpret_cast<const uint64_t *>(arg_out)[i];
   const int32_t key = (int32_t)((uint32_t)(w >> 32) ^ 0x80000000u);
   U v = dec_key<U>(key);
-  uint64_t pos = w & kNoPos;
-  if (OP == kMax) pos = kNoPos - pos;
-  if (fresh && pos == kNoPos) v = (U)0;  // nothing won: the identity is masked to 0
+  uint64_t slot = w & kNoPos;
+  if (OP == kMax) slot = kNoPos - slot;
+  if (slot == 0) {  // no element won: a fresh output's identity is masked to 0, a seeded one keeps its value
+    if (fresh) out[i] = from_acc<T>((U)0);
+    arg_out[i] = E;
+    return;
+  }
   out[i] = from_acc<T>(v);
-  arg_out[i] = pos == kNoPos ? E : (int64_t)pos;
+  arg_out[i] = (int64_t)slot - 1;
 }
 
 // ---- arg pass ----------------------------------------------------------------------------------
 __device__ __forceinline__ void arg_min(int64_t *a, int64_t e) {
   if (e < *reinterpret_cast<volatile int64_t *>(a)) atomicMin(reinterpret_cast<long long *>(a), (long long)e);
+}
+
+// Seeded MIN/MAX (the caller passed `out`): the CPU loop's strict comparison lets the value already in `out` win a
+// tie and leaves its arg at "none" (csrc/cpu/reducer.h:63-67).  The seeds are kept in arg_out (as raw bits) while
+// the values are reduced; afterwards every target whose result equals its seed is closed to the arg pass with a
+// marker below every position, and a last pass turns the markers into "none".
+constexpr int64_t kSeedWon = -1;
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) seed_stash_kernel(const T *out, int64_t *arg_out, int64_t total) {
+  const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i >= total) return;
+  int64_t bits = 0;
+  const T v = out[i];
+  memcpy(&bits, &v, sizeof(T));
+  arg_out[i] = bits;
+}
+template <typename T>
+__global__ void __launch_bounds__(kThreads) seed_compare_kernel(const T *out, int64_t *arg_out, int64_t total, int64_t E) {
+  const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i >= total) return;
+  const int64_t bits = arg_out[i];
+  T seed;
+  memcpy(&seed, &bits, sizeof(T));
+  arg_out[i] = (to_acc<T>(out[i]) == to_acc<T>(seed)) ? kSeedWon : E;
+}
+__global__ void __launch_bounds__(kThreads) seed_close_kernel(int64_t *arg_out, int64_t total, int64_t E) {
+  const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i < total && arg_out[i] == kSeedWon) arg_out[i] = E;
 }
 
 template <typename T, int VEC>
@@ -861,7 +898,13 @@ __global__ void __launch_bounds__(kThreads) scatter_bw_rows_kernel(ScatterBwPara
   if (entry >= p.B * p.E) return;
   const int64_t b = entry / p.E, e = entry - b * p.E;
   const int64_t idx = p.index[b * p.sb + e * p.se];
-  if (idx < 0 || idx >= p.N) return;
+  if (idx < 0 || idx >= p.N) {  // the forward dropped this entry: its gradient is zero
+    Pack<T, VEC> zero;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) zero.v[i] = from_acc<T>((acc_t<T>)0);
+    for (int64_t c = col; c < Kv; c += L) st_stream<T, VEC>(gi + entry * p.K + c * VEC, zero);
+    return;
+  }
   int32_t cnt = 1;
   if (p.count != nullptr) {
     cnt = p.count[(p.sb ? b : 0) * p.N + idx];
@@ -886,7 +929,7 @@ __global__ void __launch_bounds__(kThreads) scatter_bw_elems_kernel(ScatterBwPar
   const int64_t k = i % p.K, be = i / p.K;
   const int64_t b = be / p.E, e = be - b * p.E;
   const int64_t idx = p.index[b * p.sb + e * p.se + k * p.sk];
-  if (idx < 0 || idx >= p.N) return;
+  if (idx < 0 || idx >= p.N) { gi[i] = from_acc<T>((acc_t<T>)0); return; }
   T v = go[(b * p.N + idx) * p.K + k];
   if (p.count != nullptr) {
     int32_t cnt = p.count[((p.sb ? b : 0) * p.N + idx) * (p.sk ? p.K : 1) + (p.sk ? k : 0)];
@@ -977,6 +1020,11 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
   }
 
   // 1. bring the target to its starting state
+  const bool seeded_minmax = kMinMax && !p.fresh && total > 0;
+  if (seeded_minmax) {
+    if (!grid_for(total, &blocks)) return TSB_ERR_TOO_LARGE;
+    seed_stash_kernel<T><<<blocks, kThreads, 0, stream>>>(static_cast<const T *>(p.out), p.arg_out, total);
+  }
   if (total > 0) {
     const bool need_init = k16 || kKeyed || p.fresh || replicas > 1;
     if (need_init) {
@@ -1027,16 +1075,14 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
           const int64_t row_bytes = p.K * (int64_t)sizeof(float);
           if (want && vec_ok && !sliced && row_bytes <= 256 && all_rows < (1ll << 31)) {
             int64_t tile = (p.B * p.E) / (148 * 8);
-            const int64_t tile_max = env_bytes("TSB_SCATTER_CACHE_TILE", 8192);  // tuning hooks
-            tile = tile < 1024 ? 1024 : (tile > tile_max ? tile_max : tile);
-            int64_t cache_bytes = env_bytes("TSB_SCATTER_CACHE_BYTES", 32 * 1024);
-            if (cache_bytes > kCacheBytesMax) cache_bytes = kCacheBytesMax;
+            tile = tile < 1024 ? 1024 : (tile > 8192 ? 8192 : tile);
+            const int64_t cache_bytes = 32 * 1024;
             int slots_log2 = 0;
             while ((2ll << slots_log2) * (row_bytes + 8) <= cache_bytes && (2ll << slots_log2) <= tile / 4) ++slots_log2;
             const int64_t tiles = (p.B * p.E + tile - 1) / tile;
             if (tiles <= 2147483647LL && slots_log2 >= 4) {
               const size_t smem = ((size_t)1 << slots_log2) * (size_t)(row_bytes + 8);
-              static bool allowed[64] = {false};
+              static std::atomic<bool> allowed[64];  // per device; setting the attribute twice is harmless
               int dev = 0;
               if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !allowed[dev]) {
                 if (cudaFuncSetAttribute(scatter_rows_cached_kernel<T, kFull>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1084,7 +1130,8 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
   // 4. arg pass
   if (kMinMax && total > 0) {
     if (!grid_for(total, &blocks)) return TSB_ERR_TOO_LARGE;
-    fill_i64_kernel<<<blocks, kThreads, 0, stream>>>(p.arg_out, total, p.E);
+    if (seeded_minmax) seed_compare_kernel<T><<<blocks, kThreads, 0, stream>>>(static_cast<const T *>(p.out), p.arg_out, total, p.E);
+    else fill_i64_kernel<<<blocks, kThreads, 0, stream>>>(p.arg_out, total, p.E);
     if (p.E > 0) {
       if (rows) {
         if (!grid_for((p.B * p.E) << p.l_log2, &blocks)) return TSB_ERR_TOO_LARGE;
@@ -1094,6 +1141,10 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
         if (!grid_for(p.B * p.E * p.K, &blocks)) return TSB_ERR_TOO_LARGE;
         scatter_arg_elems_kernel<T><<<blocks, kThreads, 0, stream>>>(p);
       }
+    }
+    if (seeded_minmax) {
+      if (!grid_for(total, &blocks)) return TSB_ERR_TOO_LARGE;
+      seed_close_kernel<<<blocks, kThreads, 0, stream>>>(p.arg_out, total, p.E);
     }
   }
   return launch_status();

@@ -21,6 +21,7 @@
 // (csrc/cuda/scatter_cuda.cu:13-56).
 #include "scatter_grouped.cuh"
 
+#include <atomic>
 #include <cstdlib>
 
 namespace tsb {
@@ -311,13 +312,9 @@ bucket_finalize_kernel(const int2 *__restrict__ pairs, const int32_t *__restrict
 // permutation fits the shared-memory stage.  shift < 0: the shapes do not fit (too many rows for
 // kMaxBuckets buckets of kMaxBucketRows rows) and the global-atomic kernels are used.
 struct BucketGeom { int shift, P; };
-int tuning(const char *name, int fallback) {  // tuning hooks, read per call
-  const char *v = std::getenv(name);
-  const int x = v != nullptr ? std::atoi(v) : 0;
-  return x > 0 ? x : fallback;
-}
+constexpr int kBucketEntries = 12288;  // entries a bucket should hold at least (measured: 8k-16k equal, 32k slower)
 BucketGeom bucket_geom(int64_t E, int64_t N) {
-  const int64_t want = ((int64_t)tuning("TSB_GROUPED_BUCKET_ENTRIES", 12288) * N) / (E > 0 ? E : 1);  // rows holding that many entries
+  const int64_t want = ((int64_t)kBucketEntries * N) / (E > 0 ? E : 1);  // rows holding that many entries
   int shift = 6;
   while ((1ll << shift) < want && (1 << shift) < kMaxBucketRows) ++shift;  // rounded up to a power of two
   while (((N + (1ll << shift) - 1) >> shift) > kMaxBuckets && (1 << shift) < kMaxBucketRows) ++shift;
@@ -328,15 +325,14 @@ BucketGeom bucket_geom(int64_t E, int64_t N) {
 
 // Shared memory above the 48 KiB default has to be allowed per kernel and device, once.
 int allow_bucket_smem() {
-  static bool done[64] = {false};
+  static std::atomic<bool> done[64];  // per device; setting the attributes twice is harmless
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TSB_ERR_LAUNCH;
   if (done[dev]) return TSB_OK;
   const int part = (3 * kMaxBuckets + 1) * (int)sizeof(int);
   const int pair = kPartThreads * (int)sizeof(int2);
   const int fin = kFinalSmemInts * (int)sizeof(int);
-  if (cudaFuncSetAttribute(bucket_partition_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, part + 8 * pair) != cudaSuccess ||
-      cudaFuncSetAttribute(bucket_partition_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, part + 16 * pair) != cudaSuccess ||
+  if (cudaFuncSetAttribute(bucket_partition_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, part + 16 * pair) != cudaSuccess ||
       cudaFuncSetAttribute(bucket_finalize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fin) != cudaSuccess)
     return TSB_ERR_LAUNCH;
   done[dev] = true;
@@ -419,18 +415,15 @@ int scatter_group(const int64_t *index, int64_t E, int64_t N, int64_t *rowptr, i
     int2 *pairs = reinterpret_cast<int2 *>(rank);
     const int P = geom.P, R = 1 << geom.shift;
     const int64_t hist_blocks = (E + kThreads * 64 - 1) / (kThreads * 64);
-    const int part_items = tuning("TSB_GROUPED_PART_ITEMS", 16) >= 16 ? 16 : 8;
+    constexpr int part_items = 16;
     const int part_tile = kPartThreads * part_items;
     const int64_t part_blocks = (E + part_tile - 1) / part_tile;
     if (cudaMemsetAsync(hist, 0, (size_t)P * sizeof(int32_t), stream) != cudaSuccess) return TSB_ERR_LAUNCH;
     bucket_hist_kernel<<<(unsigned)hist_blocks, kThreads, (size_t)P * sizeof(int), stream>>>(index, E, N, geom.shift, P, hist);
     bucket_scan_kernel<<<1, kThreads, 0, stream>>>(hist, P, start, cursor);
     const size_t part_smem = (size_t)(3 * P + (P & 1)) * sizeof(int) + (size_t)part_tile * sizeof(int2);
-    if (part_items == 16)
-      bucket_partition_kernel<16><<<(unsigned)part_blocks, kPartThreads, part_smem, stream>>>(index, E, N, geom.shift, P, start, cursor, pairs);
-    else
-      bucket_partition_kernel<8><<<(unsigned)part_blocks, kPartThreads, part_smem, stream>>>(index, E, N, geom.shift, P, start, cursor, pairs);
-    int stage = tuning("TSB_GROUPED_STAGE_ENTRIES", 24576);
+    bucket_partition_kernel<part_items><<<(unsigned)part_blocks, kPartThreads, part_smem, stream>>>(index, E, N, geom.shift, P, start, cursor, pairs);
+    int stage = 24576;
     if (stage > kStageEntries) stage = kStageEntries;
     if (stage > kFinalSmemInts - R) stage = kFinalSmemInts - R;
     const size_t fin_smem = (size_t)(R + stage) * sizeof(int);

@@ -59,10 +59,11 @@ struct CsrGeom {
 
 // Chunk length: a power of two holding about kChunkBytes of source, shortened (down to one full
 // warp step) when the whole reduced dimension would otherwise give too few chunks to occupy the GPU.
-// Entries narrow enough for csr_flat_kernel (K == 1 always; tuning hook TSB_CSR_FLAT_ROW_BYTES).
+// Entries narrow enough for csr_flat_kernel: K == 1; the test hook TSB_CSR_FORCE_FLAT=1 sends every entry of up
+// to 64 bytes through it.
 inline bool flat_rows(int64_t K, size_t elem) {
   int64_t limit = kFlatRowBytes;
-  if (const char *v = std::getenv("TSB_CSR_FLAT_ROW_BYTES")) limit = std::atoll(v);
+  if (const char *v = std::getenv("TSB_CSR_FORCE_FLAT")) limit = (*v == '1') ? 64 : limit;
   return K == 1 || K * (int64_t)elem <= limit;
 }
 
@@ -125,7 +126,7 @@ template <typename T, int REDUCE, int VEC, typename ArgT = int64_t> struct RowAc
         // reference, the other side is scaled by exp(-|x - m|).  The identity is the lowest finite float,
         // so the first entry gives exp(-huge) = 0 for the empty sum, and an entry of -inf adds 0.
         const float m = (float)val[i], xf = (float)x;
-        const float d = xf - m;
+        const float d = xf == m ? 0.0f : xf - m;  // equal infinities: inf - inf would be NaN, upstream gives +inf
         const float e = __expf(-fabsf(d));
         const float sum = sum_of(arg[i]);
         arg[i] = word_of(d > 0.0f ? fmaf(sum, e, 1.0f) : sum + e);
@@ -147,7 +148,7 @@ template <typename T, int REDUCE, int VEC, typename ArgT = int64_t> struct RowAc
         if (better || (oval[i] == val[i] && oarg[i] < arg[i])) { val[i] = oval[i]; arg[i] = oarg[i]; }
       } else {
         const float m1 = (float)val[i], m2 = (float)oval[i];
-        const float d = m2 - m1;
+        const float d = m2 == m1 ? 0.0f : m2 - m1;
         const float e = __expf(-fabsf(d));
         const float s1 = sum_of(arg[i]), s2 = sum_of(oarg[i]);
         arg[i] = word_of(d > 0.0f ? fmaf(s1, e, s2) : fmaf(s2, e, s1));

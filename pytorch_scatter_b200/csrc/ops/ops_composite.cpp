@@ -81,6 +81,16 @@ bool index_is_sorted(torch::Tensor index) {
   return flag.item<int32_t>() == 0;  // one host sync, like upstream's dim_size inference
 }
 
+// The kernels take the entry count from src and read that many index entries: a shorter index (say, the wrong
+// `dim`) would be read out of bounds, a longer one would silently drop entries.  Upstream raises in its
+// broadcast/expand for the same mistake (torch_scatter/utils.py:4-13).
+int64_t checked_dim(const torch::Tensor &src, const torch::Tensor &index, int64_t dim) {
+  dim = dim < 0 ? src.dim() + dim : dim;
+  TSB_CHECK_INPUT(dim >= 0 && dim < src.dim());
+  TSB_CHECK_INPUT(index.dim() == 1 && index.size(0) == src.size(dim));
+  return dim;
+}
+
 int64_t groups_of(const torch::Tensor &index, std::optional<int64_t> dim_size) {
   if (dim_size.has_value()) return dim_size.value();
   return index.numel() == 0 ? 0 : index[-1].item<int64_t>() + 1;  // ascending: the last entry is the largest
@@ -92,7 +102,7 @@ class SoftmaxSorted : public torch::autograd::Function<SoftmaxSorted> {
 public:
   static variable_list forward(AutogradContext *ctx, Variable src, Variable index, int64_t dim,
                                std::optional<int64_t> dim_size, bool log) {
-    dim = dim < 0 ? src.dim() + dim : dim;
+    dim = checked_dim(src, index, dim);
     const int64_t N = groups_of(index, dim_size);
     auto lse = segment_lse(src, index, dim, N);
     auto out = gather_apply(src, lse, index, dim, log ? 2 : 1);
@@ -128,7 +138,7 @@ class LogSumExpSorted : public torch::autograd::Function<LogSumExpSorted> {
 public:
   static variable_list forward(AutogradContext *ctx, Variable src, Variable index, int64_t dim,
                                std::optional<int64_t> dim_size) {
-    dim = dim < 0 ? src.dim() + dim : dim;
+    dim = checked_dim(src, index, dim);
     const int64_t N = groups_of(index, dim_size);
     auto lse = segment_lse(src, index, dim, N);
     ctx->saved_data["dim"] = dim;
@@ -154,7 +164,7 @@ class StdSorted : public torch::autograd::Function<StdSorted> {
 public:
   static variable_list forward(AutogradContext *ctx, Variable src, Variable index, int64_t dim,
                                std::optional<int64_t> dim_size, bool unbiased) {
-    dim = dim < 0 ? src.dim() + dim : dim;
+    dim = checked_dim(src, index, dim);
     const int64_t N = groups_of(index, dim_size);
     auto iv = index_view(index, src, dim);
     auto mean_count = segment_coo_fw(src, iv, std::nullopt, N, "mean");

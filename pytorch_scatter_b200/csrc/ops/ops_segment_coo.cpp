@@ -95,8 +95,17 @@ torch::Tensor gather_coo_fw(torch::Tensor src, torch::Tensor index, std::optiona
 
   TSB_CHECK_INPUT(src.dim() >= index.dim());
   TSB_CHECK_INPUT(index.dim() >= 1);
-  for (int64_t i = 0; i < index.dim() - 1; i++) TSB_CHECK_INPUT(src.size(i) == index.size(i));
   const int64_t dim = index.dim() - 1;
+  {
+    // leading dims of the index broadcast against src's, as upstream does (csrc/cuda/segment_coo_cuda.cu:337-340);
+    // a stride-0 batch dim stays one shared row (batched_rows below)
+    auto lead = index.sizes().vec();
+    for (int64_t i = 0; i < dim; i++) {
+      TSB_CHECK_INPUT(index.size(i) == src.size(i) || index.size(i) == 1);
+      lead[i] = src.size(i);
+    }
+    index = index.expand(lead);
+  }
 
   src = src.contiguous();
 

@@ -196,17 +196,19 @@ _ROUTED_STAGING = {}
 
 
 def _routed_staging(world: int, rows: int, feat: tuple, dtype: torch.dtype, device: torch.device, group):
-    """Symmetric staging buffer [world, rows, *feat] of this rank plus the device addresses of every rank's
-    buffer; allocated and exchanged once per shape (the rendezvous is a collective)."""
+    """Two symmetric staging buffers [2, world, rows, *feat] of this rank plus the device addresses of every rank's
+    copy; allocated and exchanged once per shape (the rendezvous is a collective).  Returns a dict with the buffer,
+    the rendezvous handle, the base addresses, the byte distance between the two buffers and a call counter."""
     import os
     import torch.distributed._symmetric_memory as symm_mem
     # plain peer stores are all this path needs: keep the buffers off NVLink multicast objects
     os.environ.setdefault('TORCH_SYMM_MEM_DISABLE_MULTICAST', '1')
     key = (id(group), world, rows, feat, dtype, device.index)
     if key not in _ROUTED_STAGING:
-        buf = symm_mem.empty((world, rows) + feat, dtype=dtype, device=device)
+        buf = symm_mem.empty((2, world, rows) + feat, dtype=dtype, device=device)
         handle = symm_mem.rendezvous(buf, group if group is not None else dist.group.WORLD)
-        _ROUTED_STAGING[key] = (buf, handle, [int(p) for p in handle.buffer_ptrs])
+        _ROUTED_STAGING[key] = {'buf': buf, 'handle': handle, 'ptrs': [int(p) for p in handle.buffer_ptrs],
+                                'half_bytes': buf[0].numel() * buf.element_size(), 'calls': 0}
     return _ROUTED_STAGING[key]
 
 
@@ -225,7 +227,11 @@ def routed_exchange_available(src_local: torch.Tensor, dim_size: int, group=None
     return bool(flag.item())
 
 
-def scatter_sum_routed(src_local: torch.Tensor, index_local: torch.Tensor, dim_size: int, group=None) -> torch.Tensor:
+ROUTED_PHASES = ('grouping', 'reduction + peer stores', 'barrier', 'slab sum')
+
+
+def scatter_sum_routed(src_local: torch.Tensor, index_local: torch.Tensor, dim_size: int, group=None,
+                       timeline: Optional[list] = None) -> torch.Tensor:
     """Edge-sharded ``scatter(sum)`` along dim 0 with the exchange fused into the reduction kernel.
 
     Every rank groups its entry ids by target row and reduces all ``dim_size`` rows through that permutation in one
@@ -234,20 +240,43 @@ def scatter_sum_routed(src_local: torch.Tensor, index_local: torch.Tensor, dim_s
     kernel competes for SMs.  After a barrier every rank adds the ``world`` partial slabs it received.  Rank ``r``
     owns the contiguous rows ``[r * rows, (r + 1) * rows)`` with ``rows = ceil(dim_size / world)`` and gets them
     back (zero rows beyond ``dim_size``), in the source dtype.  CUDA + NCCL only.
+
+    Two staging buffers alternate from call to call, so one barrier per call is enough: a rank starts storing into
+    buffer ``i % 2`` of its peers only after the barrier of call ``i - 1``, which every peer reaches after it has
+    finished adding up call ``i - 2`` (the last reader of that buffer).
+
+    ``timeline``, if given, receives ``len(ROUTED_PHASES) + 1`` CUDA events recorded on the current stream at the
+    phase borders (see :data:`ROUTED_PHASES`).
     """
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     feat = tuple(src_local.shape[1:])
     rows = -(-dim_size // world)
-    buf, handle, ptrs = _routed_staging(world, rows, feat, src_local.dtype, src_local.device, group)
+    st = _routed_staging(world, rows, feat, src_local.dtype, src_local.device, group)
+    half = st['calls'] % 2
+    st['calls'] += 1
+    buf, handle = st['buf'][half], st['handle']
+    ptrs = [p + half * st['half_bytes'] for p in st['ptrs']]
+
+    def mark():
+        if timeline is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            timeline.append(ev)
+
+    mark()
     rowptr, perm = torch.ops.torch_scatter.scatter_group(index_local, dim_size)
-    # bounded waits: a rank that never arrives ends the call with an error instead of hanging the GPUs
-    handle.barrier(channel=0, timeout_ms=60000)   # nobody is still adding up the previous call's slabs
+    mark()
     torch.ops.torch_scatter.segment_sum_perm_routed(src_local, rowptr, perm, ptrs, rank, rows, dim_size)
     valid = min(max(dim_size - rank * rows, 0), rows)   # rows of this rank's block that exist; the rest is padding
     if valid < rows:                                    # nobody writes padding rows: keep them zero
         buf[:, valid:].zero_()
-    handle.barrier(channel=1, timeout_ms=60000)   # every rank's rows have landed
-    return torch.ops.torch_scatter.sum_slabs(buf)
+    mark()
+    # a bounded wait: a rank that never arrives ends the call with an error instead of hanging the GPUs
+    handle.barrier(channel=half, timeout_ms=60000)      # every rank's rows have landed
+    mark()
+    out = torch.ops.torch_scatter.sum_slabs(buf)
+    mark()
+    return out
 
 
 def _cuda_local_reduce(src, index, dim_size, reduce):

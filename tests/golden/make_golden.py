@@ -256,12 +256,32 @@ def random_cases(ts):
                     res = fn(src, index, dim, None, n)
                 cases.append({'op': name, 'reduce': None,
                               'args': {'src': src, 'index': index, 'dim': dim, 'dim_size': n}, 'out': res.clone()})
+
+    # ---- composites over an ASCENDING 1-D index (an edge list sorted by destination; the last groups empty), with
+    # the input gradients: a sorted index is what a fused implementation may special-case, so it is pinned separately.
+    # A generator of its own keeps every case above unchanged.
+    gen2 = torch.Generator().manual_seed(20240611)
+    for dtype in (torch.float, torch.half, torch.bfloat16):
+        for (shape, dim, n) in [((300,), 0, 23), ((257, 8), 0, 40), ((3, 190, 16), 1, 31), ((2, 64), -1, 9)]:
+            src = rand_src(gen2, shape, dtype)
+            index = torch.randint(0, n - 2, (shape[dim],), generator=gen2).sort()[0]
+            for name in ('scatter_softmax', 'scatter_log_softmax', 'scatter_logsumexp', 'scatter_std'):
+                fn = getattr(ts, name)
+                if name in ('scatter_softmax', 'scatter_log_softmax'):
+                    call = lambda s: fn(s, index, dim, dim_size=n)  # noqa: E731
+                else:
+                    call = lambda s: fn(s, index, dim, None, n)  # noqa: E731
+                rec = {'op': name, 'reduce': None, 'sorted_index': True,
+                       'args': {'src': src, 'index': index, 'dim': dim, 'dim_size': n}, 'out': call(src).clone()}
+                if dtype == torch.float:
+                    rec['grad'] = grads_of(call, src)
+                cases.append(rec)
     return cases
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--ref', default='/root/reference')
+    ap.add_argument('--ref', required=True, help='checkout of the upstream project (rusty1s/pytorch_scatter)')
     a = ap.parse_args()
     ts = import_upstream(a.ref)
     ka = known_answers(ts, a.ref)

@@ -307,3 +307,35 @@ def test_second_device_if_present(ts):
     index = torch.tensor([0, 0, 1, 1], device='cuda:1')
     assert ts.scatter(src, index, reduce='sum').tolist() == [3.0, 7.0]
     assert ts.segment_csr(src, torch.tensor([0, 2, 4], device='cuda:1'), reduce='sum').tolist() == [3.0, 7.0]
+
+
+def test_fused_composites_reject_a_wrong_index_length(ts):
+    """An index whose length is not src.size(dim) (say, the wrong `dim`) must raise before any kernel reads it;
+    upstream raises in its broadcast for the same mistake."""
+    src = torch.randn(6, 40, device=DEV)
+    index = torch.arange(6, device=DEV)            # ascending: would qualify for the fused kernels
+    for fn in (ts.scatter_softmax, ts.scatter_log_softmax, ts.scatter_logsumexp, ts.scatter_std):
+        with pytest.raises(RuntimeError):
+            fn(src, index, dim=1)
+        assert fn(src, index, dim=0).size(1) == 40
+
+
+def test_segment_coo_broadcast_index_forward_and_backward(ts):
+    """An index with a singleton batch dim broadcasts over src's batch dim, in gather_coo and in the backward of
+    segment_coo sum / mean (which is a gather), as upstream expands it."""
+    torch.manual_seed(11)
+    B, E, K, N = 3, 50, 4, 9
+    index = torch.randint(0, N, (1, E), device=DEV).sort(dim=1)[0]
+    full = index.expand(B, E).contiguous()
+    table = torch.randn(B, N, K, device=DEV)
+    assert torch.equal(ts.gather_coo(table, index), ts.gather_coo(table, full))
+    for reduce in ('sum', 'mean'):
+        a = torch.randn(B, E, K, device=DEV, dtype=torch.double, requires_grad=True)
+        b = a.detach().clone().requires_grad_()
+        out_a = ts.segment_coo(a, index, dim_size=N, reduce=reduce)
+        out_b = ts.segment_coo(b, full, dim_size=N, reduce=reduce)
+        assert torch.equal(out_a, out_b)
+        g = torch.randn_like(out_a)
+        out_a.backward(g)
+        out_b.backward(g)
+        assert torch.equal(a.grad, b.grad)

@@ -46,12 +46,12 @@ def row_lengths(gen, rows, kind):
 def chunk(request):
     """Chunk lengths of the row-pointer reduction (short chunks make rows straddle many chunk borders), and the kernel
     that stages chunks in shared memory (the default for K == 1 only) forced for every entry of up to 64 bytes."""
-    names = ('TSB_CSR_CHUNK_ENTRIES', 'TSB_CSR_FLAT_ROW_BYTES')
+    names = ('TSB_CSR_CHUNK_ENTRIES', 'TSB_CSR_FORCE_FLAT')
     old = {k: os.environ.get(k) for k in names}
     for k in names:
         os.environ.pop(k, None)
     if request.param == 'staged':
-        os.environ['TSB_CSR_FLAT_ROW_BYTES'] = '64'
+        os.environ['TSB_CSR_FORCE_FLAT'] = '1'
         os.environ['TSB_CSR_CHUNK_ENTRIES'] = '64'
     elif request.param is not None:
         os.environ['TSB_CSR_CHUNK_ENTRIES'] = str(request.param)
@@ -302,6 +302,14 @@ def test_scatter_elements_and_ties():
             assert_close(got, want, what=what)
             if want_arg is not None:
                 assert torch.equal(got_arg.cpu(), want_arg), what + ' arg'
+                # seeded, the seeds on the same quarter-step grid as the entries: a tie keeps the seed, arg "none"
+                seeds = rand_src(gen, (B, N, K), dtype)
+                if dtype.is_floating_point:
+                    seeds = (seeds.float() * 4).round().div(4).to(dtype)
+                want, want_arg = oracle.scatter(s, index, N, reduce, seeds)
+                got, got_arg, _ = cabi.scatter(s.cuda(), index.cuda(), N, reduce, (E * K, K, 1), out=seeds.clone().cuda())
+                assert_close(got, want, what=what + ' seeded')
+                assert torch.equal(got_arg.cpu(), want_arg), what + ' seeded arg'
 
 
 def test_scatter_rows_ties(scatter_slices):
@@ -313,21 +321,31 @@ def test_scatter_rows_ties(scatter_slices):
     for dtype in (torch.float32, torch.int32, torch.float16, torch.float64):
         src = rand_src(gen, (B, E, K), dtype)
         base = rand_src(gen, (B, N, K), dtype)
-        # seeds never equal an entry (upstream's CPU loop lets the seed win such a tie, its GPU arg pass the entry)
+        # Two sets of seeds: on the half-step grid of the entries, so that seeds tie with entries all the time
+        # (the CPU loop's strict comparison lets the value already in `out` win: arg stays "none",
+        # csrc/cpu/reducer.h:63-67), and off the grid (no seed ever equals an entry).
         if dtype.is_floating_point:
             src = (src.float() * 2).round().div(2).to(dtype)
-            base = ((base.float() * 2).round().div(2) + 0.25).to(dtype)
+            on_grid = (base.float() * 2).round().div(2).to(dtype)
+            off_grid = (on_grid.float() + 0.25).to(dtype)
         else:
-            src, base = src * 2, base * 2 + 1
+            src, on_grid = src * 2, base * 2
+            off_grid = on_grid + 1
         for reduce in ('min', 'max'):
             want, want_arg = oracle.scatter(src, index, N, reduce)
             got, got_arg, _ = cabi.scatter(src.cuda(), index.cuda(), N, reduce, (0, 1, 0))
             assert_close(got, want, what=f'ties {reduce} {dtype}')
             assert torch.equal(got_arg.cpu(), want_arg), f'ties {reduce} {dtype} arg'
-            want, want_arg = oracle.scatter(src, index, N, reduce, base)
-            got, got_arg, _ = cabi.scatter(src.cuda(), index.cuda(), N, reduce, (0, 1, 0), out=base.clone().cuda())
-            assert_close(got, want, what=f'seeded ties {reduce} {dtype}')
-            assert torch.equal(got_arg.cpu(), want_arg), f'seeded ties {reduce} {dtype} arg'
+            for seeds, name in ((off_grid, 'seeded'), (on_grid, 'seeded, seeds tie with entries')):
+                want, want_arg = oracle.scatter(src, index, N, reduce, seeds)
+                got, got_arg, _ = cabi.scatter(src.cuda(), index.cuda(), N, reduce, (0, 1, 0), out=seeds.clone().cuda())
+                assert_close(got, want, what=f'{name} {reduce} {dtype}')
+                assert torch.equal(got_arg.cpu(), want_arg), f'{name} {reduce} {dtype} arg'
+                if name != 'seeded':   # the case must really occur: some target keeps its seed against an equal entry
+                    tied = (want == seeds) & (want_arg == E)
+                    hit = torch.zeros_like(tied)
+                    hit[:, index.view(-1)] = True
+                    assert bool((tied & hit).any())
 
 
 @pytest.mark.parametrize('sort', ['buckets', 'atomic'])

@@ -1,6 +1,7 @@
 """Two-GPU checks of the edge-sharded scatter (skipped on a single-GPU box): the exchange fused into the reduction
-kernel (peer stores into the owners' staging buffers) and the NCCL per-slice variant against the single-GPU
-operator on the concatenated shards."""
+kernel (peer stores into the owners' staging buffers), the NCCL per-slice variant, and the plain one-collective
+variant for sum / mean / min / max with global arg indices, all against the single-GPU operator on the concatenated
+shards."""
 import os
 import socket
 
@@ -48,7 +49,7 @@ def _worker(rank, world, port, dtype_name, results):
         ok = []
         if routed_exchange_available(src, N):
             rows = -(-N // world)
-            for _ in range(2):   # the second call reuses the staging buffers
+            for _ in range(3):   # two staging buffers alternate: the third call reuses the first one
                 got = scatter_sum_routed(src, index, N)
             lo, hi = rank * rows, min((rank + 1) * rows, N)
             ok.append(same(got[:hi - lo], want[lo:hi]) and bool((got[hi - lo:] == 0).all()))
@@ -59,6 +60,25 @@ def _worker(rank, world, port, dtype_name, results):
         mine = owned_rows(N, world, rank, passes, sub, dev)
         valid = mine < N
         ok.append(same(got[valid], want[mine[valid]]))
+        # plain variant with one collective per reduction: sum / mean / min / max with GLOBAL arg indices, against
+        # the single-GPU operator on the concatenated shards (quantised values: ties across ranks, arg = first edge)
+        from pytorch_scatter_b200.dist import scatter_sharded
+        offsets = [0]
+        for s_, _ in shards:
+            offsets.append(offsets[-1] + s_.size(0))
+        all_src = torch.cat([s_ for s_, _ in shards]).to(dev)
+        all_index = torch.cat([i_ for _, i_ in shards]).to(dev)
+        per = -(-N // world)
+        lo, hi = rank * per, min((rank + 1) * per, N)
+        for reduce in ('sum', 'mean', 'min', 'max'):
+            res = scatter_sharded(src, index, N, reduce, edge_offset=offsets[rank], total_edges=offsets[-1])
+            if reduce in ('min', 'max'):
+                want, want_arg = getattr(ts, f'scatter_{reduce}')(all_src, all_index, 0, None, N)
+                ok.append(bool(torch.equal(res[0][:hi - lo], want[lo:hi])) and bool(torch.equal(res[1][:hi - lo], want_arg[lo:hi])))
+            else:
+                want = ts.scatter(all_src, all_index, dim=0, dim_size=N, reduce=reduce)
+                ok.append(same(res[:hi - lo], want[lo:hi]) if reduce == 'sum' else
+                          bool(torch.allclose(res[:hi - lo].float(), want[lo:hi].float(), rtol=2e-2, atol=0.05)))
         results[rank] = ok
     finally:
         dist.destroy_process_group()
@@ -83,6 +103,7 @@ def test_sharded_scatter_two_gpus(dtype_name):
             p.join()
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     for rank in range(2):
-        routed, overlapped = results[rank]
+        routed, overlapped, *plain = results[rank]
         assert routed in (True, None), f'rank {rank}: routed exchange wrong'
         assert overlapped, f'rank {rank}: overlapped exchange wrong'
+        assert all(plain) and len(plain) == 4, f'rank {rank}: scatter_sharded sum/mean/min/max: {plain}'

@@ -99,8 +99,6 @@ def test_recorded_upstream_outputs(ts):
         what = f"#{i} {case['op']} {case['reduce']} {case['out'].dtype} {tuple(case['args']['src'].shape)}"
         assert_close(out, case['out'], what=what)
         if 'arg' in case:
-            if case['out'].dtype in (torch.half, torch.bfloat16) and case['op'].startswith('scatter'):
-                continue
             assert torch.equal(arg.cpu(), case['arg']), what + ' arg'
 
 

@@ -13,7 +13,8 @@ import pytest
 import torch
 
 import cabi
-from helpers import assert_close
+from helpers import assert_close, assert_sum_close
+from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -58,6 +59,14 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row():
             assert torch.equal(got, want)  # both are deterministic: same chunks, same order
             if want_arg is not None:
                 assert torch.equal(got_arg, want_arg)
+            # and against the restatement of upstream's CPU loop directly
+            ref, ref_arg = oracle.segment_csr(src.cpu(), indptr.cpu(), reduce)
+            if reduce == 'max':
+                assert torch.equal(got.cpu(), ref) and torch.equal(got_arg.cpu(), ref_arg)
+            else:
+                mass = oracle.segment_csr(src.cpu().double().abs(), indptr.cpu(), reduce)[0]
+                assert_sum_close(got, oracle.segment_csr(src.cpu().double(), indptr.cpu(), reduce)[0], mass,
+                                 what=f'noalloc {reduce} {dtype} vs oracle')
 
 
 def test_noalloc_rejects_problems_beyond_its_scratch():
