@@ -635,21 +635,59 @@ def cpu_baseline(args):
         return {'value': None, 'unit': UNIT, 'cores': None, 'kind': None, 'sample': f'failed: {e}'}
 
 
+def zipf_index(E, N, dev, g):
+    """E i.i.d. draws from p(k) ~ k^-1.2 over N targets, passed through a random permutation of the targets."""
+    prob = torch.arange(1, N + 1, device=dev, dtype=torch.float64).pow(-1.2)
+    ranks = torch.multinomial((prob / prob.sum()).float(), E, replacement=True, generator=g)
+    return torch.randperm(N, device=dev, generator=g)[ranks]
+
+
 def run_profile_op(args):
-    """Profiling helper: `--profile-op csr|scatter` runs warmup+steps calls of ONE operator on a
-    `--rows`-sized copy of the workload and exits; meant to be wrapped in ncu on a small case."""
+    """Profiling helper, meant to be wrapped in ncu on a small case: runs warmup+steps calls of ONE operator and exits.
+    `csr` / `scatter`: the benchmark's operators on a `--rows`-sized copy of its workload.  `c4-sum` / `c4-max`:
+    scatter of fp32 [`--entries` x 16] under a Zipf(1.2) index over 100,000 targets.  `c3-*`: segment_coo / softmax on
+    the sorted index of a `--rows`-sized workload in `--dtype`.  `c5-scatter`: bf16 F=128, `--entries` edges of a
+    power-law graph into `--rows` target rows."""
     import pytorch_scatter_b200 as ts
-    indptr, _, shuffled, src = make_workload(args.rows, SEED)
-    src, indptr, shuffled = src.cuda(), indptr.cuda(), shuffled.cuda()
-    out = torch.empty(args.rows, FEAT, device='cuda')
+    dev = torch.device('cuda')
+    g = torch.Generator(device=dev).manual_seed(SEED)
+    op = args.profile_op
+    dtype = {'fp32': torch.float32, 'bf16': torch.bfloat16, 'fp16': torch.float16}[args.dtype]
+    if op in ('csr', 'scatter'):
+        indptr, _, shuffled, src = make_workload(args.rows, SEED)
+        src, indptr, shuffled = src.cuda(), indptr.cuda(), shuffled.cuda()
+        out = torch.empty(args.rows, FEAT, device='cuda')
+        fn = (lambda: ts.segment_csr(src, indptr, out=out, reduce='sum')) if op == 'csr' else \
+            (lambda: ts.scatter(src, shuffled, dim=0, dim_size=args.rows, reduce='sum'))
+        entries = src.size(0)
+    elif op in ('c4-sum', 'c4-max'):
+        entries, N = args.entries, 100000
+        idx = zipf_index(entries, N, dev, g)
+        src = torch.randn(entries, 16, device=dev, generator=g)
+        fn = (lambda: ts.scatter_sum(src, idx, 0, None, N)) if op == 'c4-sum' else (lambda: ts.scatter_max(src, idx, 0, None, N))
+    elif op.startswith('c3-'):
+        lens = row_lengths(args.rows, SEED, force_long=max(1, 8 * args.rows // ROWS))
+        index = torch.repeat_interleave(torch.arange(args.rows, device=dev), lens.to(dev))
+        entries = index.numel()
+        src = torch.randn(entries, args.feat, device=dev, generator=g).to(dtype)
+        fn = {'c3-sum': lambda: ts.segment_sum_coo(src, index, None, args.rows),
+              'c3-max': lambda: ts.segment_max_coo(src, index, None, args.rows),
+              'c3-softmax': lambda: ts.scatter_softmax(src, index, 0, dim_size=args.rows)}[op]
+    elif op == 'c5-scatter':
+        entries, N = args.entries, args.rows
+        lens = row_lengths(N, SEED + 6, mean=20.0, force_long=8).to(dev)
+        here = torch.binomial(lens.float(), torch.full((N,), min(1.0, entries / float(lens.sum())), device=dev), generator=g).long()
+        idx = torch.repeat_interleave(torch.arange(N, device=dev), here)
+        idx = idx[torch.randperm(idx.numel(), device=dev, generator=g)]
+        entries = idx.numel()
+        src = torch.randn(entries, 128, device=dev, generator=g).bfloat16()
+        fn = lambda: ts.scatter_sum(src, idx, 0, None, N)  # noqa: E731
+    else:
+        raise ValueError(op)
     for _ in range(args.warmup + args.steps):
-        if args.profile_op == 'csr':
-            ts.segment_csr(src, indptr, out=out, reduce='sum')
-        else:
-            ts.scatter(src, shuffled, dim=0, dim_size=args.rows, reduce='sum')
+        fn()
     torch.cuda.synchronize()
-    print(json.dumps({'profile_op': args.profile_op, 'rows': args.rows, 'entries': src.size(0),
-                      'calls': args.warmup + args.steps}))
+    print(json.dumps({'profile_op': op, 'rows': args.rows, 'entries': entries, 'calls': args.warmup + args.steps}))
 
 
 def run_suite(args):
@@ -816,8 +854,12 @@ def main():
     ap.add_argument('--no-c5', action='store_true', help='skip the GNN-scale block (bf16 F=128, 10 M nodes / 200 M edges)')
     ap.add_argument('--suite', action='store_true', help='per-operator table over the other configurations')
     ap.add_argument('--suite-only', default='', help='comma-separated configs to run, e.g. C3,C4')
-    ap.add_argument('--profile-op', choices=['csr', 'scatter'], default=None)
+    ap.add_argument('--profile-op', default=None,
+                    choices=['csr', 'scatter', 'c4-sum', 'c4-max', 'c3-sum', 'c3-max', 'c3-softmax', 'c5-scatter'])
     ap.add_argument('--rows', type=int, default=ROWS, help='rows of the workload for --profile-op')
+    ap.add_argument('--entries', type=int, default=1 << 22, help='entries for --profile-op c4-* / c5-scatter')
+    ap.add_argument('--feat', type=int, default=64, help='features for --profile-op c3-*')
+    ap.add_argument('--dtype', default='fp32', choices=['fp32', 'bf16', 'fp16'], help='dtype for --profile-op c3-*')
     args = ap.parse_args()
     if args.profile_op is not None:
         run_profile_op(args)

@@ -198,20 +198,26 @@ int tsb_segment_csr_perm(const void *src, const int64_t *rowptr, const int32_t *
                          int dtype, int reduce, int out_seeded,
                          void *workspace, size_t workspace_bytes, tsb_stream_t stream);
 
-/* tsb_segment_csr_perm for a scatter sharded over `world` <= 8 GPUs (SUM or MEAN of this rank's entries, write-only):
+/* tsb_segment_csr_perm for a scatter sharded over `world` <= 8 GPUs (SUM of this rank's entries, write-only):
  * GPU q owns the rows [q*rows_per_owner, (q+1)*rows_per_owner) and holds a staging buffer [world, rows_per_owner, K]
  * at owner_base[q] (a HOST array of `world` device pointers, peers' memory included: anything this GPU may store
  * to).  Every finished row n is stored into slab `rank` of its owner's buffer, so the partial rows cross NVLink as
  * plain stores while the reduction is still running; once all ranks have finished (the caller's barrier), every
- * owner adds its `world` slabs.  rows_per_owner * world >= N.  No counterpart upstream (its scatter is single-GPU). */
+ * owner adds its `world` slabs.  rows_per_owner * world >= N.
+ *   wide_staging != 0    the staging buffers hold the accumulation type (fp32 for fp16 / bf16 sources, the source type
+ *                        otherwise): 16-bit partial sums then cross NVLink unrounded and the sharded result equals
+ *                        the single-GPU one up to summation order; 0: staging buffers of the source type (half the
+ *                        NVLink bytes for 16-bit sources, every rank's partial rounded once more).
+ * No counterpart upstream (its scatter is single-GPU). */
 int tsb_segment_csr_perm_routed(const void *src, const int64_t *rowptr, const int32_t *perm,
-                                void *const *owner_base, int world, int rank, int64_t rows_per_owner,
+                                void *const *owner_base, int world, int rank, int64_t rows_per_owner, int wide_staging,
                                 int64_t E, int64_t K, int64_t N, int dtype, int reduce,
                                 void *workspace, size_t workspace_bytes, tsb_stream_t stream);
 
 /* The owner's last step of the routed scatter: out[i] = sum over q < world of slabs[q * elems + i] (accumulated in fp32
- * for 16-bit dtypes), one streaming pass. */
-int tsb_sum_slabs(const void *slabs, void *out, int world, int64_t elems, int dtype, tsb_stream_t stream);
+ * for 16-bit dtypes), one streaming pass.  wide_slabs != 0: the slabs hold the accumulation type (see above), out the
+ * dtype. */
+int tsb_sum_slabs(const void *slabs, void *out, int world, int64_t elems, int dtype, int wide_slabs, tsb_stream_t stream);
 
 /* One slice of an unsorted scatter SUM, for sharded use: adds the E edges of this call (src [E,K], 1-D index [E])
  * into the target rows [row_lo, row_hi) of `partial` [N,K], after zeroing exactly those rows; targets outside the

@@ -30,7 +30,7 @@ struct CsrParams {
   // belong to no row.  Single batch only.
   bool skip_outside = false;
   // Optional routing of the finished rows to their owners (a sharded scatter over `route_world` GPUs,
-  // SUM/MEAN, single batch): row n belongs to GPU q = n / route_rows and is stored at
+  // SUM, single batch): row n belongs to GPU q = n / route_rows and is stored at
   // route_base[q] + ((route_rank * route_rows + n % route_rows) * K) elements, i.e. into the slab this
   // rank owns inside q's staging buffer [route_world, route_rows, K].  route_base[q] may be peer memory:
   // the rows then cross NVLink as plain stores while the reduction is still running.  `out` is unused.
@@ -38,6 +38,10 @@ struct CsrParams {
   void *route_base[kMaxRoute] = {nullptr};
   int route_world = 0, route_rank = 0;
   int64_t route_rows = 0;
+  // Staging buffers in accumulation precision: fp16 / bf16 partial sums travel as fp32 and are rounded once, by the
+  // owner, after the slabs have been added (twice the bytes over NVLink; without it every rank rounds its partial to
+  // 16 bits first).  No difference for the other types, whose accumulators have the source type.
+  bool route_wide = false;
   int mode;
   void *workspace;        // csr_reduce_workspace_bytes(...) bytes, 256-byte aligned
   size_t workspace_bytes;

@@ -153,6 +153,7 @@ struct ScatterParams {
   int l_log2;
   int fresh;
   int replicas;        // copies of the output the updates are spread over (1: none)
+  int binned;          // 1: scatter_rows_binned_kernel is launched too and takes the indices the probe calls skewed
   const int *clustered;  // device flags written by scatter_probe_kernel: [0] 1 = neighbouring entries share targets,
                          // [1] 1 = entries far apart often share targets (a skewed index)
 };
@@ -227,124 +228,28 @@ __global__ void __launch_bounds__(kThreads) scatter_rows_direct_kernel(ScatterPa
   using U = acc_t<T>;
   const T *__restrict__ src = static_cast<const T *>(p.src);
   if (p.clustered[0] != 0) return;                       // the run-combining kernel takes clustered indices
+  if (p.binned && p.clustered[1] != 0) return;           // the tile kernel takes skewed ones
   U *target = static_cast<U *>(p.target);
   if (p.replicas > 1) target += (blockIdx.x % p.replicas) * (p.B * p.N * p.K);
   const int L = 1 << p.l_log2;
   const int64_t Kv = p.K / VEC;
-  const int64_t entry = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> p.l_log2;
   const int col = threadIdx.x & (L - 1);
-  if (entry >= p.B * p.E) return;
-  const int64_t b = entry / p.E, e = entry - b * p.E;
-  const int64_t idx = p.index[b * p.sb + e * p.se];
-  if (idx < 0 || idx >= p.N) return;
-  const T *srow = src + entry * p.K;
-  U *trow = target + (b * p.N + idx) * p.K;
-  for (int64_t c = col; c < Kv; c += L) apply_pack<OP, T, VEC>(trow + c * VEC, ld_stream<T, VEC>(srow + c * VEC));
-  // one count per row of the index itself: a batch-broadcast index is counted for b == 0 only
-  if (p.count != nullptr && col == 0 && (p.sb != 0 || b == 0)) atomicAdd(p.count + (p.sb ? b : 0) * p.N + idx, 1);
-}
-
-// Small, contended outputs under a skewed index (a few rows take most of the entries): what bounds the direct kernel
-// is same-address atomic throughput in L2.  Here a CTA accumulates a tile of entries through a direct-mapped cache of
-// `slots` rows in shared memory: the first row that hashes to a free slot claims it (hot rows come early and often, so
-// they get theirs), later entries of that row are added with shared-memory atomics, all other entries go to global
-// memory as before; at the end every claimed slot is flushed with one global update per element.  The cache is used
-// when the probe's second flag says the index is skewed (duplicates among sampled, non-adjacent entries), otherwise
-// the kernel sends every entry to global memory like the direct kernel; fp32 accumulation, SUM only.  (For MIN/MAX
-// the cache was measured and loses, 2.65 -> 3.27 ms on the same index: their global updates are already filtered by a
-// plain load, and a hot row stops updating once it holds a large value.)  (A variant that
-// reserved a slot on the first sighting and cached only from the second on, to spare rows seen once the flush, was
-// slower on both the skewed and the uniform case.)
-constexpr int kCacheBytesMax = 96 * 1024;
-
-template <typename T, int VEC, bool USE_CACHE>
-__device__ __forceinline__ void cached_tile(const ScatterParams &p, int tile_entries, int slots_log2, float *s_val,
-                                            int *s_tag, int *s_cnt) {
-  using U = acc_t<T>;
-  const int slots = 1 << slots_log2;
-  const T *__restrict__ src = static_cast<const T *>(p.src);
-  U *target = static_cast<U *>(p.target);
-  if (p.replicas > 1) target += (blockIdx.x % p.replicas) * (p.B * p.N * p.K);
-  if (USE_CACHE) {
-    for (int i = threadIdx.x; i < slots * (int)p.K; i += kThreads) s_val[i] = 0.0f;
-    for (int i = threadIdx.x; i < slots; i += kThreads) { s_tag[i] = -1; s_cnt[i] = 0; }
-    __syncthreads();
-  }
-  const int L = 1 << p.l_log2;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int col = lane & (L - 1);
-  const int sub = lane >> p.l_log2;
-  const int eps = 32 >> p.l_log2;
-  const int64_t Kv = p.K / VEC;
+  const int64_t per_cta = kThreads >> p.l_log2;
   const int64_t M = p.B * p.E;
-  const int64_t tile0 = (int64_t)blockIdx.x * tile_entries;
-  const int per_round = (kThreads / 32) * eps;
-  for (int it = 0; it < tile_entries; it += per_round) {  // CTA-uniform trip count: the shuffle below needs every lane
-    const int64_t entry = tile0 + it + warp * eps + sub;
-    const bool in_tile = it + warp * eps + sub < tile_entries && entry < M;
-    int64_t grow = -1;
-    int64_t b = 0;
-    if (in_tile) {
-      b = entry / p.E;
-      const int64_t idx = p.index[b * p.sb + (entry - b * p.E) * p.se];
-      if (idx >= 0 && idx < p.N) grow = b * p.N + idx;
-    }
-    const bool valid = grow >= 0;
-    bool hit = false;
-    int slot = 0;
-    if (USE_CACHE) {
-      slot = valid ? (int)(((unsigned)grow * 2654435761u) >> (32 - slots_log2)) : 0;
-      int seen = valid ? *reinterpret_cast<volatile int *>(s_tag + slot) : -2;
-      const bool claim = valid && seen == -1;
-      if (claim && col == 0) seen = atomicCAS(s_tag + slot, -1, (int)grow);
-      seen = __shfl_sync(kFullMask, seen, lane - col);  // the lane group's first lane decides for the group
-      hit = valid && (seen == (int)grow || (claim && seen == -1));
-    }
-    if (!valid) continue;
+  // The grid is capped (see direct_grid): a CTA walks the entry blocks blockIdx.x, blockIdx.x + gridDim.x, ... so that
+  // a launch whose index the flags hand to another kernel costs a few thousand CTAs, not one per 256 lanes of work.
+  for (int64_t first = (int64_t)blockIdx.x * per_cta; first < M; first += (int64_t)gridDim.x * per_cta) {
+    const int64_t entry = first + (threadIdx.x >> p.l_log2);
+    if (entry >= M) continue;
+    const int64_t b = entry / p.E, e = entry - b * p.E;
+    const int64_t idx = p.index[b * p.sb + e * p.se];
+    if (idx < 0 || idx >= p.N) continue;
     const T *srow = src + entry * p.K;
-    if (USE_CACHE && hit) {
-      float *crow = s_val + (size_t)slot * p.K;
-      for (int64_t c = col; c < Kv; c += L) {
-        const Pack<T, VEC> v = ld_stream<T, VEC>(srow + c * VEC);
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) atomicAdd(crow + c * VEC + i, to_acc<T>(v.v[i]));
-      }
-      if (p.count != nullptr && col == 0 && (p.sb != 0 || b == 0)) atomicAdd(s_cnt + slot, 1);
-    } else {
-      U *trow = target + grow * p.K;
-      for (int64_t c = col; c < Kv; c += L) apply_pack<kSum, T, VEC>(trow + c * VEC, ld_stream<T, VEC>(srow + c * VEC));
-      if (p.count != nullptr && col == 0 && (p.sb != 0 || b == 0))
-        atomicAdd(p.count + (p.sb ? b : 0) * p.N + (grow - b * p.N), 1);
-    }
+    U *trow = target + (b * p.N + idx) * p.K;
+    for (int64_t c = col; c < Kv; c += L) apply_pack<OP, T, VEC>(trow + c * VEC, ld_stream<T, VEC>(srow + c * VEC));
+    // one count per row of the index itself: a batch-broadcast index is counted for b == 0 only
+    if (p.count != nullptr && col == 0 && (p.sb != 0 || b == 0)) atomicAdd(p.count + (p.sb ? b : 0) * p.N + idx, 1);
   }
-  if (!USE_CACHE) return;
-  __syncthreads();
-  // flush: one warp per claimed slot at a time
-  for (int slot = warp; slot < slots; slot += kThreads / 32) {
-    const int grow = s_tag[slot];
-    if (grow < 0) continue;  // warp-uniform
-    const float *crow = s_val + (size_t)slot * p.K;
-    U *trow = target + (int64_t)grow * p.K;
-    for (int k = lane; k < (int)p.K; k += 32) atom_add(trow + k, crow[k]);
-    if (p.count != nullptr && lane == 0 && s_cnt[slot] != 0) {
-      const int64_t b = grow / p.N;
-      atomicAdd(p.count + (p.sb ? b : 0) * p.N + (grow - b * p.N), s_cnt[slot]);
-    }
-  }
-}
-
-template <typename T, int VEC>
-__global__ void __launch_bounds__(kThreads) scatter_rows_cached_kernel(ScatterParams p, int tile_entries, int slots_log2) {
-  static_assert(std::is_same<acc_t<T>, float>::value, "fp32 accumulation only");
-  extern __shared__ float s_cache[];
-  const int slots = 1 << slots_log2;
-  float *s_val = s_cache;                                         // [slots][K]
-  int *s_tag = reinterpret_cast<int *>(s_cache + (size_t)slots * p.K);  // [slots] target row over all batches, -1: free
-  int *s_cnt = s_tag + slots;                                     // [slots] entries seen (MEAN's count)
-  if (p.clustered[0] != 0) return;  // clustered: the run-combining kernel
-  // skewed: through the cache; otherwise every entry goes straight to global memory (CTA-uniform choice)
-  if (p.clustered[1] != 0) cached_tile<T, VEC, true>(p, tile_entries, slots_log2, s_val, s_tag, s_cnt);
-  else cached_tile<T, VEC, false>(p, tile_entries, slots_log2, s_val, s_tag, s_cnt);
 }
 
 constexpr int kRangeBatches = 4;  // 32-entry batches per group: a group is 128 consecutive entries
@@ -625,6 +530,221 @@ __global__ void __launch_bounds__(kThreads, 4) scatter_rows_runs_kernel(ScatterP
   }
 }
 
+// ---- skewed index, small output: group a tile's entries by target inside the CTA, then walk runs ----------------
+// An index where a few targets take most of the entries (a Zipf-like degree distribution) makes every per-entry
+// update scheme pay for same-address atomics: in L2 for the direct kernels, in shared memory for a row cache (sixteen
+// scalar shared-memory atomics per 64-byte entry kept the SMs busy 72 % of the time with DRAM at a quarter of its
+// rate).  Here a CTA takes a tile of kBinTile consecutive entries and
+//   1. bins them by a hash of the target row: one shared-memory counter update per ENTRY (not per value) gives the
+//      entry's rank inside its bin,
+//   2. scans the bin counts and writes (target, entry) pairs into bin order: entries of one target are now
+//      neighbours, up to the few other targets that share its bin,
+//   3. cuts that list into one contiguous piece per lane group (L lanes, one 16-byte pack of the row each); a lane
+//      group walks its piece entry by entry, source rows arriving through a cp.async ring, and keeps accumulating in
+//      registers while the target stays the same: ONE global update per run, no shuffle and no shared-memory atomic
+//      on values.  (A first version combined the runs of a warp step with a segmented scan over the lane groups:
+//      219 warp instructions per 8 entries, issue-bound at 1.49 ms on the Zipf workload.)
+// A tile of 4096 Zipf(1.2) entries over 100,000 targets holds about 1200 distinct targets, so 3-4 times fewer updates
+// reach L2 and the hottest target receives one update per lane group and tile instead of one per entry.  MIN/MAX keep
+// value and entry id per run and settle both with one packed 64-bit atomic per value (see below), ties towards the
+// smaller entry id.  The kernel runs only when the probe flags the index as skewed and not clustered.
+constexpr int kBinTile = 4096;        // entries per CTA
+constexpr int kBinBins = 4096;        // hash bins (power of two)
+constexpr int kBinItems = kBinTile / kThreads;
+constexpr int kBinRing = 8;           // cp.async ring depth in entries per lane group
+
+template <typename T, int VEC> constexpr size_t binned_smem_bytes() {
+  // (target, entry) pairs, then the ring; the bin counters live in the ring's space until the walk starts
+  constexpr size_t ring = sizeof(Pack<T, VEC>) * kThreads * kBinRing;
+  constexpr size_t cnt = sizeof(int) * (kBinBins + kThreads / 32);
+  return sizeof(int2) * kBinTile + (ring > cnt ? ring : cnt);
+}
+
+template <int OP> __device__ __forceinline__ uint64_t pack_minmax(int32_t key, uint64_t slot);
+template <int OP> __device__ __forceinline__ void atom_packed(uint64_t *addr, uint64_t v);
+
+template <typename T, int OP, int VEC>
+__global__ void __launch_bounds__(kThreads, 3) scatter_rows_binned_kernel(ScatterParams p) {
+  using U = acc_t<T>;
+  constexpr int kWarps = kThreads / 32;
+  constexpr bool kMinMax = (OP == kMin || OP == kMax);
+  extern __shared__ __align__(16) unsigned char s_binned[];
+  int2 *s_pair = reinterpret_cast<int2 *>(s_binned);            // x: target row over all batches, y: entry within the tile
+  unsigned char *s_rest = s_binned + sizeof(int2) * kBinTile;
+  auto s_ring = reinterpret_cast<Pack<T, VEC>(*)[kThreads]>(s_rest);   // [kBinRing][kThreads]
+  int *s_cnt = reinterpret_cast<int *>(s_rest);                 // bins, until the walk starts
+  int *s_warp_sum = s_cnt + kBinBins;
+  const int64_t tile0 = (int64_t)blockIdx.x * kBinTile;
+  // not skewed: the one-update-per-entry kernels; sums of a clustered index: the runs kernel
+  if (p.clustered[1] == 0 || (!kMinMax && p.clustered[0] != 0)) return;
+  const T *__restrict__ src = static_cast<const T *>(p.src);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t M = p.B * p.E;
+
+  for (int i = tid; i < kBinBins; i += kThreads) s_cnt[i] = 0;
+  __syncthreads();
+  // 1. targets of this thread's entries (coalesced loads, all in flight), rank inside the bin
+  int row[kBinItems], rank[kBinItems];
+#pragma unroll
+  for (int j = 0; j < kBinItems; ++j) {
+    const int64_t ent = tile0 + j * kThreads + tid;
+    row[j] = -1;
+    if (ent < M) {
+      const int64_t b = (p.B == 1) ? 0 : ent / p.E;
+      const int64_t idx = p.index[b * p.sb + (ent - b * p.E) * p.se];
+      if (idx >= 0 && idx < p.N) row[j] = (int)(b * p.N + idx);   // B * N < 2^31 (checked by the launcher)
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kBinItems; ++j) {
+    rank[j] = 0;
+    if (row[j] >= 0) rank[j] = atomicAdd(&s_cnt[((unsigned)row[j] * 2654435761u) >> 20], 1);
+  }
+  __syncthreads();
+  // 2. exclusive scan of the bin counts (kBinBins / kThreads consecutive bins per thread)
+  {
+    constexpr int kPer = kBinBins / kThreads;
+    int c[kPer], v = 0;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) { c[i] = s_cnt[tid * kPer + i]; v += c[i]; }
+    int incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int o = __shfl_up_sync(kFullMask, incl, off);
+      if (lane >= off) incl += o;
+    }
+    if (lane == 31) s_warp_sum[warp] = incl;
+    __syncthreads();
+    int before = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) before += (w < warp) ? s_warp_sum[w] : 0;
+    int run = before + incl - v;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) { s_cnt[tid * kPer + i] = run; run += c[i]; }
+  }
+  __syncthreads();
+  int n = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) n += s_warp_sum[w];
+#pragma unroll
+  for (int j = 0; j < kBinItems; ++j)
+    if (row[j] >= 0) s_pair[s_cnt[((unsigned)row[j] * 2654435761u) >> 20] + rank[j]] = make_int2(row[j], j * kThreads + tid);
+  __syncthreads();  // the list is complete and the bin counters are dead: their space becomes the ring
+  if (n == 0) return;
+
+  // 3. every lane group walks its piece of the list
+  const int L = 1 << p.l_log2;
+  const int col = lane & (L - 1);
+  const int groups = kThreads >> p.l_log2;
+  const int gid = tid >> p.l_log2;
+  const int64_t Kv = p.K / VEC;
+  // an odd piece length keeps the groups' list reads on different shared-memory banks
+  const int piece = ((n + groups - 1) / groups) | 1;
+  const int start = gid * piece;
+  const int my_n = start >= n ? 0 : (n - start < piece ? n - start : piece);
+  const int2 *list = s_pair + start;
+  const int64_t all_rows = p.B * p.N;
+  U *target = nullptr;
+  uint64_t *packed = nullptr;
+  if constexpr (kMinMax) packed = reinterpret_cast<uint64_t *>(p.arg_out);
+  else target = static_cast<U *>(p.target) + (p.replicas > 1 ? (blockIdx.x % p.replicas) * (p.B * p.N * p.K) : 0);
+  constexpr uint32_t kNone = 0xffffffffu;
+
+  for (int64_t cb = 0; cb < Kv; cb += L) {
+    const int64_t c = cb + col;
+    const bool col_ok = c < Kv;
+    auto issue = [&](int step, int slot) {
+      if (step < my_n && col_ok) {
+        const int64_t ent = tile0 + list[step].y;
+        async_copy_pack<T, VEC>(&s_ring[slot][tid], src + ent * p.K + c * VEC);
+      }
+      async_commit();
+    };
+    U val[VEC];
+    uint32_t arg[kMinMax ? VEC : 1];
+    uint64_t seen[kMinMax ? VEC : 1];   // MIN/MAX: the target's packed words as they were when the run started
+    int cur = -1, cnt = 0;
+    auto restart = [&]() {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        val[k] = reduce_identity<T, OP>();
+        if (kMinMax) arg[k] = kNone;
+      }
+      cnt = 0;
+      if constexpr (kMinMax) {
+        // Fetched now, used when the run ends: the load has the whole run to arrive, so the walk never waits for L2.
+        // The words only ever move towards the winner, so an old copy filters conservatively: an update it lets
+        // through may turn out to be unnecessary, one it stops can never have won.
+        if (cur >= 0 && cur < all_rows && col_ok) {
+          const uint64_t *addr = packed + (int64_t)cur * p.K + c * VEC;
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) seen[k] = *reinterpret_cast<const volatile uint64_t *>(addr + k);
+        }
+      }
+    };
+    auto flush = [&]() {  // one update for the finished run of target `cur`
+      if (cur < 0 || cur >= all_rows || !col_ok) return;
+      if constexpr (kMinMax) {
+        uint64_t *addr = packed + (int64_t)cur * p.K + c * VEC;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          if (arg[k] == kNone) continue;
+          const uint64_t w = pack_minmax<OP>(enc_key(val[k]), (uint64_t)arg[k] + 1);
+          if (OP == kMax) {
+            if (w > seen[k]) atomicMax(reinterpret_cast<unsigned long long *>(addr + k), (unsigned long long)w);
+          } else {
+            if (w < seen[k]) atomicMin(reinterpret_cast<unsigned long long *>(addr + k), (unsigned long long)w);
+          }
+        }
+      } else {
+        apply_acc<OP, U, VEC>(target + (int64_t)cur * p.K + c * VEC, val);
+        if (p.count != nullptr && c == 0) {
+          const int64_t b = cur / p.N;
+          if (p.sb != 0 || b == 0) atomicAdd(p.count + (p.sb ? cur : cur - b * p.N), cnt);
+        }
+      }
+    };
+#pragma unroll
+    for (int j = 0; j < kBinRing; ++j) issue(j, j);
+    restart();
+    int slot = 0;
+    for (int step = 0; step < piece; ++step) {   // CTA-uniform trip count: one commit group per step and thread
+      async_wait_all_but<kBinRing - 1>();
+      if (step < my_n) {
+        const int2 pr = list[step];
+        if (pr.x != cur) {
+          flush();
+          cur = pr.x;
+          restart();
+        }
+        const Pack<T, VEC> v = s_ring[slot][tid];
+        cnt += 1;
+        if (col_ok) {
+          if constexpr (kMinMax) {
+            const int64_t ent = tile0 + pr.y;
+            const uint32_t e = (uint32_t)(p.B == 1 ? ent : ent % p.E);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+              const U x = to_acc<T>(v.v[k]);
+              if (is_nan(x)) continue;
+              const bool better = (OP == kMin) ? (x < val[k]) : (x > val[k]);
+              // the identity is a legal value: a first winner equal to it must still be recorded
+              if (better || (x == val[k] && e < arg[k])) { val[k] = x; arg[k] = e; }
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) val[k] = combine<OP, U>(val[k], to_acc<T>(v.v[k]));
+          }
+        }
+      }
+      issue(step + kBinRing, slot);
+      slot = (slot + 1) & (kBinRing - 1);
+    }
+    async_wait_all_but<0>();
+    flush();
+  }
+}
+
 template <typename T, int OP>
 __global__ void __launch_bounds__(kThreads) scatter_elems_kernel(ScatterParams p) {
   using U = acc_t<T>;
@@ -756,21 +876,26 @@ __device__ __forceinline__ void packed_update(uint64_t *addr, T x, int64_t e, in
 
 template <typename T, int OP, int VEC>
 __global__ void __launch_bounds__(kThreads) packed_rows_kernel(ScatterParams p) {
+  if (p.binned && p.clustered[1] != 0) return;  // a skewed index: scatter_rows_binned_kernel takes it
   const T *__restrict__ src = static_cast<const T *>(p.src);
   uint64_t *packed = reinterpret_cast<uint64_t *>(p.arg_out);
   const int L = 1 << p.l_log2;
   const int64_t Kv = p.K / VEC;
-  const int64_t entry = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> p.l_log2;
   const int col = threadIdx.x & (L - 1);
-  if (entry >= p.B * p.E) return;
-  const int64_t b = entry / p.E, e = entry - b * p.E;
-  const int64_t idx = p.index[b * p.sb + e * p.se];
-  if (idx < 0 || idx >= p.N) return;
-  const int64_t obase = (b * p.N + idx) * p.K;
-  for (int64_t c = col; c < Kv; c += L) {
-    const Pack<T, VEC> v = ld_stream<T, VEC>(src + entry * p.K + c * VEC);
+  const int64_t per_cta = kThreads >> p.l_log2;
+  const int64_t M = p.B * p.E;
+  for (int64_t first = (int64_t)blockIdx.x * per_cta; first < M; first += (int64_t)gridDim.x * per_cta) {  // capped grid
+    const int64_t entry = first + (threadIdx.x >> p.l_log2);
+    if (entry >= M) continue;
+    const int64_t b = entry / p.E, e = entry - b * p.E;
+    const int64_t idx = p.index[b * p.sb + e * p.se];
+    if (idx < 0 || idx >= p.N) continue;
+    const int64_t obase = (b * p.N + idx) * p.K;
+    for (int64_t c = col; c < Kv; c += L) {
+      const Pack<T, VEC> v = ld_stream<T, VEC>(src + entry * p.K + c * VEC);
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) packed_update<T, OP>(packed + obase + c * VEC + i, v.v[i], e, p.fresh);
+      for (int i = 0; i < VEC; ++i) packed_update<T, OP>(packed + obase + c * VEC + i, v.v[i], e, p.fresh);
+    }
   }
 }
 
@@ -945,6 +1070,15 @@ inline int64_t env_bytes(const char *name, int64_t fallback) {
   return x > 0 ? (int64_t)x : fallback;
 }
 
+// Grid of the one-update-per-entry row kernels, which walk the entries with a grid stride: enough CTAs to fill the
+// device many times over (dynamic balance), few enough that a launch which turns out to have nothing to do is cheap.
+inline unsigned direct_grid(int64_t entries, int l_log2) {
+  const int64_t per_cta = kThreads >> l_log2;
+  const int64_t need = (entries + per_cta - 1) / per_cta;
+  const int64_t cap = (int64_t)sm_count() * 64;
+  return (unsigned)(need < 1 ? 1 : (need < cap ? need : cap));
+}
+
 inline bool grid_for(int64_t threads, unsigned *blocks) {
   const int64_t nb = (threads + kThreads - 1) / kThreads;
   if (nb > 2147483647LL) return false;
@@ -975,7 +1109,12 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
   // Replicated accumulation: small output, index constant along the features, enough entries to matter.
   int replicas = replicas_for(total * (int64_t)sizeof(U));
   if (!rows || p.B * p.E < (1 << 16)) replicas = 1;
-  replicas = (int)env_bytes("TSB_SCATTER_REPLICAS", replicas);  // test / tuning hook
+  const bool small_output = replicas > 1;   // "small" as in: could be contended, several copies would fit in L2
+  // fp32 accumulators: a skewed index is taken by the tile kernel that walks runs, which needs no copies, and for any
+  // other index the copies only cost their initialisation and the fold (1 M entries into 65,536 rows x 32 floats:
+  // 0.136 ms with seven copies, 0.082 ms without)
+  if (OP == kSum && std::is_same<U, float>::value) replicas = 1;
+  replicas = (int)env_bytes("TSB_SCATTER_REPLICAS", replicas);  // test hook
   if (replicas > replicas_for(total * (int64_t)sizeof(U))) replicas = replicas_for(total * (int64_t)sizeof(U));
   int *flag = static_cast<int *>(workspace);                       // first 256 bytes: the probe's verdict
   void *scratch = static_cast<unsigned char *>(workspace) + 256;  // then accumulators / replicas
@@ -994,18 +1133,44 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
 
   // MIN / MAX on 4-byte accumulation types: value and arg in one pass through packed 64-bit atomics
   if constexpr (kMinMax && sizeof(U) == 4) {
-    // (small, contended outputs do better with the replicated two-pass scheme below)
-    if (p.E < 0xfffffffell && replicas == 1) {
+    // Small outputs (the ones other types replicate): the tile kernel, which walks runs of equal targets with one
+    // packed update per run when the probe calls the index skewed and sends one packed update per element otherwise
+    // (1 M entries into 65,536 rows x 32: 0.17 ms against 0.31 ms for the replicated two-pass scheme below; 33.5 M
+    // Zipf entries into 100,000 rows x 16: 2.65 ms before).  TSB_SCATTER_CACHED=0 (test hook) keeps the two-pass scheme.
+    const char *skew_env = std::getenv("TSB_SCATTER_CACHED");  // test hook: "0" / "1" dictate the skew verdict
+    const int forced_skew_mm = (skew_env != nullptr && (*skew_env == '0' || *skew_env == '1')) ? (*skew_env - '0') : -1;
+    const bool vec_rows = rows && (p.K % kFull == 0) && aligned16(p.src);
+    const bool binned = replicas > 1 && forced_skew_mm != 0 && vec_rows && p.B * p.N < (1ll << 31) && p.E > 0;
+    if (p.E < 0xfffffffell && (replicas == 1 || binned)) {
       if (total == 0) return TSB_OK;
       if (!grid_for(total, &blocks)) return TSB_ERR_TOO_LARGE;
       packed_init_kernel<T, OP><<<blocks, kThreads, 0, stream>>>(static_cast<const T *>(p.out),
                                                                   reinterpret_cast<uint64_t *>(p.arg_out), total, p.fresh);
       if (p.E > 0) {
-        const bool vec_ok = rows && (p.K % kFull == 0) && aligned16(p.src);
+        const bool vec_ok = vec_rows;
         const int64_t Kv = p.K / (vec_ok ? kFull : 1);
         p.l_log2 = (int)(Kv >= 32 ? 5 : ilog2_ceil(Kv));
+        p.clustered = nullptr;
+        p.binned = 0;
+        if (binned) {
+          p.binned = 1;
+          const int64_t bin_tiles = (p.B * p.E + kBinTile - 1) / kBinTile;
+          if (bin_tiles > 2147483647LL) return TSB_ERR_TOO_LARGE;
+          p.clustered = flag;
+          scatter_probe_kernel<<<1, kThreads, 0, stream>>>(p, flag, -1, forced_skew_mm);
+          constexpr size_t smem = binned_smem_bytes<T, kFull>();
+          static std::atomic<bool> allowed[64];  // per device; setting the attribute twice is harmless
+          int dev = 0;
+          if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !allowed[dev]) {
+            if (cudaFuncSetAttribute(scatter_rows_binned_kernel<T, OP, kFull>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem) != cudaSuccess)
+              return TSB_ERR_LAUNCH;
+            allowed[dev] = true;
+          }
+          scatter_rows_binned_kernel<T, OP, kFull><<<(unsigned)bin_tiles, kThreads, smem, stream>>>(p);
+        }
         if (rows) {
-          if (!grid_for((p.B * p.E) << p.l_log2, &blocks)) return TSB_ERR_TOO_LARGE;
+          blocks = direct_grid(p.B * p.E, p.l_log2);
           if (vec_ok) packed_rows_kernel<T, OP, kFull><<<blocks, kThreads, 0, stream>>>(p);
           else packed_rows_kernel<T, OP, 1><<<blocks, kThreads, 0, stream>>>(p);
         } else {
@@ -1058,7 +1223,7 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
       scatter_probe_kernel<<<1, kThreads, 0, stream>>>(p, flag, forced, forced_skew);
       unsigned blocks_direct = 0, blocks_batched = 0, blocks_range = 0;
       if (!grid_for((p.B * p.E + kRangeBatches * kRangeGroups - 1) / (kRangeBatches * kRangeGroups), &blocks_range)) return TSB_ERR_TOO_LARGE;  // 1024 entries per warp
-      if (!grid_for((p.B * p.E) << p.l_log2, &blocks_direct)) return TSB_ERR_TOO_LARGE;                    // L lanes per entry
+      blocks_direct = direct_grid(p.B * p.E, p.l_log2);                                                      // L lanes per entry, grid stride
       if (!grid_for((p.B * p.E + kBatches - 1) / kBatches, &blocks_batched)) return TSB_ERR_TOO_LARGE;  // 128 entries per warp
       const bool zero_slices = sliced && !k16 && p.fresh;
       const int64_t all_rows = p.B * p.N;
@@ -1068,36 +1233,26 @@ int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t strea
         if (zero_slices && cudaMemsetAsync(static_cast<U *>(p.target) + lo * p.K, 0,
                                            (size_t)((hi - lo) * p.K) * sizeof(U), stream) != cudaSuccess)
           return TSB_ERR_LAUNCH;
-        bool cached = false;
         if constexpr (OP == kSum && std::is_same<U, float>::value) {
-          // small, replicated (= possibly contended) output with short rows: accumulate through the shared-memory cache
-          const bool want = forced_skew == 1 || (forced_skew != 0 && replicas > 1);
-          const int64_t row_bytes = p.K * (int64_t)sizeof(float);
-          if (want && vec_ok && !sliced && row_bytes <= 256 && all_rows < (1ll << 31)) {
-            int64_t tile = (p.B * p.E) / (148 * 8);
-            tile = tile < 1024 ? 1024 : (tile > 8192 ? 8192 : tile);
-            const int64_t cache_bytes = 32 * 1024;
-            int slots_log2 = 0;
-            while ((2ll << slots_log2) * (row_bytes + 8) <= cache_bytes && (2ll << slots_log2) <= tile / 4) ++slots_log2;
-            const int64_t tiles = (p.B * p.E + tile - 1) / tile;
-            if (tiles <= 2147483647LL && slots_log2 >= 4) {
-              const size_t smem = ((size_t)1 << slots_log2) * (size_t)(row_bytes + 8);
-              static std::atomic<bool> allowed[64];  // per device; setting the attribute twice is harmless
-              int dev = 0;
-              if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !allowed[dev]) {
-                if (cudaFuncSetAttribute(scatter_rows_cached_kernel<T, kFull>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kCacheBytesMax) != cudaSuccess)
-                  return TSB_ERR_LAUNCH;
-                allowed[dev] = true;
-              }
-              scatter_rows_cached_kernel<T, kFull><<<(unsigned)tiles, kThreads, smem, stream>>>(p, (int)tile, slots_log2);
-              cached = true;
+          // small (= possibly contended) output: a skewed index goes through scatter_rows_binned_kernel, any other
+          // through the kernels below, which then leave skewed indices alone (device-side choice, ScatterParams::binned)
+          const bool want = forced_skew == 1 || (forced_skew != 0 && small_output);
+          const int64_t bin_tiles = (p.B * p.E + kBinTile - 1) / kBinTile;
+          if (want && vec_ok && !sliced && all_rows < (1ll << 31) && bin_tiles <= 2147483647LL) {
+            constexpr size_t smem = binned_smem_bytes<T, kFull>();
+            static std::atomic<bool> allowed[64];  // per device; setting the attribute twice is harmless
+            int dev = 0;
+            if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !allowed[dev]) {
+              if (cudaFuncSetAttribute(scatter_rows_binned_kernel<T, kSum, kFull>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem) != cudaSuccess)
+                return TSB_ERR_LAUNCH;
+              allowed[dev] = true;
             }
+            p.binned = 1;
+            scatter_rows_binned_kernel<T, kSum, kFull><<<(unsigned)bin_tiles, kThreads, smem, stream>>>(p);
           }
         }
-        if (cached) {  // it covers the skewed and the plain case; clustered indices still go to the runs kernel
-          scatter_rows_runs_kernel<T, OP, kFull><<<blocks_batched, kThreads, 0, stream>>>(p, lo, hi, replicas);
-        } else if (vec_ok) {
+        if (vec_ok) {
           bool ranged = false;
           if constexpr (OP == kSum) {  // only sums are ever sliced
             if (sliced) { scatter_rows_range_kernel<T, OP, kFull><<<blocks_range, kThreads, 0, stream>>>(p, lo, hi); ranged = true; }
@@ -1241,6 +1396,7 @@ extern "C" int tsb_scatter(const void *src, const int64_t *index, void *out, int
   p.l_log2 = 0;
   p.fresh = out_seeded ? 0 : 1;
   p.replicas = 1;
+  p.binned = 0;
   p.clustered = nullptr;
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
     switch (reduce) {
@@ -1300,7 +1456,7 @@ extern "C" int tsb_scatter_sum_slice(const void *src, const int64_t *index, void
   p.arg_out = nullptr; p.count = nullptr;
   p.B = 1; p.E = E; p.K = K; p.N = N;
   p.sb = 0; p.se = 1; p.sk = 0;
-  p.l_log2 = 0; p.fresh = 1; p.replicas = 1; p.clustered = nullptr;
+  p.l_log2 = 0; p.fresh = 1; p.replicas = 1; p.binned = 0; p.clustered = nullptr;
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
     return run_scatter_sum_slice<scalar_t>(p, row_lo, row_hi, static_cast<int *>(workspace),
                                            reinterpret_cast<cudaStream_t>(stream));

@@ -474,23 +474,36 @@ int run_scatter_grouped(const void *src, const int64_t *index, void *out, int64_
 
 namespace tsb {
 namespace {
-// out[i] = sum over q of slabs[q * elems + i], accumulated in acc_t<T> (fp32 for 16-bit), 16 bytes per thread.
-template <typename T, int VEC>
-__global__ void __launch_bounds__(kThreads) sum_slabs_kernel(const T *__restrict__ slabs, T *__restrict__ out, int world, int64_t elems) {
+// out[i] = sum over q of slabs[q * elems + i], accumulated in acc_t<T> (fp32 for 16-bit), 16 bytes of slab per thread.
+// S is the slabs' element type: T, or acc_t<T> when the partial sums travelled in accumulation precision.
+template <typename S, typename T, int VEC>
+__global__ void __launch_bounds__(kThreads) sum_slabs_kernel(const S *__restrict__ slabs, T *__restrict__ out, int world, int64_t elems) {
   const int64_t i = ((int64_t)blockIdx.x * kThreads + threadIdx.x) * VEC;
   if (i >= elems) return;
   acc_t<T> acc[VEC];
 #pragma unroll
   for (int k = 0; k < VEC; ++k) acc[k] = (acc_t<T>)0;
   for (int q = 0; q < world; ++q) {
-    const Pack<T, VEC> v = ld_stream<T, VEC>(slabs + (int64_t)q * elems + i);
+    const Pack<S, VEC> v = ld_stream<S, VEC>(slabs + (int64_t)q * elems + i);
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) acc[k] += to_acc<T>(v.v[k]);
+    for (int k = 0; k < VEC; ++k) acc[k] += (acc_t<T>)to_acc<S>(v.v[k]);
   }
   Pack<T, VEC> o;
 #pragma unroll
   for (int k = 0; k < VEC; ++k) o.v[k] = from_acc<T>(acc[k]);
   st_stream<T, VEC>(out + i, o);
+}
+
+template <typename S, typename T>
+int launch_sum_slabs(const void *slabs, void *out, int world, int64_t elems, cudaStream_t st) {
+  constexpr int kFull = full_vec<S>();
+  const bool vec_ok = elems % kFull == 0 && aligned16(slabs) && (reinterpret_cast<uintptr_t>(out) % (sizeof(T) * kFull) == 0);
+  const int64_t threads = vec_ok ? elems / kFull : elems;
+  const int64_t blocks = (threads + kThreads - 1) / kThreads;
+  if (blocks > 2147483647LL) return TSB_ERR_TOO_LARGE;
+  if (vec_ok) sum_slabs_kernel<S, T, kFull><<<(unsigned)blocks, kThreads, 0, st>>>(static_cast<const S *>(slabs), static_cast<T *>(out), world, elems);
+  else sum_slabs_kernel<S, T, 1><<<(unsigned)blocks, kThreads, 0, st>>>(static_cast<const S *>(slabs), static_cast<T *>(out), world, elems);
+  return launch_status();
 }
 }  // namespace
 }  // namespace tsb
@@ -546,8 +559,8 @@ extern "C" int tsb_segment_csr_perm(const void *src, const int64_t *rowptr, cons
 
 extern "C" int tsb_segment_csr_perm_routed(const void *src, const int64_t *rowptr, const int32_t *perm,
                                            void *const *owner_base, int world, int rank, int64_t rows_per_owner,
-                                           int64_t E, int64_t K, int64_t N, int dtype, int reduce, void *workspace,
-                                           size_t workspace_bytes, tsb_stream_t stream) {
+                                           int wide_staging, int64_t E, int64_t K, int64_t N, int dtype, int reduce,
+                                           void *workspace, size_t workspace_bytes, tsb_stream_t stream) {
   using namespace tsb;
   if (E < 0 || K < 0 || N < 0 || owner_base == nullptr || world < 1 || world > CsrParams::kMaxRoute) return TSB_ERR_ARG;
   if (K == 0 || N == 0) return TSB_OK;
@@ -566,26 +579,21 @@ extern "C" int tsb_segment_csr_perm_routed(const void *src, const int64_t *rowpt
   p.route_world = world;
   p.route_rank = rank;
   p.route_rows = rows_per_owner;
+  p.route_wide = wide_staging != 0;
   p.workspace = workspace;
   p.workspace_bytes = workspace_bytes;
   return launch_csr_reduce(p, dtype, reduce, reinterpret_cast<cudaStream_t>(stream));
 }
 
-extern "C" int tsb_sum_slabs(const void *slabs, void *out, int world, int64_t elems, int dtype, tsb_stream_t stream) {
+extern "C" int tsb_sum_slabs(const void *slabs, void *out, int world, int64_t elems, int dtype, int wide_slabs,
+                             tsb_stream_t stream) {
   using namespace tsb;
   if (world < 1 || elems < 0) return TSB_ERR_ARG;
   if (elems == 0) return TSB_OK;
   if (slabs == nullptr || out == nullptr) return TSB_ERR_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   return TSB_DISPATCH_DTYPE(dtype, [&]() -> int {
-    constexpr int kFull = full_vec<scalar_t>();
-    const bool vec_ok = elems % kFull == 0 && aligned16(slabs) && aligned16(out);
-    const int64_t threads = vec_ok ? elems / kFull : elems;
-    const int64_t blocks = (threads + kThreads - 1) / kThreads;
-    if (blocks > 2147483647LL) return TSB_ERR_TOO_LARGE;
-    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (vec_ok) sum_slabs_kernel<scalar_t, kFull><<<(unsigned)blocks, kThreads, 0, st>>>(static_cast<const scalar_t *>(slabs), static_cast<scalar_t *>(out), world, elems);
-    else sum_slabs_kernel<scalar_t, 1><<<(unsigned)blocks, kThreads, 0, st>>>(static_cast<const scalar_t *>(slabs), static_cast<scalar_t *>(out), world, elems);
-    return launch_status();
+    if (wide_slabs) return launch_sum_slabs<acc_t<scalar_t>, scalar_t>(slabs, out, world, elems, st);
+    return launch_sum_slabs<scalar_t, scalar_t>(slabs, out, world, elems, st);
   });
 }
-

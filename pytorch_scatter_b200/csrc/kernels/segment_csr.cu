@@ -205,6 +205,30 @@ __device__ __forceinline__ T *row_address(const CsrParams &p, int64_t grow, int6
   }
 }
 
+// A routed row of a 16-bit source kept in fp32 (CsrParams::route_wide): this lane's VEC sums go to the owner's
+// fp32 staging buffer as they are.  True if the row was stored.
+template <typename T, int REDUCE, int VEC, bool EXTRAS, typename ArgT>
+__device__ __forceinline__ bool store_wide_routed(const CsrParams &p, const RowAcc<T, REDUCE, VEC, ArgT> &acc,
+                                                  int64_t grow, int64_t col) {
+  if constexpr (EXTRAS && sizeof(T) == 2 && REDUCE == kSum) {
+    if (p.route_world > 0 && p.route_wide) {
+      const int64_t q = grow / p.route_rows;
+      const int64_t local = grow - q * p.route_rows;
+      float *dst = static_cast<float *>(p.route_base[q]) + ((int64_t)p.route_rank * p.route_rows + local) * p.K + col;
+      if constexpr (VEC % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < VEC; i += 4)
+          *reinterpret_cast<float4 *>(dst + i) = make_float4(acc.val[i], acc.val[i + 1], acc.val[i + 2], acc.val[i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) dst[i] = acc.val[i];
+      }
+      return true;
+    }
+  }
+  return false;
+}
+
 // Writes one finished row (this lane's VEC columns of it).  `acc` is the reduction over the row's
 // source entries only; in kCooSeeded mode the row's previous value of `out` joins here.  Arg indices
 // in `acc` are relative to `arg_base`; `arg_none` marks "no element won" and becomes `sentinel`.
@@ -400,7 +424,7 @@ __global__ void __launch_bounds__(32, stream_ctas_per_sm<T, REDUCE, VEC>()) csr_
           head_pending = false;
         } else {
           const int64_t grow = b * p.N + row;
-          if (sub == 0 && col_ok) {
+          if (sub == 0 && col_ok && !store_wide_routed<T, REDUCE, VEC, EXTRAS, int>(p, tot, grow, c * VEC)) {
             write_row<T, REDUCE, VEC, int>(tot, row_address<T, REDUCE, EXTRAS>(p, grow, c * VEC),
                                            kArg ? p.arg_out + grow * p.K + c * VEC : nullptr,
                                            (int64_t)(cur_end - cur_start), p.mode, p.E, INDIRECT ? 0 : cs, kRelInf);
@@ -715,9 +739,10 @@ __global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeo
         if (Acc::kPair) oarg[i] = g.carry_arg[at + i];
       }
       acc.merge(oval, oarg);
-      write_row<T, REDUCE, VEC, int64_t>(acc, row_address<T, REDUCE, EXTRAS>(p, grow, c * VEC),
-                                         kArg ? p.arg_out + grow * p.K + c * VEC : nullptr, re - rs, p.mode, p.E,
-                                         0, p.E);
+      if (!store_wide_routed<T, REDUCE, VEC, EXTRAS, int64_t>(p, acc, grow, c * VEC))
+        write_row<T, REDUCE, VEC, int64_t>(acc, row_address<T, REDUCE, EXTRAS>(p, grow, c * VEC),
+                                           kArg ? p.arg_out + grow * p.K + c * VEC : nullptr, re - rs, p.mode, p.E,
+                                           0, p.E);
     }
   }
   if (lane == 0 && p.count_out != nullptr) {
@@ -837,8 +862,7 @@ int launch_csr_reduce(const CsrParams &p, int dtype, int reduce, cudaStream_t st
   if (p.indptr == nullptr || (p.out == nullptr && p.route_world == 0)) return TSB_ERR_ARG;
   if (p.route_world != 0) {
     if (p.route_world < 0 || p.route_world > CsrParams::kMaxRoute || p.route_rank < 0 || p.route_rank >= p.route_world ||
-        p.route_rows < 1 || p.route_rows * p.route_world < p.N || p.B != 1 || p.mode == kCooSeeded ||
-        (reduce != TSB_SUM && reduce != TSB_MEAN))
+        p.route_rows < 1 || p.route_rows * p.route_world < p.N || p.B != 1 || p.mode == kCooSeeded || reduce != TSB_SUM)
       return TSB_ERR_ARG;
     for (int q = 0; q < p.route_world; ++q)
       if (p.route_base[q] == nullptr) return TSB_ERR_ARG;

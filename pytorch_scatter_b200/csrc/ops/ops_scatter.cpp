@@ -350,7 +350,7 @@ torch::Tensor segment_sum_perm(torch::Tensor src, torch::Tensor rowptr, torch::T
 // The same reduction with every finished row stored straight into its owner's staging buffer
 // (owner_ptrs: device addresses of the `world` buffers [world, rows_per_owner, ...], peers included).
 void segment_sum_perm_routed(torch::Tensor src, torch::Tensor rowptr, torch::Tensor perm, std::vector<int64_t> owner_ptrs,
-                             int64_t rank, int64_t rows_per_owner, int64_t dim_size) {
+                             int64_t rank, int64_t rows_per_owner, int64_t dim_size, bool wide_staging) {
   TSB_CHECK_CUDA(src);
   TSB_CHECK_CUDA(rowptr);
   TSB_CHECK_CUDA(perm);
@@ -370,19 +370,23 @@ void segment_sum_perm_routed(torch::Tensor src, torch::Tensor rowptr, torch::Ten
   const size_t ws_bytes = tsb_segment_csr_perm_workspace_bytes(1, E, K, dim_size, dtype_enum(src), TSB_SUM);
   auto workspace = torch::empty({(int64_t)ws_bytes}, src.options().dtype(torch::kUInt8));
   check_status(tsb_segment_csr_perm_routed(src.data_ptr(), rowptr.data_ptr<int64_t>(), perm.data_ptr<int32_t>(),
-                                           bases.data(), world, (int)rank, rows_per_owner, E, K, dim_size, dtype_enum(src),
+                                           bases.data(), world, (int)rank, rows_per_owner, wide_staging ? 1 : 0, E, K, dim_size, dtype_enum(src),
                                            TSB_SUM, workspace.data_ptr(), ws_bytes, current_stream()),
                "tsb_segment_csr_perm_routed");
 }
 
-// slabs [world, ...] -> their sum over dim 0 (the owner's last step of the routed scatter)
-torch::Tensor sum_slabs(torch::Tensor slabs) {
+// slabs [world, ...] -> their sum over dim 0 (the owner's last step of the routed scatter), in `dtype`; the slabs
+// hold `dtype` or, for fp16 / bf16 results, fp32 partial sums
+torch::Tensor sum_slabs(torch::Tensor slabs, at::ScalarType dtype) {
   TSB_CHECK_CUDA(slabs);
   TSB_CHECK_INPUT(slabs.dim() >= 1 && slabs.is_contiguous());
+  const bool wide = slabs.scalar_type() != dtype;
+  TSB_CHECK_INPUT(!wide || (slabs.scalar_type() == at::ScalarType::Float &&
+                            (dtype == at::ScalarType::Half || dtype == at::ScalarType::BFloat16)));
   c10::cuda::CUDAGuard guard(slabs.device());
-  auto out = torch::empty(slabs.sizes().slice(1), slabs.options());
-  check_status(tsb_sum_slabs(slabs.data_ptr(), out.data_ptr(), (int)slabs.size(0), out.numel(), dtype_enum(slabs),
-                             current_stream()),
+  auto out = torch::empty(slabs.sizes().slice(1), slabs.options().dtype(dtype));
+  check_status(tsb_sum_slabs(slabs.data_ptr(), out.data_ptr(), (int)slabs.size(0), out.numel(), dtype_enum(out),
+                             wide ? 1 : 0, current_stream()),
                "tsb_sum_slabs");
   return out;
 }

@@ -212,13 +212,14 @@ def _routed_staging(world: int, rows: int, feat: tuple, dtype: torch.dtype, devi
     return _ROUTED_STAGING[key]
 
 
-def routed_exchange_available(src_local: torch.Tensor, dim_size: int, group=None) -> bool:
+def routed_exchange_available(src_local: torch.Tensor, dim_size: int, group=None, wide_partials: bool = True) -> bool:
     """Sets up the staging buffers :func:`scatter_sum_routed` needs for this shape and says whether that worked on
     EVERY rank (a collective: all ranks must call it).  False means: use :func:`scatter_sum_overlapped`."""
     world = dist.get_world_size(group)
     ok = 1
     try:
-        _routed_staging(world, -(-dim_size // world), tuple(src_local.shape[1:]), src_local.dtype, src_local.device, group)
+        _routed_staging(world, -(-dim_size // world), tuple(src_local.shape[1:]),
+                        _staging_dtype(src_local.dtype, wide_partials), src_local.device, group)
     except Exception as exc:  # noqa: BLE001  (no symmetric memory on this box, whatever the reason)
         print(f'[pytorch_scatter_b200.dist] routed exchange unavailable: {type(exc).__name__}: {exc}', flush=True)
         ok = 0
@@ -230,8 +231,12 @@ def routed_exchange_available(src_local: torch.Tensor, dim_size: int, group=None
 ROUTED_PHASES = ('grouping', 'reduction + peer stores', 'barrier', 'slab sum')
 
 
+def _staging_dtype(dtype: torch.dtype, wide: bool) -> torch.dtype:
+    return torch.float32 if wide and dtype in (torch.float16, torch.bfloat16) else dtype
+
+
 def scatter_sum_routed(src_local: torch.Tensor, index_local: torch.Tensor, dim_size: int, group=None,
-                       timeline: Optional[list] = None) -> torch.Tensor:
+                       timeline: Optional[list] = None, wide_partials: bool = True) -> torch.Tensor:
     """Edge-sharded ``scatter(sum)`` along dim 0 with the exchange fused into the reduction kernel.
 
     Every rank groups its entry ids by target row and reduces all ``dim_size`` rows through that permutation in one
@@ -245,13 +250,18 @@ def scatter_sum_routed(src_local: torch.Tensor, index_local: torch.Tensor, dim_s
     buffer ``i % 2`` of its peers only after the barrier of call ``i - 1``, which every peer reaches after it has
     finished adding up call ``i - 2`` (the last reader of that buffer).
 
+    ``wide_partials`` (default): fp16 / bf16 partial sums cross NVLink as fp32 and are rounded once, by the owner, so
+    the result equals the single-GPU operator's up to summation order.  ``False`` halves the NVLink bytes of 16-bit
+    sources at the price of one more rounding per rank (error up to ``world`` half-ulps of the largest partial).
+
     ``timeline``, if given, receives ``len(ROUTED_PHASES) + 1`` CUDA events recorded on the current stream at the
     phase borders (see :data:`ROUTED_PHASES`).
     """
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     feat = tuple(src_local.shape[1:])
     rows = -(-dim_size // world)
-    st = _routed_staging(world, rows, feat, src_local.dtype, src_local.device, group)
+    wide = wide_partials and src_local.dtype in (torch.float16, torch.bfloat16)
+    st = _routed_staging(world, rows, feat, _staging_dtype(src_local.dtype, wide), src_local.device, group)
     half = st['calls'] % 2
     st['calls'] += 1
     buf, handle = st['buf'][half], st['handle']
@@ -266,7 +276,7 @@ def scatter_sum_routed(src_local: torch.Tensor, index_local: torch.Tensor, dim_s
     mark()
     rowptr, perm = torch.ops.torch_scatter.scatter_group(index_local, dim_size)
     mark()
-    torch.ops.torch_scatter.segment_sum_perm_routed(src_local, rowptr, perm, ptrs, rank, rows, dim_size)
+    torch.ops.torch_scatter.segment_sum_perm_routed(src_local, rowptr, perm, ptrs, rank, rows, dim_size, wide)
     valid = min(max(dim_size - rank * rows, 0), rows)   # rows of this rank's block that exist; the rest is padding
     if valid < rows:                                    # nobody writes padding rows: keep them zero
         buf[:, valid:].zero_()
@@ -274,7 +284,7 @@ def scatter_sum_routed(src_local: torch.Tensor, index_local: torch.Tensor, dim_s
     # a bounded wait: a rank that never arrives ends the call with an error instead of hanging the GPUs
     handle.barrier(channel=half, timeout_ms=60000)      # every rank's rows have landed
     mark()
-    out = torch.ops.torch_scatter.sum_slabs(buf)
+    out = torch.ops.torch_scatter.sum_slabs(buf, src_local.dtype)
     mark()
     return out
 

@@ -509,8 +509,11 @@ def test_routed_rows_two_ranks_emulated():
     gen = torch.Generator().manual_seed(57)
     world, N, K = 2, 1001, 16
     rows = -(-N // world)
-    for dtype in (torch.float32, torch.bfloat16, torch.int64):
-        staging = [torch.full((world, rows, K), 9, dtype=dtype).cuda() for _ in range(world)]   # owner q's buffer
+    for dtype, wide in ((torch.float32, True), (torch.bfloat16, False), (torch.bfloat16, True), (torch.float16, True),
+                        (torch.int64, True)):
+        # wide: 16-bit partial sums are staged in fp32 and rounded once by the owner
+        stage_dtype = torch.float32 if wide and dtype in (torch.float16, torch.bfloat16) else dtype
+        staging = [torch.full((world, rows, K), 9, dtype=stage_dtype).cuda() for _ in range(world)]   # owner q's buffer
         ptrs = [t.data_ptr() for t in staging]
         shards = []
         for rank in range(world):
@@ -520,14 +523,18 @@ def test_routed_rows_two_ranks_emulated():
             src = rand_src(gen, (E, K), dtype)
             shards.append((src, index))
             rowptr, perm = torch.ops.torch_scatter.scatter_group(index.cuda(), N)
-            torch.ops.torch_scatter.segment_sum_perm_routed(src.cuda(), rowptr, perm, ptrs, rank, rows, N)
-        got = torch.cat([torch.ops.torch_scatter.sum_slabs(buf) for buf in staging])[:N]
+            torch.ops.torch_scatter.segment_sum_perm_routed(src.cuda(), rowptr, perm, ptrs, rank, rows, N, wide)
+        got = torch.cat([torch.ops.torch_scatter.sum_slabs(buf, dtype) for buf in staging])[:N]
+        assert got.dtype == dtype
         src_all = torch.cat([s for s, _ in shards])
         index_all = torch.cat([i for _, i in shards])
         if dtype.is_floating_point:
             want64 = oracle.scatter(src_all.double().view(1, -1, K), index_all.view(1, -1, 1), N, 'sum')[0][0]
             mass64 = oracle.scatter(src_all.double().abs().view(1, -1, K), index_all.view(1, -1, 1), N, 'sum')[0][0]
-            assert_sum_close(got.to(dtype), want64, mass64, what=f'routed {dtype}')
+            assert_sum_close(got, want64, mass64, what=f'routed {dtype}')
+            if wide and dtype != torch.float32:   # unrounded partials: as good as the single-GPU operator
+                want = oracle.scatter(src_all.view(1, -1, K), index_all.view(1, -1, 1), N, 'sum')[0][0]
+                assert_close(got, want, what=f'routed {dtype}, fp32 partials')
         else:
             want = oracle.scatter(src_all.view(1, -1, K), index_all.view(1, -1, 1), N, 'sum')[0][0]
             assert_close(got, want, what=f'routed {dtype}')
