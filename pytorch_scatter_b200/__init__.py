@@ -36,6 +36,7 @@ if torch.version.cuda is not None and cuda_version != -1:  # pragma: no cover
             f'Detected that PyTorch and torch_scatter were compiled with different CUDA major '
             f'versions ({_t_major} vs {_major}).')
 
+from . import _meta  # noqa  (fake kernels for tracing compilers)
 from .scatter import scatter_sum, scatter_add, scatter_mul  # noqa
 from .scatter import scatter_mean, scatter_min, scatter_max, scatter  # noqa
 from .segment_csr import segment_sum_csr, segment_add_csr  # noqa

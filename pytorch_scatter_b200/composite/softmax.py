@@ -23,6 +23,9 @@ def _fused_ok(src: torch.Tensor, index: torch.Tensor) -> bool:
     order costs one small kernel and a host sync (the same kind upstream pays to infer ``dim_size``)."""
     if index.dim() != 1 or index.numel() == 0 or not src.is_cuda:
         return False
+    if not torch.jit.is_scripting():
+        if torch.compiler.is_compiling():   # whether the index is sorted is a property of the data: not traceable
+            return False
     if not (src.dtype == torch.float32 or src.dtype == torch.float16 or src.dtype == torch.bfloat16):
         return False
     return torch.ops.torch_scatter.index_is_sorted(index)

@@ -131,7 +131,10 @@ template <typename T, int VEC> __device__ __forceinline__ void st_stream(T *p, c
 template <typename T, int VEC> __device__ __forceinline__ void async_copy_pack(Pack<T, VEC> *smem_dst, const T *gsrc) {
   constexpr int bytes = sizeof(T) * VEC;
   const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
-  if constexpr (bytes == 16) {
+  if constexpr (bytes == 32) {  // a double pack: two 16-byte copies
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gsrc) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16), "l"(reinterpret_cast<const char *>(gsrc) + 16) : "memory");
+  } else if constexpr (bytes == 16) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gsrc) : "memory");
   } else if constexpr (bytes == 8) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(gsrc) : "memory");
@@ -164,6 +167,7 @@ inline int ilog2_ceil(int64_t v) {
   return l;
 }
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool aligned32(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? TSB_OK : TSB_ERR_LAUNCH; }
 

@@ -3,6 +3,7 @@
 // layer only moves torch tensors' device pointers, sizes and the current CUDA stream across it.
 #pragma once
 
+#include <ATen/core/dispatch/Dispatcher.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/script.h>
@@ -87,12 +88,22 @@ inline BatchedRows batched_rows(const torch::Tensor &t) {
   return r;
 }
 
+// Every routine that touches tensor DATA is an operator of its own (torch_scatter::_*, CUDA kernels registered in the
+// registry files, shape-only "fake" kernels registered from Python in pytorch_scatter_b200/_meta.py).  The drivers
+// below look their operator up once and call it through the dispatcher, so the public operators - argument handling
+// and autograd written against these drivers - run unchanged on real tensors, and on fake tensors when a tracing
+// compiler propagates shapes through them (upstream registers no fake kernels: its operators break the graph).
+template <typename Signature> inline c10::TypedOperatorHandle<Signature> internal_op(const char *name) {
+  return c10::Dispatcher::singleton().findSchemaOrThrow(name, "").typed<Signature>();
+}
+inline torch::Tensor no_tensor(const torch::Tensor &like) { return torch::empty({0}, like.options()); }
+
 // ---- forward/backward drivers shared by the registry files ------------------------------------
 std::tuple<torch::Tensor, std::optional<torch::Tensor>>
 segment_csr_fw(torch::Tensor src, torch::Tensor indptr, std::optional<torch::Tensor> optional_out,
                const std::string &reduce);
 torch::Tensor gather_csr_fw(torch::Tensor src, torch::Tensor indptr, std::optional<torch::Tensor> optional_out,
-                            bool divide_by_count);
+                            bool divide_by_count, std::optional<int64_t> length);
 
 std::tuple<torch::Tensor, std::optional<torch::Tensor>>
 segment_coo_fw(torch::Tensor src, torch::Tensor index, std::optional<torch::Tensor> optional_out,

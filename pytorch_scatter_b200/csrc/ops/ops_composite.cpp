@@ -31,7 +31,7 @@ Flat flat_dims(const torch::Tensor &x, int64_t dim) {
 }
 
 // fp32 table [.., N, ..] of log-sum-exp per group along dim (-inf for groups nobody names)
-torch::Tensor segment_lse(const torch::Tensor &src_, const torch::Tensor &index, int64_t dim, int64_t N) {
+torch::Tensor segment_lse_impl(torch::Tensor src_, torch::Tensor index, int64_t dim, int64_t N) {
   c10::cuda::CUDAGuard guard(src_.device());
   auto src = src_.contiguous();
   auto sizes = src.sizes().vec();
@@ -51,8 +51,8 @@ torch::Tensor segment_lse(const torch::Tensor &src_, const torch::Tensor &index,
 
 // out = op(x, table[.., index, ..]) [* scale[.., index, ..]] along dim, tables fp32;
 // op 1: exp(x - row), 2: x - row, 3: (x - row)^2
-torch::Tensor gather_apply(const torch::Tensor &x_, const torch::Tensor &table_, const torch::Tensor &index, int64_t dim,
-                           int op, const std::optional<torch::Tensor> &scale_ = std::nullopt) {
+torch::Tensor gather_apply_impl(torch::Tensor x_, torch::Tensor table_, torch::Tensor index, int64_t dim, int64_t op,
+                                std::optional<torch::Tensor> scale_) {
   c10::cuda::CUDAGuard guard(x_.device());
   auto x = x_.contiguous();
   auto table = table_.contiguous();
@@ -64,9 +64,21 @@ torch::Tensor gather_apply(const torch::Tensor &x_, const torch::Tensor &table_,
   auto idx = index.contiguous();
   check_status(tsb_gather_coo_apply2(x.data_ptr(), table.data_ptr<float>(), scale.defined() ? scale.data_ptr<float>() : nullptr,
                                      idx.data_ptr<int64_t>(), out.data_ptr(), f.B, f.E, f.K, table.size(dim), 0,
-                                     dtype_enum(x), op, current_stream()),
+                                     dtype_enum(x), (int)op, current_stream()),
                "tsb_gather_coo_apply2");
   return out;
+}
+
+// the two data-touching routines above as operators (see ops_common.h)
+torch::Tensor segment_lse(const torch::Tensor &src, const torch::Tensor &index, int64_t dim, int64_t N) {
+  static auto op = internal_op<torch::Tensor(torch::Tensor, torch::Tensor, int64_t, int64_t)>("torch_scatter::_segment_lse");
+  return op.call(src, index, dim, N);
+}
+torch::Tensor gather_apply(const torch::Tensor &x, const torch::Tensor &table, const torch::Tensor &index, int64_t dim,
+                           int64_t op_code, const std::optional<torch::Tensor> &scale = std::nullopt) {
+  static auto op = internal_op<torch::Tensor(torch::Tensor, torch::Tensor, torch::Tensor, int64_t, int64_t,
+                                             std::optional<torch::Tensor>)>("torch_scatter::_gather_apply");
+  return op.call(x, table, index, dim, op_code, scale);
 }
 
 bool index_is_sorted(torch::Tensor index) {
@@ -206,8 +218,16 @@ torch::Tensor logsumexp_sorted(torch::Tensor src, torch::Tensor index, int64_t d
 }  // namespace tsb_ops
 
 TORCH_LIBRARY_FRAGMENT(torch_scatter, m) {
-  m.def("index_is_sorted", &tsb_ops::index_is_sorted);
+  m.def("index_is_sorted(Tensor index) -> bool");   // reads the data: a CUDA kernel of its own, with a fake twin
   m.def("softmax_sorted", &tsb_ops::softmax_sorted);
   m.def("logsumexp_sorted", &tsb_ops::logsumexp_sorted);
   m.def("std_sorted", &tsb_ops::std_sorted);
+  m.def("_segment_lse(Tensor src, Tensor index, int dim, int groups) -> Tensor");
+  m.def("_gather_apply(Tensor x, Tensor table, Tensor index, int dim, int op, Tensor? scale) -> Tensor");
+}
+
+TORCH_LIBRARY_IMPL(torch_scatter, CUDA, m) {
+  m.impl("index_is_sorted", &tsb_ops::index_is_sorted);
+  m.impl("_segment_lse", &tsb_ops::segment_lse_impl);
+  m.impl("_gather_apply", &tsb_ops::gather_apply_impl);
 }

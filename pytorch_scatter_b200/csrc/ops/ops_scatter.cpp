@@ -65,9 +65,9 @@ struct ScatterResult {
 };
 
 // index must already be broadcast to src's shape.
-ScatterResult scatter_fw(torch::Tensor src, torch::Tensor index, int64_t dim,
-                         std::optional<torch::Tensor> optional_out, std::optional<int64_t> dim_size,
-                         const std::string &reduce) {
+ScatterResult scatter_impl(torch::Tensor src, torch::Tensor index, int64_t dim,
+                           std::optional<torch::Tensor> optional_out, std::optional<int64_t> dim_size,
+                           const std::string &reduce) {
   TSB_CHECK_CUDA(src);
   TSB_CHECK_CUDA(index);
   if (optional_out.has_value()) TSB_CHECK_CUDA(optional_out.value());
@@ -139,9 +139,33 @@ ScatterResult scatter_fw(torch::Tensor src, torch::Tensor index, int64_t dim,
   return r;
 }
 
+// dispatcher form of the forward: (out, arg_out for MIN/MAX, int32 count for MEAN; placeholders otherwise)
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> scatter_op(torch::Tensor src, torch::Tensor index, int64_t dim,
+                                                                   std::optional<torch::Tensor> optional_out,
+                                                                   std::optional<int64_t> dim_size, std::string reduce) {
+  auto r = scatter_impl(src, index, dim, optional_out, dim_size, reduce);
+  return std::make_tuple(r.out, r.arg_out.has_value() ? r.arg_out.value() : no_tensor(index),
+                         r.count.has_value() ? r.count.value() : no_tensor(index));
+}
+
+ScatterResult scatter_fw(torch::Tensor src, torch::Tensor index, int64_t dim, std::optional<torch::Tensor> optional_out,
+                         std::optional<int64_t> dim_size, const std::string &reduce) {
+  TSB_CHECK_CUDA(src);
+  TSB_CHECK_CUDA(index);
+  static auto op = internal_op<std::tuple<torch::Tensor, torch::Tensor, torch::Tensor>(
+      torch::Tensor, torch::Tensor, int64_t, std::optional<torch::Tensor>, std::optional<int64_t>, std::string)>(
+      "torch_scatter::_scatter_fw");
+  auto t = op.call(src, index, dim, optional_out, dim_size, reduce);
+  ScatterResult r;
+  r.out = std::get<0>(t);
+  if (reduce == "min" || reduce == "max") r.arg_out = std::get<1>(t);
+  if (reduce == "mean") r.count = std::get<2>(t);
+  return r;
+}
+
 // grad_in[b,e,k] = grad_out[b, index(b,e,k), k] (/ count): the gather behind SUM / MEAN / MUL backward.
-torch::Tensor scatter_bw(const torch::Tensor &grad_out_, const torch::Tensor &index, int64_t dim,
-                         const std::vector<int64_t> &src_shape, std::optional<torch::Tensor> count) {
+torch::Tensor scatter_bw_impl(torch::Tensor grad_out_, torch::Tensor index, int64_t dim, std::vector<int64_t> src_shape,
+                              std::optional<torch::Tensor> count) {
   c10::cuda::CUDAGuard guard(grad_out_.device());
   auto grad_out = grad_out_.contiguous();
   auto grad_in = torch::empty(src_shape, grad_out.options());
@@ -157,6 +181,13 @@ torch::Tensor scatter_bw(const torch::Tensor &grad_out_, const torch::Tensor &in
                                     fi.sb, fi.se, fi.sk, dtype_enum(grad_out), current_stream()),
                "tsb_scatter_backward");
   return grad_in;
+}
+
+torch::Tensor scatter_bw(const torch::Tensor &grad_out, const torch::Tensor &index, int64_t dim,
+                         const std::vector<int64_t> &src_shape, std::optional<torch::Tensor> count) {
+  static auto op = internal_op<torch::Tensor(torch::Tensor, torch::Tensor, int64_t, std::vector<int64_t>,
+                                             std::optional<torch::Tensor>)>("torch_scatter::_scatter_bw");
+  return op.call(grad_out, index, dim, src_shape, count);
 }
 
 using torch::autograd::AutogradContext;
@@ -427,9 +458,17 @@ TORCH_LIBRARY_FRAGMENT(torch_scatter, m) {
   m.def("scatter_max", &tsb_ops::scatter_max);
   // not part of upstream's operator set: the index read-back its composites do with Tensor.gather
   m.def("gather_rows", &tsb_ops::gather_rows);
+  // the data-touching halves (see ops_common.h)
+  m.def("_scatter_fw(Tensor src, Tensor index, int dim, Tensor? out, int? dim_size, str reduce) -> (Tensor, Tensor, Tensor)");
+  m.def("_scatter_bw(Tensor grad_out, Tensor index, int dim, int[] src_shape, Tensor? count) -> Tensor");
   m.def("scatter_sum_slice", &tsb_ops::scatter_sum_slice);
   m.def("scatter_group", &tsb_ops::scatter_group);
   m.def("segment_sum_perm", &tsb_ops::segment_sum_perm);
   m.def("segment_sum_perm_routed", &tsb_ops::segment_sum_perm_routed);
   m.def("sum_slabs", &tsb_ops::sum_slabs);
+}
+
+TORCH_LIBRARY_IMPL(torch_scatter, CUDA, m) {
+  m.impl("_scatter_fw", &tsb_ops::scatter_op);
+  m.impl("_scatter_bw", &tsb_ops::scatter_bw_impl);
 }

@@ -4,9 +4,10 @@
 
 namespace tsb_ops {
 
+namespace {
 std::tuple<torch::Tensor, std::optional<torch::Tensor>>
-segment_coo_fw(torch::Tensor src, torch::Tensor index, std::optional<torch::Tensor> optional_out,
-               std::optional<int64_t> dim_size, const std::string &reduce) {
+segment_coo_impl(torch::Tensor src, torch::Tensor index, std::optional<torch::Tensor> optional_out,
+                 std::optional<int64_t> dim_size, const std::string &reduce) {
   TSB_CHECK_CUDA(src);
   TSB_CHECK_CUDA(index);
   if (optional_out.has_value()) TSB_CHECK_CUDA(optional_out.value());
@@ -85,8 +86,8 @@ segment_coo_fw(torch::Tensor src, torch::Tensor index, std::optional<torch::Tens
   return std::make_tuple(out, arg_out);
 }
 
-torch::Tensor gather_coo_fw(torch::Tensor src, torch::Tensor index, std::optional<torch::Tensor> optional_out,
-                            std::optional<torch::Tensor> count) {
+torch::Tensor gather_coo_impl(torch::Tensor src, torch::Tensor index, std::optional<torch::Tensor> optional_out,
+                              std::optional<torch::Tensor> count) {
   TSB_CHECK_CUDA(src);
   TSB_CHECK_CUDA(index);
   if (optional_out.has_value()) TSB_CHECK_CUDA(optional_out.value());
@@ -149,6 +150,37 @@ torch::Tensor gather_coo_fw(torch::Tensor src, torch::Tensor index, std::optiona
   return out;
 }
 
+// dispatcher form: (out, arg_out for MIN/MAX, count for MEAN, else a placeholder)
+std::tuple<torch::Tensor, torch::Tensor> segment_coo_op(torch::Tensor src, torch::Tensor index,
+                                                        std::optional<torch::Tensor> optional_out,
+                                                        std::optional<int64_t> dim_size, std::string reduce) {
+  auto r = segment_coo_impl(src, index, optional_out, dim_size, reduce);
+  return std::make_tuple(std::get<0>(r), std::get<1>(r).has_value() ? std::get<1>(r).value() : no_tensor(index));
+}
+}  // namespace
+
+std::tuple<torch::Tensor, std::optional<torch::Tensor>>
+segment_coo_fw(torch::Tensor src, torch::Tensor index, std::optional<torch::Tensor> optional_out,
+               std::optional<int64_t> dim_size, const std::string &reduce) {
+  TSB_CHECK_CUDA(src);
+  TSB_CHECK_CUDA(index);
+  static auto op = internal_op<std::tuple<torch::Tensor, torch::Tensor>(torch::Tensor, torch::Tensor, std::optional<torch::Tensor>,
+                                                                        std::optional<int64_t>, std::string)>(
+      "torch_scatter::_segment_coo_fw");
+  auto r = op.call(src, index, optional_out, dim_size, reduce);
+  const bool extra = reduce == "min" || reduce == "max" || reduce == "mean";
+  return std::make_tuple(std::get<0>(r), extra ? std::optional<torch::Tensor>(std::get<1>(r)) : std::nullopt);
+}
+
+torch::Tensor gather_coo_fw(torch::Tensor src, torch::Tensor index, std::optional<torch::Tensor> optional_out,
+                            std::optional<torch::Tensor> count) {
+  TSB_CHECK_CUDA(src);
+  TSB_CHECK_CUDA(index);
+  static auto op = internal_op<torch::Tensor(torch::Tensor, torch::Tensor, std::optional<torch::Tensor>,
+                                             std::optional<torch::Tensor>)>("torch_scatter::_gather_coo_fw");
+  return op.call(src, index, optional_out, count);
+}
+
 namespace {
 
 using torch::autograd::AutogradContext;
@@ -170,8 +202,8 @@ public:
     auto grad_out = grad_outs[0];
     auto index = ctx->get_saved_variables()[0];
     auto src_shape = list2vec(ctx->saved_data["src_shape"].toIntList());
-    auto grad_in = torch::empty(src_shape, grad_out.options());
-    gather_coo_fw(grad_out, index, grad_in, std::nullopt);
+    // no `out`: an operator that writes into an argument is invisible to a tracing compiler
+    auto grad_in = gather_coo_fw(grad_out, index, std::nullopt, std::nullopt);
     return {grad_in, Variable(), Variable(), Variable()};
   }
 };
@@ -193,8 +225,7 @@ public:
     auto grad_out = grad_outs[0];
     auto saved = ctx->get_saved_variables();
     auto src_shape = list2vec(ctx->saved_data["src_shape"].toIntList());
-    auto grad_in = torch::empty(src_shape, grad_out.options());
-    if (grad_in.numel() > 0) gather_coo_fw(grad_out, saved[0], grad_in, saved[1].to(grad_out.scalar_type()));
+    auto grad_in = gather_coo_fw(grad_out, saved[0], std::nullopt, saved[1].to(grad_out.scalar_type()));
     return {grad_in, Variable(), Variable(), Variable()};
   }
 };
@@ -236,8 +267,7 @@ public:
     auto grad_out = grad_outs[0];
     auto index = ctx->get_saved_variables()[0];
     auto src_shape = list2vec(ctx->saved_data["src_shape"].toIntList());
-    auto grad_in = torch::zeros(src_shape, grad_out.options());
-    segment_coo_fw(grad_out, index, grad_in, std::nullopt, "sum");
+    auto grad_in = std::get<0>(segment_coo_fw(grad_out, index, std::nullopt, src_shape[index.dim() - 1], "sum"));
     return {grad_in, Variable(), Variable()};
   }
 };
@@ -275,4 +305,12 @@ TORCH_LIBRARY_FRAGMENT(torch_scatter, m) {
   m.def("segment_min_coo", &tsb_ops::segment_min_coo);
   m.def("segment_max_coo", &tsb_ops::segment_max_coo);
   m.def("gather_coo", &tsb_ops::gather_coo);
+  // the data-touching halves (see ops_common.h)
+  m.def("_segment_coo_fw(Tensor src, Tensor index, Tensor? out, int? dim_size, str reduce) -> (Tensor, Tensor)");
+  m.def("_gather_coo_fw(Tensor src, Tensor index, Tensor? out, Tensor? count) -> Tensor");
+}
+
+TORCH_LIBRARY_IMPL(torch_scatter, CUDA, m) {
+  m.impl("_segment_coo_fw", &tsb_ops::segment_coo_op);
+  m.impl("_gather_coo_fw", &tsb_ops::gather_coo_impl);
 }

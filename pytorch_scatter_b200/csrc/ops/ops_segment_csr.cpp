@@ -5,9 +5,10 @@
 
 namespace tsb_ops {
 
+namespace {
 std::tuple<torch::Tensor, std::optional<torch::Tensor>>
-segment_csr_fw(torch::Tensor src, torch::Tensor indptr, std::optional<torch::Tensor> optional_out,
-               const std::string &reduce) {
+segment_csr_impl(torch::Tensor src, torch::Tensor indptr, std::optional<torch::Tensor> optional_out,
+                 const std::string &reduce) {
   TSB_CHECK_CUDA(src);
   TSB_CHECK_CUDA(indptr);
   if (optional_out.has_value()) TSB_CHECK_CUDA(optional_out.value());
@@ -69,8 +70,9 @@ segment_csr_fw(torch::Tensor src, torch::Tensor indptr, std::optional<torch::Ten
   return std::make_tuple(out, arg_out);
 }
 
-torch::Tensor gather_csr_fw(torch::Tensor src, torch::Tensor indptr, std::optional<torch::Tensor> optional_out,
-                            bool divide_by_count) {
+// `length`: the output's size along the gathered dimension when the caller knows it (no `out`, no host sync)
+torch::Tensor gather_csr_impl(torch::Tensor src, torch::Tensor indptr, std::optional<torch::Tensor> optional_out,
+                              std::optional<int64_t> length, bool divide_by_count) {
   TSB_CHECK_CUDA(src);
   TSB_CHECK_CUDA(indptr);
   if (optional_out.has_value()) TSB_CHECK_CUDA(optional_out.value());
@@ -98,7 +100,9 @@ torch::Tensor gather_csr_fw(torch::Tensor src, torch::Tensor indptr, std::option
       if (i != dim) TSB_CHECK_INPUT(src.size(i) == out.size(i));
   } else {
     auto out_sizes = src.sizes().vec();
-    if (src.numel() > 0)
+    if (length.has_value())
+      out_sizes[dim] = length.value();
+    else if (src.numel() > 0)
       out_sizes[dim] = indptr.flatten()[-1].item<int64_t>();  // host sync, as upstream (segment_csr_cuda.cu:248)
     else
       out_sizes[dim] = 0;
@@ -109,6 +113,7 @@ torch::Tensor gather_csr_fw(torch::Tensor src, torch::Tensor indptr, std::option
     if (!optional_out.has_value()) out.fill_(0);
     return out;
   }
+  if (length.has_value() && !optional_out.has_value()) out.zero_();  // positions no row covers (a backward pass: no gradient)
 
   const int64_t B = indptr.numel() / indptr.size(-1);
   const int64_t N = src.size(dim);
@@ -125,8 +130,7 @@ torch::Tensor gather_csr_fw(torch::Tensor src, torch::Tensor indptr, std::option
   return out;
 }
 
-torch::Tensor arg_backward(const torch::Tensor &grad_out_, const torch::Tensor &arg_out,
-                           std::vector<int64_t> src_shape, int64_t dim) {
+torch::Tensor arg_backward_impl(torch::Tensor grad_out_, torch::Tensor arg_out, std::vector<int64_t> src_shape, int64_t dim) {
   c10::cuda::CUDAGuard guard(grad_out_.device());
   auto grad_out = grad_out_.contiguous();
   auto arg = arg_out.contiguous();
@@ -140,6 +144,42 @@ torch::Tensor arg_backward(const torch::Tensor &grad_out_, const torch::Tensor &
                                 dtype_enum(grad_out), current_stream()),
                "tsb_arg_backward");
   return grad_in;
+}
+
+// dispatcher form: (out, arg_out or a placeholder)
+std::tuple<torch::Tensor, torch::Tensor> segment_csr_op(torch::Tensor src, torch::Tensor indptr,
+                                                        std::optional<torch::Tensor> optional_out, std::string reduce) {
+  auto r = segment_csr_impl(src, indptr, optional_out, reduce);
+  return std::make_tuple(std::get<0>(r), std::get<1>(r).has_value() ? std::get<1>(r).value() : no_tensor(indptr));
+}
+}  // namespace
+
+std::tuple<torch::Tensor, std::optional<torch::Tensor>>
+segment_csr_fw(torch::Tensor src, torch::Tensor indptr, std::optional<torch::Tensor> optional_out,
+               const std::string &reduce) {
+  TSB_CHECK_CUDA(src);
+  TSB_CHECK_CUDA(indptr);
+  static auto op = internal_op<std::tuple<torch::Tensor, torch::Tensor>(torch::Tensor, torch::Tensor, std::optional<torch::Tensor>,
+                                                                        std::string)>("torch_scatter::_segment_csr_fw");
+  auto r = op.call(src, indptr, optional_out, reduce);
+  const bool minmax = reduce == "min" || reduce == "max";
+  return std::make_tuple(std::get<0>(r), minmax ? std::optional<torch::Tensor>(std::get<1>(r)) : std::nullopt);
+}
+
+torch::Tensor gather_csr_fw(torch::Tensor src, torch::Tensor indptr, std::optional<torch::Tensor> optional_out,
+                            bool divide_by_count, std::optional<int64_t> length) {
+  TSB_CHECK_CUDA(src);
+  TSB_CHECK_CUDA(indptr);
+  static auto op = internal_op<torch::Tensor(torch::Tensor, torch::Tensor, std::optional<torch::Tensor>, std::optional<int64_t>,
+                                             bool)>("torch_scatter::_gather_csr_fw");
+  return op.call(src, indptr, optional_out, length, divide_by_count);
+}
+
+torch::Tensor arg_backward(const torch::Tensor &grad_out, const torch::Tensor &arg_out, std::vector<int64_t> src_shape,
+                           int64_t dim) {
+  static auto op = internal_op<torch::Tensor(torch::Tensor, torch::Tensor, std::vector<int64_t>, int64_t)>(
+      "torch_scatter::_arg_backward");
+  return op.call(grad_out, arg_out, src_shape, dim);
 }
 
 namespace {
@@ -164,8 +204,8 @@ public:
     auto grad_out = grad_outs[0];
     auto indptr = ctx->get_saved_variables()[0];
     auto src_shape = list2vec(ctx->saved_data["src_shape"].toIntList());
-    auto grad_in = torch::empty(src_shape, grad_out.options());
-    if (grad_in.numel() > 0) gather_csr_fw(grad_out, indptr, grad_in, MEAN);
+    // no `out`: an operator that writes into an argument is invisible to a tracing compiler
+    auto grad_in = gather_csr_fw(grad_out, indptr, std::nullopt, MEAN, src_shape[indptr.dim() - 1]);
     return {grad_in, Variable(), Variable()};
   }
 };
@@ -199,7 +239,7 @@ public:
   static variable_list forward(AutogradContext *ctx, Variable src, Variable indptr,
                                std::optional<Variable> optional_out) {
     ctx->saved_data["src_shape"] = src.sizes();
-    auto out = gather_csr_fw(src, indptr, optional_out, false);
+    auto out = gather_csr_fw(src, indptr, optional_out, false, std::nullopt);
     ctx->save_for_backward({indptr});
     if (optional_out.has_value()) ctx->mark_dirty({optional_out.value()});
     return {out};
@@ -208,6 +248,9 @@ public:
     auto grad_out = grad_outs[0];
     auto indptr = ctx->get_saved_variables()[0];
     auto src_shape = list2vec(ctx->saved_data["src_shape"].toIntList());
+    const int64_t dim = indptr.dim() - 1;
+    if (indptr.size(dim) - 1 == src_shape[dim])   // the usual case: no `out`, visible to a tracing compiler
+      return {std::get<0>(segment_csr_fw(grad_out, indptr, std::nullopt, "sum")), Variable(), Variable()};
     auto grad_in = torch::empty(src_shape, grad_out.options());
     segment_csr_fw(grad_out, indptr, grad_in, "sum");
     return {grad_in, Variable(), Variable()};
@@ -245,4 +288,14 @@ TORCH_LIBRARY_FRAGMENT(torch_scatter, m) {
   m.def("segment_max_csr", &tsb_ops::segment_max_csr);
   m.def("gather_csr", &tsb_ops::gather_csr);
   m.def("cuda_version", &tsb_ops::cuda_version);
+  // the data-touching halves (see ops_common.h)
+  m.def("_segment_csr_fw(Tensor src, Tensor indptr, Tensor? out, str reduce) -> (Tensor, Tensor)");
+  m.def("_gather_csr_fw(Tensor src, Tensor indptr, Tensor? out, int? length, bool divide_by_count) -> Tensor");
+  m.def("_arg_backward(Tensor grad_out, Tensor arg_out, int[] src_shape, int dim) -> Tensor");
+}
+
+TORCH_LIBRARY_IMPL(torch_scatter, CUDA, m) {
+  m.impl("_segment_csr_fw", &tsb_ops::segment_csr_op);
+  m.impl("_gather_csr_fw", &tsb_ops::gather_csr_impl);
+  m.impl("_arg_backward", &tsb_ops::arg_backward_impl);
 }

@@ -33,7 +33,7 @@ pytestmark = pytest.mark.gpu
 
 DEV = 'cuda'
 HOOKS = ('TSB_CSR_CHUNK_ENTRIES', 'TSB_CSR_FORCE_FLAT', 'TSB_SCATTER_SLICE_BYTES', 'TSB_SCATTER_REPLICAS',
-         'TSB_SCATTER_CLUSTERED', 'TSB_SCATTER_GROUPED', 'TSB_SCATTER_GROUPED_SORT', 'TSB_SCATTER_CACHED')
+         'TSB_SCATTER_CLUSTERED', 'TSB_SCATTER_GROUPED', 'TSB_SCATTER_GROUPED_SORT', 'TSB_SCATTER_CACHED', 'TSB_CSR_KERNEL')
 
 
 @pytest.fixture(scope='module')

@@ -42,17 +42,25 @@ def row_lengths(gen, rows, kind):
     return lens
 
 
-@pytest.fixture(params=[None, 32, 64, 'staged'], ids=['chunk-default', 'chunk-32', 'chunk-64', 'staged-rows'])
+@pytest.fixture(params=[None, 32, 64, 'staged', 'walk', 'walk-32', 'stream', 'stream-32'],
+                ids=['chunk-default', 'chunk-32', 'chunk-64', 'staged-rows', 'walk', 'walk-chunk-32', 'stream', 'stream-chunk-32'])
 def chunk(request):
-    """Chunk lengths of the row-pointer reduction (short chunks make rows straddle many chunk borders), and the kernel
-    that stages chunks in shared memory (the default for K == 1 only) forced for every entry of up to 64 bytes."""
-    names = ('TSB_CSR_CHUNK_ENTRIES', 'TSB_CSR_FORCE_FLAT')
+    """Chunk lengths of the row-pointer reduction (short chunks make rows straddle many chunk borders), the kernel
+    that stages chunks in shared memory (the default for K == 1 only) forced for every entry of up to 64 bytes, and
+    each of the two chunk kernels (lane groups walking pieces / the warp streaming steps) dictated where the library
+    would pick by shape."""
+    names = ('TSB_CSR_CHUNK_ENTRIES', 'TSB_CSR_FORCE_FLAT', 'TSB_CSR_KERNEL')
     old = {k: os.environ.get(k) for k in names}
     for k in names:
         os.environ.pop(k, None)
     if request.param == 'staged':
         os.environ['TSB_CSR_FORCE_FLAT'] = '1'
         os.environ['TSB_CSR_CHUNK_ENTRIES'] = '64'
+    elif isinstance(request.param, str):
+        kernel, _, entries = request.param.partition('-')
+        os.environ['TSB_CSR_KERNEL'] = kernel
+        if entries:
+            os.environ['TSB_CSR_CHUNK_ENTRIES'] = entries
     elif request.param is not None:
         os.environ['TSB_CSR_CHUNK_ENTRIES'] = str(request.param)
     yield request.param
@@ -215,7 +223,7 @@ def test_gathers(K):
 
 
 @pytest.fixture(params=['one-pass', 'sliced', 'replicated', 'runs', 'runs-sliced', 'direct', 'grouped', 'grouped-chunk32',
-                        'grouped-atomic', 'cached', 'cached-replicated'])
+                        'grouped-atomic', 'grouped-walk', 'grouped-walk-chunk32', 'grouped-stream', 'cached', 'cached-replicated'])
 def scatter_slices(request):
     """Forces the variants the launcher normally picks by size or by probing the index: sliced multi-pass
     accumulation (outputs larger than L2), accumulation into several copies of the output (small,
@@ -223,7 +231,7 @@ def scatter_slices(request):
     entries by target row and reduces rows through the permutation (also with 32-entry chunks, so that rows
     straddle many chunk borders)."""
     names = ('TSB_SCATTER_SLICE_BYTES', 'TSB_SCATTER_REPLICAS', 'TSB_SCATTER_CLUSTERED', 'TSB_SCATTER_GROUPED',
-             'TSB_CSR_CHUNK_ENTRIES', 'TSB_SCATTER_GROUPED_SORT', 'TSB_SCATTER_CACHED')
+             'TSB_CSR_CHUNK_ENTRIES', 'TSB_SCATTER_GROUPED_SORT', 'TSB_SCATTER_CACHED', 'TSB_CSR_KERNEL')
     old = {k: os.environ.get(k) for k in names}
     for k in names:
         os.environ.pop(k, None)
@@ -236,8 +244,10 @@ def scatter_slices(request):
     if request.param == 'direct':          # the one-update-per-entry kernels, even on a sorted index
         os.environ['TSB_SCATTER_CLUSTERED'] = '0'
     os.environ['TSB_SCATTER_GROUPED'] = '1' if request.param.startswith('grouped') else '0'
-    if request.param == 'grouped-chunk32':
+    if request.param.endswith('chunk32'):
         os.environ['TSB_CSR_CHUNK_ENTRIES'] = '32'
+    if 'walk' in request.param or 'stream' in request.param:   # which chunk kernel reduces the grouped rows
+        os.environ['TSB_CSR_KERNEL'] = 'walk' if 'walk' in request.param else 'stream'
     if request.param.startswith('cached'):  # fp32 sums through the shared-memory row cache (skewed indices)
         os.environ['TSB_SCATTER_CACHED'] = '1'
         os.environ['TSB_SCATTER_CLUSTERED'] = '0'
