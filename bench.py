@@ -241,10 +241,25 @@ def check_results(ts, w, world, rank, dev, scatter_step):
         dist.reduce_scatter_tensor(mass_b, mass)
         want, mass = want_b, mass_b
     got = scatter_step(src, w['shuffled'])
-    valid = min(max(ROWS - rank * per, 0), per)
-    sc_ratio = float(((got[:valid].double() - want[:valid]).abs() / (1e-5 * mass[:valid] + 1e-30)).max())
-    if got.size(0) > valid:   # padding rows of the last block stay zero
-        sc_ratio = max(sc_ratio, float('inf') if bool((got[valid:] != 0).any()) else 0.0)
+    if world > 1 and got.size(0) != per:
+        # the NCCL per-slice variant interleaves ownership: compare the rows this rank really holds
+        from pytorch_scatter_b200.dist import overlapped_layout, owned_rows
+        passes, sub = overlapped_layout(ROWS, world, FEAT * 4)
+        mine = owned_rows(ROWS, world, rank, passes, sub, dev)
+        ok_rows = mine < ROWS
+        full_want = torch.zeros(per * world, FEAT, dtype=torch.float64, device=dev)
+        full_mass = torch.zeros(per * world, FEAT, dtype=torch.float64, device=dev)
+        gathered_w = [torch.empty_like(want) for _ in range(world)]
+        gathered_m = [torch.empty_like(mass) for _ in range(world)]
+        dist.all_gather(gathered_w, want)
+        dist.all_gather(gathered_m, mass)
+        full_want, full_mass = torch.cat(gathered_w), torch.cat(gathered_m)
+        sc_ratio = float(((got[ok_rows].double() - full_want[mine[ok_rows]]).abs() / (1e-5 * full_mass[mine[ok_rows]] + 1e-30)).max())
+    else:
+        valid = min(max(ROWS - rank * per, 0), per)
+        sc_ratio = float(((got[:valid].double() - want[:valid]).abs() / (1e-5 * mass[:valid] + 1e-30)).max())
+        if got.size(0) > valid:   # padding rows of the last block stay zero
+            sc_ratio = max(sc_ratio, float('inf') if bool((got[valid:] != 0).any()) else 0.0)
     worst = torch.tensor([csr_ratio, sc_ratio], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(worst, op=dist.ReduceOp.MAX)
@@ -416,7 +431,7 @@ def run_ours(args):
         if world == 1:
             return ts.scatter(s, ix, dim=0, dim_size=ROWS, reduce='sum')
         if exchange['kind'] is None:   # decided once, by all ranks together
-            if routed_exchange_available(s, ROWS):
+            if args.exchange != 'nccl' and routed_exchange_available(s, ROWS):
                 exchange['kind'] = 'peer stores from the reduction kernel (symmetric memory), owners add the slabs'
             else:
                 exchange['kind'] = 'NCCL reduce-scatter per output slice, overlapped with the next slice'
@@ -607,8 +622,11 @@ def run_ours(args):
         }
         if routed:
             line['ops']['scatter_phases_ms'] = {
-                name: {'max': float(allt[:, 4 + k].max()), 'mean': float(allt[:, 4 + k].mean())}
+                name: {'max': float(allt[:, 4 + k].max()), 'mean': float(allt[:, 4 + k].mean()),
+                       'per_rank': [round(float(x), 4) for x in allt[:, 4 + k].tolist()]}
                 for k, name in enumerate(ROUTED_PHASES)}
+            line['ops']['per_rank_ms'] = {'segment_csr_sum': [round(float(x), 4) for x in allt[:, 1].tolist()],
+                                          'scatter_sum': [round(float(x), 4) for x in allt[:, 2].tolist()]}
         if c5 is not None:
             line['c5'] = c5
         if world == 1 and not args.no_cpu_baseline:
@@ -644,7 +662,8 @@ def zipf_index(E, N, dev, g):
 
 def run_profile_op(args):
     """Profiling helper, meant to be wrapped in ncu on a small case: runs warmup+steps calls of ONE operator and exits.
-    `csr` / `scatter`: the benchmark's operators on a `--rows`-sized copy of its workload.  `c4-sum` / `c4-max`:
+    `csr` / `scatter` / `gather-csr`: the benchmark's operators (and the backward of the first) on a `--rows`-sized copy of
+    its workload with `--feat` features in `--dtype`.  `c4-sum` / `c4-max`:
     scatter of fp32 [`--entries` x 16] under a Zipf(1.2) index over 100,000 targets.  `c3-*`: segment_coo / softmax on
     the sorted index of a `--rows`-sized workload in `--dtype`.  `c5-scatter`: bf16 F=128, `--entries` edges of a
     power-law graph into `--rows` target rows."""
@@ -653,12 +672,15 @@ def run_profile_op(args):
     g = torch.Generator(device=dev).manual_seed(SEED)
     op = args.profile_op
     dtype = {'fp32': torch.float32, 'bf16': torch.bfloat16, 'fp16': torch.float16}[args.dtype]
-    if op in ('csr', 'scatter'):
-        indptr, _, shuffled, src = make_workload(args.rows, SEED)
-        src, indptr, shuffled = src.cuda(), indptr.cuda(), shuffled.cuda()
-        out = torch.empty(args.rows, FEAT, device='cuda')
-        fn = (lambda: ts.segment_csr(src, indptr, out=out, reduce='sum')) if op == 'csr' else \
-            (lambda: ts.scatter(src, shuffled, dim=0, dim_size=args.rows, reduce='sum'))
+    if op in ('csr', 'scatter', 'gather-csr'):
+        indptr, _, shuffled, src = make_workload(args.rows, SEED, feat=args.feat)
+        src, indptr, shuffled = src.to(dtype).cuda(), indptr.cuda(), shuffled.cuda()
+        if args.feat == 1:
+            src = src.view(-1)   # a 1-D source: the K == 1 kernel
+        out = torch.empty((args.rows, args.feat) if args.feat > 1 else (args.rows,), device='cuda', dtype=dtype)
+        fn = {'csr': lambda: ts.segment_csr(src, indptr, out=out, reduce='sum'),
+              'scatter': lambda: ts.scatter(src, shuffled, dim=0, dim_size=args.rows, reduce='sum'),
+              'gather-csr': lambda: ts.gather_csr(out, indptr, src)}[op]
         entries = src.size(0)
     elif op in ('c4-sum', 'c4-max'):
         entries, N = args.entries, 100000
@@ -688,6 +710,71 @@ def run_profile_op(args):
         fn()
     torch.cuda.synchronize()
     print(json.dumps({'profile_op': op, 'rows': args.rows, 'entries': entries, 'calls': args.warmup + args.steps}))
+
+
+def run_comparator(args):
+    """`--comparator`: the upstream project's own CUDA kernels (compiled for sm_100 into oracle/_ref/ by
+    `make -C oracle refcuda`), timed on this GPU in THIS process, which must not import pytorch_scatter_b200 (both
+    register the torch_scatter::* operators).  One JSON line per operator; `python bench.py --suite` gives this
+    library's times for the same shapes.  A comparator, not an oracle: upstream's float order and arg ties on the GPU
+    are not deterministic."""
+    ref_dir = osp.join(ROOT, 'oracle', '_ref')
+    libs = sorted(f for f in os.listdir(ref_dir) if f.endswith('_cuda.so')) if osp.isdir(ref_dir) else []
+    if len(libs) < 3:
+        print(json.dumps({'comparator': 'unavailable', 'why': 'oracle/_ref/_*_cuda.so not built (make -C oracle refcuda REF=...)'}))
+        return
+    for f in libs:
+        torch.ops.load_library(osp.join(ref_dir, f))
+    ops = torch.ops.torch_scatter
+    dev = torch.device('cuda')
+    g = torch.Generator(device=dev).manual_seed(SEED)
+    peaks_path = osp.join(ROOT, 'MEASURED_PEAKS.json')
+    peak = float(json.load(open(peaks_path))['hbm_gbs']) if osp.exists(peaks_path) else 6650.0
+
+    def timeit(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        return statistics.median(times)
+
+    def emit(config, op, ms, nbytes):
+        gbs = nbytes / ms / 1e6
+        print(json.dumps({'comparator': 'upstream csrc/cuda for sm_100', 'suite': config, 'op': op, 'ms': round(ms, 4),
+                          'GB/s': round(gbs, 1), 'frac_of_measured_peak': round(gbs / peak, 3)}), flush=True)
+
+    # C2 / C3 at F=64 fp32: the benchmark's workload
+    lens = row_lengths(ROWS, SEED, force_long=8)
+    indptr = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)]).to(dev)
+    nnz = int(indptr[-1])
+    index = torch.repeat_interleave(torch.arange(ROWS, device=dev), lens.to(dev))
+    shuffled = index[torch.randperm(nnz, device=dev, generator=g)]
+    src = torch.randn(nnz, FEAT, device=dev, generator=g)
+    b_csr, b_sc = algorithmic_bytes(ROWS, nnz)
+    emit('C2', 'segment_csr sum fp32 F=64', timeit(lambda: ops.segment_sum_csr(src, indptr, None)), b_csr)
+    emit('C2', 'segment_csr max fp32 F=64', timeit(lambda: ops.segment_max_csr(src, indptr, None)), b_csr + ROWS * FEAT * 8)
+    emit('C3', 'segment_coo sum fp32 F=64', timeit(lambda: ops.segment_sum_coo(src, index, None, ROWS)), b_sc)
+    wide = shuffled.view(-1, 1).expand(-1, FEAT)
+    emit('bench', 'scatter sum fp32 F=64, shuffled index (upstream scatter_kernel)', timeit(lambda: ops.scatter_sum(src, wide, 0, None, ROWS)), b_sc)
+    emit('bench', 'scatter sum fp32 F=64, shuffled index (ATen scatter_add_, what upstream\'s Python scatter_sum calls)',
+         timeit(lambda: torch.zeros(ROWS, FEAT, device=dev).scatter_add_(0, wide, src)), b_sc)
+    del src, wide, index, shuffled
+    # C4: Zipf(1.2) index over 100,000 targets, fp32 [33.5 M x 16]
+    E, F, N = 1 << 25, 16, 100000
+    idx = zipf_index(E, N, dev, g).view(-1, 1).expand(-1, F)
+    src = torch.randn(E, F, device=dev, generator=g)
+    nb = E * F * 4 + E * 8 + N * F * 4
+    emit('C4', 'scatter sum fp32 [33554432x16] Zipf(1.2)->100000 (ATen scatter_add_)',
+         timeit(lambda: torch.zeros(N, F, device=dev).scatter_add_(0, idx, src)), nb)
+    emit('C4', 'scatter max fp32 [33554432x16] Zipf(1.2)->100000 (upstream scatter_kernel + arg kernel)',
+         timeit(lambda: ops.scatter_max(src, idx, 0, None, N)), nb + N * F * 8)
 
 
 def run_suite(args):
@@ -851,16 +938,23 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--ref-fraction', type=int, default=4, help='reference arm runs on 1/this of the rows')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--exchange', default='auto', choices=['auto', 'nccl'],
+                    help='N > 1: auto = peer stores from the reduction kernel when symmetric memory is available; nccl = '
+                         'the per-slice NCCL reduce-scatter variant')
     ap.add_argument('--no-c5', action='store_true', help='skip the GNN-scale block (bf16 F=128, 10 M nodes / 200 M edges)')
+    ap.add_argument('--comparator', action='store_true', help="upstream's own CUDA kernels (oracle/_ref/_*_cuda.so) on this GPU")
     ap.add_argument('--suite', action='store_true', help='per-operator table over the other configurations')
     ap.add_argument('--suite-only', default='', help='comma-separated configs to run, e.g. C3,C4')
     ap.add_argument('--profile-op', default=None,
-                    choices=['csr', 'scatter', 'c4-sum', 'c4-max', 'c3-sum', 'c3-max', 'c3-softmax', 'c5-scatter'])
+                    choices=['csr', 'scatter', 'gather-csr', 'c4-sum', 'c4-max', 'c3-sum', 'c3-max', 'c3-softmax', 'c5-scatter'])
     ap.add_argument('--rows', type=int, default=ROWS, help='rows of the workload for --profile-op')
     ap.add_argument('--entries', type=int, default=1 << 22, help='entries for --profile-op c4-* / c5-scatter')
-    ap.add_argument('--feat', type=int, default=64, help='features for --profile-op c3-*')
-    ap.add_argument('--dtype', default='fp32', choices=['fp32', 'bf16', 'fp16'], help='dtype for --profile-op c3-*')
+    ap.add_argument('--feat', type=int, default=64, help='features for --profile-op csr / scatter / gather-csr / c3-*')
+    ap.add_argument('--dtype', default='fp32', choices=['fp32', 'bf16', 'fp16'], help='dtype for --profile-op csr / scatter / gather-csr / c3-*')
     args = ap.parse_args()
+    if args.comparator:
+        run_comparator(args)
+        return
     if args.profile_op is not None:
         run_profile_op(args)
         return

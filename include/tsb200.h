@@ -6,7 +6,10 @@
  *   - returns 0 (TSB_OK) or a tsb_status error code, never throws,
  *   - launches on the stream it is given and returns without synchronising,
  *   - allocates no memory: scratch comes from the caller (query the *_workspace_bytes twin first),
- *   - is re-entrant; the only global state is read-only per-device attributes cached on first use.
+ *   - is re-entrant.  Global state: per-device attributes cached on first use (SM count, opt-in shared-memory sizes:
+ *     idempotent, written through atomics).  The one exception is tsb_segment_csr_noalloc, whose scratch is a single
+ *     array inside the library: calls that overlap on one device race on it, and its first call per device (which looks
+ *     the array's address up) must come before any stream capture.
  *
  * Canonical flattened shapes (the same B/E/K/N flattening the upstream launchers use,
  * csrc/cuda/scatter_cuda.cu:103-110, segment_csr_cuda.cu:144-146, segment_coo_cuda.cu:207-211):
@@ -31,7 +34,11 @@ extern "C" {
 typedef struct CUstream_st *tsb_stream_t;
 
 /* element types of src/out (the six types the upstream test-suite exercises, torch_scatter/testing.py:7-10) */
-enum tsb_dtype { TSB_F32 = 0, TSB_F64 = 1, TSB_F16 = 2, TSB_BF16 = 3, TSB_I32 = 4, TSB_I64 = 5 };
+/* The narrow integers (upstream dispatches them with AT_DISPATCH_ALL_TYPES_AND2, csrc/cuda/scatter_cuda.cu:114,
+ * segment_csr_cuda.cu:150, segment_coo_cuda.cu:217) accumulate in int32 and are narrowed once at the end: identical to
+ * accumulating in the narrow type (two's-complement wrap) for SUM / MUL / MIN / MAX; MEAN divides the narrowed sum. */
+enum tsb_dtype { TSB_F32 = 0, TSB_F64 = 1, TSB_F16 = 2, TSB_BF16 = 3, TSB_I32 = 4, TSB_I64 = 5,
+                 TSB_U8 = 6, TSB_I8 = 7, TSB_I16 = 8 };
 
 /* reductions (csrc/cuda/reducer.cuh:8-13; "div" is unreachable upstream and is not provided) */
 enum tsb_reduce { TSB_SUM = 0, TSB_MEAN = 1, TSB_MIN = 2, TSB_MAX = 3, TSB_MUL = 4,

@@ -19,7 +19,8 @@ import torch
 _HERE = osp.dirname(osp.abspath(__file__))
 _LIB_PATH = osp.join(_HERE, 'liboracle.so')
 REDUCE = {'sum': 0, 'add': 0, 'mean': 1, 'min': 2, 'max': 3, 'mul': 4}
-_SUFFIX = {torch.float32: 'f32', torch.float64: 'f64', torch.int32: 'i32', torch.int64: 'i64'}
+_SUFFIX = {torch.float32: 'f32', torch.float64: 'f64', torch.int32: 'i32', torch.int64: 'i64',
+           torch.uint8: 'u8', torch.int8: 'i8', torch.int16: 'i16'}
 _lib = None
 
 

@@ -9,7 +9,7 @@
  * (tests/golden/, produced by tests/golden/make_golden.py).
  *
  * Shapes are the flattened ones of the upstream loops: src [B,E,K], out [B,N,K], int64 indices.
- * One instantiation per arithmetic type: f32, f64, i32, i64.  16-bit floats are checked through the
+ * One instantiation per arithmetic type: f32, f64, i32, i64, u8, i8, i16.  16-bit floats are checked through the
  * f32 instantiation on up-converted inputs (upstream accumulates them in fp32 for the segment ops,
  * csrc/cpu/segment_csr_cpu.cpp:62) and rounded by the caller.
  *
@@ -184,3 +184,8 @@ DEFINE_ORACLE(f32, float, FLT_MAX, -FLT_MAX)
 DEFINE_ORACLE(f64, double, DBL_MAX, -DBL_MAX)
 DEFINE_ORACLE(i32, int32_t, INT32_MAX, INT32_MIN)
 DEFINE_ORACLE(i64, int64_t, INT64_MAX, INT64_MIN)
+/* the narrow integers upstream dispatches as well (AT_DISPATCH_ALL_TYPES_AND2): arithmetic in the type itself, i.e.
+ * promoted to int and narrowed back after every step, as the C++ loops do */
+DEFINE_ORACLE(u8, uint8_t, UINT8_MAX, 0)
+DEFINE_ORACLE(i8, int8_t, INT8_MAX, INT8_MIN)
+DEFINE_ORACLE(i16, int16_t, INT16_MAX, INT16_MIN)

@@ -24,6 +24,10 @@ constexpr unsigned kFullMask = 0xffffffffu;
 template <typename T> struct AccOf { using type = T; };
 template <> struct AccOf<__half> { using type = float; };
 template <> struct AccOf<__nv_bfloat16> { using type = float; };
+// narrow integers accumulate in int32 (the same result modulo 2^bits as accumulating in the type itself)
+template <> struct AccOf<uint8_t> { using type = int32_t; };
+template <> struct AccOf<int8_t> { using type = int32_t; };
+template <> struct AccOf<int16_t> { using type = int32_t; };
 template <typename T> using acc_t = typename AccOf<T>::type;
 
 template <typename T> __host__ __device__ __forceinline__ acc_t<T> to_acc(T v) { return (acc_t<T>)v; }
@@ -81,7 +85,10 @@ template <typename T, int REDUCE> __host__ __device__ __forceinline__ acc_t<T> r
 // full width of the type).
 template <typename T, int VEC> struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
 
-template <typename T> constexpr int full_vec() { return 16 / (int)sizeof(T); }
+// (narrow integers move element by element: rare types, not worth sixteen accumulators per lane)
+template <typename T> constexpr int full_vec() {
+  return (std::is_integral<T>::value && sizeof(T) < 4) ? 1 : 16 / (int)sizeof(T);
+}
 
 // Streaming (evict-first) load of a pack: the reductions read src exactly once.
 template <typename T, int VEC> __device__ __forceinline__ Pack<T, VEC> ld_stream(const T *p) {
@@ -169,6 +176,21 @@ inline int ilog2_ceil(int64_t v) {
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline bool aligned32(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
 
+// element / accumulator sizes of a tsb_dtype
+inline size_t dtype_elem_bytes(int dtype) {
+  switch (dtype) {
+    case TSB_F64: case TSB_I64: return 8;
+    case TSB_F16: case TSB_BF16: case TSB_I16: return 2;
+    case TSB_U8: case TSB_I8: return 1;
+    default: return 4;
+  }
+}
+inline size_t dtype_acc_bytes(int dtype) { return (dtype == TSB_F64 || dtype == TSB_I64) ? 8 : 4; }
+inline bool dtype_is_integer(int dtype) { return dtype == TSB_I32 || dtype == TSB_I64 || dtype == TSB_U8 || dtype == TSB_I8 || dtype == TSB_I16; }
+inline bool dtype_accumulates_wider(int dtype) {
+  return dtype == TSB_F16 || dtype == TSB_BF16 || dtype == TSB_U8 || dtype == TSB_I8 || dtype == TSB_I16;
+}
+
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? TSB_OK : TSB_ERR_LAUNCH; }
 
 inline int sm_count() {
@@ -183,7 +205,7 @@ inline int sm_count() {
   return cached[dev];
 }
 
-// Dispatch a generic lambda-like macro body over the six dtypes.
+// Dispatch a generic lambda-like macro body over the nine dtypes.
 #define TSB_DISPATCH_DTYPE(dtype, ...)                                              \
   [&]() -> int {                                                                    \
     switch (dtype) {                                                                \
@@ -193,6 +215,9 @@ inline int sm_count() {
       case TSB_BF16: { using scalar_t = __nv_bfloat16; return __VA_ARGS__(); }      \
       case TSB_I32: { using scalar_t = int32_t; return __VA_ARGS__(); }             \
       case TSB_I64: { using scalar_t = int64_t; return __VA_ARGS__(); }             \
+      case TSB_U8: { using scalar_t = uint8_t; return __VA_ARGS__(); }              \
+      case TSB_I8: { using scalar_t = int8_t; return __VA_ARGS__(); }               \
+      case TSB_I16: { using scalar_t = int16_t; return __VA_ARGS__(); }             \
       default: return TSB_ERR_DTYPE;                                                \
     }                                                                               \
   }()

@@ -303,7 +303,7 @@ extern "C" int tsb_gather_csr(const void *src, const int64_t *indptr, void *out,
   if (B < 0 || E < 0 || K < 0 || N < 0) return TSB_ERR_ARG;
   if (B * N * K == 0 || E == 0) return TSB_OK;
   if (src == nullptr || indptr == nullptr || out == nullptr) return TSB_ERR_ARG;
-  if (divide_by_count && (dtype == TSB_I32 || dtype == TSB_I64)) return TSB_ERR_DTYPE;
+  if (divide_by_count && dtype_is_integer(dtype)) return TSB_ERR_DTYPE;
   GatherCsrParams p;
   p.src = src; p.indptr = indptr; p.out = out;
   p.B = B; p.E = E; p.K = K; p.N = N; p.bstride = indptr_batch_stride;
@@ -320,7 +320,7 @@ extern "C" int tsb_gather_coo(const void *src, const int64_t *index, void *out, 
   if (B < 0 || E < 0 || K < 0 || N < 0) return TSB_ERR_ARG;
   if (B * E * K == 0 || N == 0) return TSB_OK;
   if (src == nullptr || index == nullptr || out == nullptr) return TSB_ERR_ARG;
-  if (count != nullptr && (dtype == TSB_I32 || dtype == TSB_I64)) return TSB_ERR_DTYPE;
+  if (count != nullptr && dtype_is_integer(dtype)) return TSB_ERR_DTYPE;
   GatherCooParams p;
   p.src = src; p.index = index; p.out = out; p.count = count;
   p.x = nullptr; p.op = 0; p.scale = nullptr;

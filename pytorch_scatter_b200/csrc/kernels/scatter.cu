@@ -774,23 +774,23 @@ scatter_init_kernel(const T *out, acc_t<T> *target, int64_t total, int fresh, in
   else target[i] = v;
 }
 
-template <typename T> __device__ __forceinline__ T mean_div(T v, int32_t c) { return v / (T)c; }
+// floats divide; integers round toward -inf (torch_scatter/scatter.py:65, div_ with rounding_mode='floor')
+template <typename T> __device__ __forceinline__ T mean_div(T v, int32_t c) {
+  if constexpr (std::is_integral<T>::value) {
+    using W = typename std::conditional<sizeof(T) == 8, int64_t, int32_t>::type;
+    const W a = (W)v, b = (W)c;
+    W q = a / b;
+    if ((a % b != 0) && (a < 0)) --q;
+    return (T)q;
+  } else {
+    return v / (T)c;
+  }
+}
 template <> __device__ __forceinline__ __half mean_div<__half>(__half v, int32_t c) {
   return __float2half_rn(__half2float(v) / __half2float(__int2half_rn(c)));
 }
 template <> __device__ __forceinline__ __nv_bfloat16 mean_div<__nv_bfloat16>(__nv_bfloat16 v, int32_t c) {
   return __float2bfloat16_rn(__bfloat162float(v) / __bfloat162float(__int2bfloat16_rn(c)));
-}
-// integer mean rounds toward -inf (torch_scatter/scatter.py:65, div_ with rounding_mode='floor')
-template <> __device__ __forceinline__ int32_t mean_div<int32_t>(int32_t v, int32_t c) {
-  int32_t q = v / c;
-  if ((v % c != 0) && (v < 0)) --q;
-  return q;
-}
-template <> __device__ __forceinline__ int64_t mean_div<int64_t>(int64_t v, int32_t c) {
-  int64_t q = v / c;
-  if ((v % c != 0) && (v < 0)) --q;
-  return q;
 }
 
 template <typename T, int OP>
@@ -1097,7 +1097,7 @@ inline int replicas_for(int64_t target_bytes) {
 template <typename T, int OP>
 int run_scatter(ScatterParams p, int reduce, void *workspace, cudaStream_t stream) {
   using U = acc_t<T>;
-  constexpr bool k16 = sizeof(T) == 2;
+  constexpr bool k16 = !std::is_same<T, acc_t<T>>::value;   // accumulates in a wider workspace: fp16 / bf16 -> fp32, narrow ints -> int32
   constexpr bool kMinMax = (OP == kMin || OP == kMax);
   constexpr bool kKeyed = kMinMax && !std::is_same<key_t<U>, U>::value;
   constexpr int kFull = full_vec<T>();
@@ -1333,8 +1333,8 @@ namespace {
 // it wins once the accumulation target no longer stays in L2 (the reductions then re-fetch output
 // lines or re-read the index per slice), for MIN/MAX earlier because value+arg targets are twice as big.
 bool prefer_grouped(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce) {
-  const int64_t acc = (dtype == TSB_F64 || dtype == TSB_I64) ? 8 : 4;
-  const int64_t elem = (dtype == TSB_F64 || dtype == TSB_I64) ? 8 : (dtype == TSB_F16 || dtype == TSB_BF16) ? 2 : 4;
+  const int64_t acc = (int64_t)tsb::dtype_acc_bytes(dtype);
+  const int64_t elem = (int64_t)tsb::dtype_elem_bytes(dtype);
   const int64_t target_bytes = B * N * K * acc;
   // products have no native atomic (compare-and-swap loops): grouping wins as soon as there is work to speak of
   if (reduce == TSB_MUL) return B * E * K >= (1ll << 18) && E < (1ll << 30);
@@ -1350,8 +1350,8 @@ int grouped_override() {  // test / tuning hook: "0" never, "1" whenever the sha
 
 extern "C" size_t tsb_scatter_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce) {
   if (B < 0 || E < 0 || N < 0 || K < 0) return 0;
-  const bool k16 = dtype == TSB_F16 || dtype == TSB_BF16;
-  const size_t acc = (dtype == TSB_F64 || dtype == TSB_I64) ? 8 : 4;
+  const bool k16 = tsb::dtype_accumulates_wider(dtype);
+  const size_t acc = tsb::dtype_acc_bytes(dtype);
   const size_t target = (size_t)B * (size_t)N * (size_t)K * acc;
   const int replicas = tsb::replicas_for((int64_t)target);
   size_t scratch = (k16 || replicas > 1) ? target * (size_t)replicas : 0;

@@ -363,7 +363,7 @@ bool scatter_grouped_possible(int64_t B, int64_t E, int64_t K, int64_t N, int64_
                               int dtype, int reduce) {
   if (reduce != TSB_SUM && reduce != TSB_MEAN && reduce != TSB_MIN && reduce != TSB_MAX && reduce != TSB_MUL) return false;
   // the CSR mean truncates integers, upstream's scatter_mean floors them (torch_scatter/scatter.py:65)
-  if (reduce == TSB_MEAN && (dtype == TSB_I32 || dtype == TSB_I64)) return false;
+  if (reduce == TSB_MEAN && dtype_is_integer(dtype)) return false;
   if (sk != 0 || (E > 1 && se != 1) || (B > 1 && sb != 0)) return false;  // one index entry per source row, shared by the batches
   return B >= 1 && K >= 1 && N >= 1 && E >= 1 && E < (1ll << 30) && N < (1ll << 31) - 1;
 }
@@ -538,9 +538,7 @@ extern "C" int tsb_segment_csr_perm(const void *src, const int64_t *rowptr, cons
   if (rowptr == nullptr || out == nullptr || (E > 0 && (src == nullptr || perm == nullptr))) return TSB_ERR_ARG;
   const bool slice = row_lo != 0 || row_hi != N;
   if (slice && B != 1) return TSB_ERR_ARG;
-  size_t elem = 4;
-  if (dtype == TSB_F64 || dtype == TSB_I64) elem = 8;
-  else if (dtype == TSB_F16 || dtype == TSB_BF16) elem = 2;
+  const size_t elem = dtype_elem_bytes(dtype);
   CsrParams p;
   p.src = src;
   p.indptr = rowptr + row_lo;

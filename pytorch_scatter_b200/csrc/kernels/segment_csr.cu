@@ -22,274 +22,13 @@
 //
 // Replaces segment_csr_kernel / segment_csr_broadcast_kernel of the upstream project
 // (csrc/cuda/segment_csr_cuda.cu:15-95), which walk each row with a single thread per feature.
-#include <cstdlib>
 #include <mutex>
 
-#include "csr_reduce.cuh"
+#include "csr_rows.cuh"
 
 namespace tsb {
 
 namespace {
-
-// Resident single-warp CTAs per SM the streaming kernel is compiled for (caps its registers at 80),
-// and the depth of its shared-memory load ring (a power of two): 16 steps of 512 bytes = 8 KiB in
-// flight per warp, 192 KiB per SM.
-constexpr int kMinCtasPerSm = 24;
-constexpr int kRingDepth = 16;
-constexpr int kWindowRows = 31;          // lane j holds row pointer j of the window, so rows+1 <= 32
-constexpr int kRelInf = 0x3fffffff;      // "never ends inside this chunk"
-constexpr int64_t kChunkBytes = 128 * 1024;
-constexpr int64_t kFlatTileBytes = 32 * 1024;  // K == 1: a chunk is staged whole in shared memory (csr_flat_kernel)
-constexpr int kFlatThreads = 128;
-constexpr int64_t kFlatRowBytes = 0;           // widest entry (besides K == 1) that goes through csr_flat_kernel: none.
-                                               // Measured at 64 / 128 / 256 bytes per entry: 0.45 vs 0.26 ms (fp32 F=16),
-                                               // 1.07 vs 0.55 ms (bf16 F=64), 1.54 vs 0.73 ms (fp32 F=64) against the stream.
-constexpr int kFlatLongRow = 64;               // entries inside the chunk from which a warp, not a thread, reduces a row
-
-struct CsrGeom {
-  int l_log2;            // lanes per entry
-  int chunk_entries;     // C: entries per chunk (a power of two >= 32)
-  int64_t chunks;        // chunks per batch = max(1, ceil(E / C))
-  // workspace: per chunk two partial rows (HEAD, TAIL) of K accumulators, the same of int64 arg
-  // indices for MIN/MAX, and the id of the row whose HEAD partial the chunk stored (-1: none)
-  void *carry_val;
-  int64_t *carry_arg;
-  int64_t *head_row;
-};
-
-// Chunk length: a power of two holding about kChunkBytes of source, shortened (down to one full
-// warp step) when the whole reduced dimension would otherwise give too few chunks to occupy the GPU.
-// Entries narrow enough for csr_flat_kernel: K == 1; the test hook TSB_CSR_FORCE_FLAT=1 sends every entry of up
-// to 64 bytes through it.
-inline bool flat_rows(int64_t K, size_t elem) {
-  int64_t limit = kFlatRowBytes;
-  if (const char *v = std::getenv("TSB_CSR_FORCE_FLAT")) limit = (*v == '1') ? 64 : limit;
-  return K == 1 || K * (int64_t)elem <= limit;
-}
-
-inline int chunk_entries_for(int64_t K, size_t elem, int64_t E) {
-  const bool flat = flat_rows(K, elem);
-  int64_t c = (flat ? kFlatTileBytes : kChunkBytes) / (K * (int64_t)elem);
-  // ~7 single-warp CTAs per resident slot of a 148-SM part; flat kernel: 128-thread CTAs that pay two row searches each
-  const int64_t want_chunks = flat ? 4096 : 16384;
-  if (E / want_chunks < c) c = E / want_chunks;
-  if (const char *forced = std::getenv("TSB_CSR_CHUNK_ENTRIES")) {  // test hook: force short chunks
-    const long long v = std::atoll(forced);
-    if (v >= 32) c = v;
-  }
-  int64_t pow2 = 32;
-  while (pow2 * 2 <= c && pow2 < (1 << 20)) pow2 *= 2;
-  return (int)pow2;
-}
-
-// Per-lane accumulators of one row: VEC values and, for the reductions that need it, a second word per
-// value - the arg index for MIN/MAX, the bits of the running sum for LSE.
-// LSE is the online log-sum-exp: `val` holds the running maximum m, the second word the running sum
-// s = sum exp(x - m); two partials combine as m = max(m1, m2), s = s1 exp(m1 - m) + s2 exp(m2 - m), and
-// the row result is m + log s.  It exists for fp32 accumulators only (fp32 / fp16 / bf16 sources).
-template <typename T, int REDUCE, int VEC, typename ArgT = int64_t> struct RowAcc {
-  using A = acc_t<T>;
-  static constexpr bool kArg = (REDUCE == kMin || REDUCE == kMax);
-  static constexpr bool kLseAcc = (REDUCE == kLse);
-  static constexpr bool kPair = kArg || kLseAcc;
-  A val[VEC];
-  ArgT arg[kPair ? VEC : 1];
-
-  static __device__ __forceinline__ float sum_of(ArgT word) { return __int_as_float((int)word); }
-  static __device__ __forceinline__ ArgT word_of(float s) { return (ArgT)__float_as_int(s); }
-
-  __device__ __forceinline__ void init(ArgT sentinel) {
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-      val[i] = reduce_identity<T, REDUCE>();
-      if (kArg) arg[i] = sentinel;
-      if (kLseAcc) arg[i] = word_of(0.0f);
-    }
-  }
-  // Entries arrive in increasing e within a lane, so strict comparisons keep the first winner
-  // (csrc/cpu/reducer.h:63-67).
-  // TIES (entries arrive in no particular order): an equal value wins if its id is smaller.
-  template <bool TIES = false> __device__ __forceinline__ void update(const Pack<T, VEC> &v, ArgT e, ArgT none = 0) {
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-      const A x = to_acc<T>(v.v[i]);
-      if (REDUCE == kSum || REDUCE == kMean) {
-        val[i] += x;
-      } else if (REDUCE == kMul) {
-        val[i] *= x;
-      } else if (REDUCE == kMin) {
-        if (x < val[i] || (TIES && x == val[i] && e < arg[i] && arg[i] != none)) { val[i] = x; arg[i] = e; }
-      } else if (REDUCE == kMax) {
-        if (x > val[i] || (TIES && x == val[i] && e < arg[i] && arg[i] != none)) { val[i] = x; arg[i] = e; }
-      } else {
-        // One exponential, no branch: whichever of the running maximum and x is larger becomes the
-        // reference, the other side is scaled by exp(-|x - m|).  The identity is the lowest finite float,
-        // so the first entry gives exp(-huge) = 0 for the empty sum, and an entry of -inf adds 0.
-        const float m = (float)val[i], xf = (float)x;
-        const float d = xf == m ? 0.0f : xf - m;  // equal infinities: inf - inf would be NaN, upstream gives +inf
-        const float e = __expf(-fabsf(d));
-        const float sum = sum_of(arg[i]);
-        arg[i] = word_of(d > 0.0f ? fmaf(sum, e, 1.0f) : sum + e);
-        val[i] = (A)fmaxf(m, xf);
-      }
-    }
-  }
-  // Merge another lane's partial; for MIN/MAX the smaller position wins on equal values so that the
-  // final arg is the first occurrence over the whole row.
-  __device__ __forceinline__ void merge(const A *oval, const ArgT *oarg) {
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-      if (REDUCE == kSum || REDUCE == kMean) {
-        val[i] += oval[i];
-      } else if (REDUCE == kMul) {
-        val[i] *= oval[i];
-      } else if (kArg) {
-        const bool better = (REDUCE == kMin) ? (oval[i] < val[i]) : (oval[i] > val[i]);
-        if (better || (oval[i] == val[i] && oarg[i] < arg[i])) { val[i] = oval[i]; arg[i] = oarg[i]; }
-      } else {
-        const float m1 = (float)val[i], m2 = (float)oval[i];
-        const float d = m2 == m1 ? 0.0f : m2 - m1;
-        const float e = __expf(-fabsf(d));
-        const float s1 = sum_of(arg[i]), s2 = sum_of(oarg[i]);
-        arg[i] = word_of(d > 0.0f ? fmaf(s1, e, s2) : fmaf(s2, e, s1));
-        val[i] = (A)fmaxf(m1, m2);
-      }
-    }
-  }
-  __device__ __forceinline__ void butterfly(int from, int to) {
-    for (int off = from; off < to; off <<= 1) {
-      A oval[VEC];
-      ArgT oarg[kPair ? VEC : 1];
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        oval[i] = shfl_xor<A>(val[i], off);
-        if (kPair) oarg[i] = shfl_xor<ArgT>(arg[i], off);
-      }
-      merge(oval, oarg);
-    }
-  }
-};
-
-// MEAN: the row total times 1/count (count as upstream's writer converts it: an int, at least 1;
-// csrc/cpu/reducer.h:74-75).  For floating types one reciprocal per row replaces VEC divisions; the
-// result differs from a true division by at most one ulp, far inside the 1e-5 tolerance.  Integer
-// types divide exactly (truncating, as the CPU loop does).
-template <typename T> struct MeanScale {
-  acc_t<T> inv;
-  __device__ __forceinline__ explicit MeanScale(int64_t count) : inv((acc_t<T>)1 / (acc_t<T>)(int)count) {}
-  __device__ __forceinline__ T apply(acc_t<T> v) const { return from_acc<T>(v * inv); }
-};
-template <> struct MeanScale<int32_t> {
-  int32_t c;
-  __device__ __forceinline__ explicit MeanScale(int64_t count) : c((int32_t)count) {}
-  __device__ __forceinline__ int32_t apply(int32_t v) const { return v / c; }
-};
-template <> struct MeanScale<int64_t> {
-  int64_t c;
-  __device__ __forceinline__ explicit MeanScale(int64_t count) : c((int64_t)(int)count) {}
-  __device__ __forceinline__ int64_t apply(int64_t v) const { return v / c; }
-};
-
-// Address of element `off` of the output: T everywhere except the LSE table, which is fp32.
-template <typename T, int REDUCE, bool EXTRAS>
-__device__ __forceinline__ T *row_address(const CsrParams &p, int64_t grow, int64_t col) {
-  if constexpr (REDUCE == kLse) {
-    return reinterpret_cast<T *>(static_cast<float *>(p.out) + grow * p.K + col);
-  } else {
-    if (EXTRAS && p.route_world > 0) {  // sharded scatter: the row goes to its owner's staging buffer (maybe over NVLink)
-      const int64_t q = grow / p.route_rows;
-      const int64_t local = grow - q * p.route_rows;
-      return static_cast<T *>(p.route_base[q]) + ((int64_t)p.route_rank * p.route_rows + local) * p.K + col;
-    }
-    return static_cast<T *>(p.out) + grow * p.K + col;
-  }
-}
-
-// A routed row of a 16-bit source kept in fp32 (CsrParams::route_wide): this lane's VEC sums go to the owner's
-// fp32 staging buffer as they are.  True if the row was stored.
-template <typename T, int REDUCE, int VEC, bool EXTRAS, typename ArgT>
-__device__ __forceinline__ bool store_wide_routed(const CsrParams &p, const RowAcc<T, REDUCE, VEC, ArgT> &acc,
-                                                  int64_t grow, int64_t col) {
-  if constexpr (EXTRAS && sizeof(T) == 2 && REDUCE == kSum) {
-    if (p.route_world > 0 && p.route_wide) {
-      const int64_t q = grow / p.route_rows;
-      const int64_t local = grow - q * p.route_rows;
-      float *dst = static_cast<float *>(p.route_base[q]) + ((int64_t)p.route_rank * p.route_rows + local) * p.K + col;
-      if constexpr (VEC % 4 == 0) {
-#pragma unroll
-        for (int i = 0; i < VEC; i += 4)
-          *reinterpret_cast<float4 *>(dst + i) = make_float4(acc.val[i], acc.val[i + 1], acc.val[i + 2], acc.val[i + 3]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) dst[i] = acc.val[i];
-      }
-      return true;
-    }
-  }
-  return false;
-}
-
-// Writes one finished row (this lane's VEC columns of it).  `acc` is the reduction over the row's
-// source entries only; in kCooSeeded mode the row's previous value of `out` joins here.  Arg indices
-// in `acc` are relative to `arg_base`; `arg_none` marks "no element won" and becomes `sentinel`.
-template <typename T, int REDUCE, int VEC, typename ArgT>
-__device__ __forceinline__ void write_row(const RowAcc<T, REDUCE, VEC, ArgT> &acc, T *out_p, int64_t *arg_p,
-                                          int64_t len, int mode, int64_t sentinel, int64_t arg_base, ArgT arg_none) {
-  using A = acc_t<T>;
-  constexpr bool kArg = RowAcc<T, REDUCE, VEC, ArgT>::kArg;
-  if (mode == kCooSeeded && len == 0) {  // a row the index never names keeps its value
-    if (kArg) {
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) arg_p[i] = sentinel;
-    }
-    return;
-  }
-  Pack<T, VEC> seed;
-  if (mode == kCooSeeded) seed = ld_pack<T, VEC>(out_p);
-  Pack<T, VEC> o;
-  if constexpr (REDUCE == kLse) {
-    // m + log s, fp32 whatever T is (a 16-bit table would cost the softmax its accuracy): `out_p` is the
-    // fp32 address.  A row without (finite) entries gives -inf.
-    float *o = reinterpret_cast<float *>(out_p);
-    float r[VEC];
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-      const float sum = RowAcc<T, REDUCE, VEC, ArgT>::sum_of(acc.arg[i]);
-      r[i] = sum == 0.0f ? -INFINITY : (float)acc.val[i] + __logf(sum);
-    }
-    if constexpr (VEC % 4 == 0) {
-#pragma unroll
-      for (int i = 0; i < VEC; i += 4) *reinterpret_cast<float4 *>(o + i) = make_float4(r[i], r[i + 1], r[i + 2], r[i + 3]);
-    } else {
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) o[i] = r[i];
-    }
-    return;
-  }
-  const MeanScale<T> scale(REDUCE == kMean && len > 0 ? len : 1);
-#pragma unroll
-  for (int i = 0; i < VEC; ++i) {
-    A v = acc.val[i];
-    if (!kArg) {
-      if (mode == kCooSeeded) v = (REDUCE == kMul) ? v * to_acc<T>(seed.v[i]) : v + to_acc<T>(seed.v[i]);
-      o.v[i] = (REDUCE == kMean) ? scale.apply(v) : from_acc<T>(v);
-    } else {
-      int64_t a = (acc.arg[i] == arg_none) ? sentinel : arg_base + (int64_t)acc.arg[i];
-      if (mode == kCsr) {
-        if (len == 0) { v = (A)0; a = sentinel; }
-      } else if (mode == kCooFresh) {
-        if (v == reduce_identity<T, REDUCE>()) v = (A)0;
-      } else {
-        const A s = to_acc<T>(seed.v[i]);
-        const bool seed_wins = (REDUCE == kMin) ? (s <= v) : (s >= v);
-        if (seed_wins) { v = s; a = sentinel; }
-      }
-      o.v[i] = from_acc<T>(v);
-      arg_p[i] = a;
-    }
-  }
-  st_pack<T, VEC>(out_p, o);
-}
 
 // Streaming kernel: blockIdx.x = (batch, chunk); one warp.
 // 16-bit MIN/MAX carry eight fp32 values and eight arg indices per lane: under the 80-register cap they spill, so
@@ -518,292 +257,6 @@ __global__ void __launch_bounds__(32, stream_ctas_per_sm<T, REDUCE, VEC>()) csr_
       }
     }
   }
-}
-
-__device__ __forceinline__ int64_t first_row_ending_after(const int64_t *ip, int64_t N, int64_t pos, int lane);
-
-// ---------------------------------------------------------------------------------------------------------------
-// Walking kernel: the same chunks, carries and fix-up as the streaming kernel, another division of labour inside
-// the warp.  The streaming kernel spreads every 512-byte step over all lane groups and closes rows with a shuffle
-// butterfly over the groups: at fp32 with 256-byte entries that is hidden behind DRAM, but with 16-bit data, narrow
-// entries or rows of two or three entries it is what bounds the kernel (86 to 169 warp instructions per step
-// counted).  Here every lane group (the L lanes that hold one entry) owns a contiguous PIECE of the chunk,
-// C / (32 / L) entries, and walks it entry by entry on its own: accumulate while the row lasts, write the row when
-// it ends - no shuffle per step, no butterfly per row.  What the groups share is settled once per chunk:
-//   * before the walk the warp scans the row pointers from the chunk's first row (32 per load) and counts, for each
-//     group, the rows that end at or before the piece's start: that is the group's first row;
-//   * a row that runs from one piece into the next is never written during the walk.  The group where it ends keeps
-//     what it saw of it (its "head"), every group keeps the row still open at its piece's end (its "tail"), and after
-//     the walk a scan over the groups hands every tail to the group where the row goes on, in a fixed order.  The
-//     chunk's own HEAD / TAIL partials go to the workspace exactly as in the streaming kernel.
-// Row pointers live in per-group register windows (lane j of a group holds pointer j of the window, L - 1 rows per
-// reload, reloads hit L1 after the scan); all shuffles inside a group's divergent code name that group's lanes only.
-// Entries of at least four 16-byte packs' worth of lanes are required (L >= 4).
-template <typename T, int REDUCE, int VEC> constexpr int walk_ctas_per_sm() {
-  return (sizeof(T) == 2 && VEC > 1 && (REDUCE == kMin || REDUCE == kMax)) ? 12 : 20;
-}
-constexpr int kWalkRing = 12;   // entries in flight per lane group
-
-template <typename T, int REDUCE, int VEC, int MODE>
-__global__ void __launch_bounds__(32, walk_ctas_per_sm<T, REDUCE, VEC>()) csr_walk_kernel(CsrParams p, CsrGeom g) {
-  constexpr bool INDIRECT = MODE >= 1;
-  constexpr bool EXTRAS = MODE == 2;
-  using A = acc_t<T>;
-  using Acc = RowAcc<T, REDUCE, VEC, int>;  // arg indices relative to the chunk start (source entries with a permutation)
-  constexpr bool kArg = Acc::kArg;
-  constexpr int kBefore = -1;               // a row pointer that lies before the chunk
-
-  const T *__restrict__ src = static_cast<const T *>(p.src);
-  const int L = 1 << g.l_log2;
-  const int lane = threadIdx.x;
-  const int col = lane & (L - 1);
-  const int sub = lane >> g.l_log2;
-  const int eps = 32 >> g.l_log2;
-  const unsigned gmask = (L == 32 ? kFullMask : ((1u << L) - 1u)) << (sub << g.l_log2);  // this group's lanes
-  const int gbase = sub << g.l_log2;
-  const int64_t Kv = p.K / VEC;
-
-  int64_t chunk_id = blockIdx.x;
-  if (EXTRAS && p.route_world > 1) {  // start with the next owner's rows (see the streaming kernel)
-    int64_t first_row = (int64_t)((p.route_rank + 1) % p.route_world) * p.route_rows;
-    if (first_row > p.N) first_row = p.N;
-    chunk_id = (chunk_id + clamp64(p.indptr[first_row], 0, p.E) / g.chunk_entries) % g.chunks;  // single batch
-  }
-  const int64_t b = chunk_id / g.chunks;
-  const int64_t w = chunk_id - b * g.chunks;
-  const int64_t cs = w * g.chunk_entries;
-  const int64_t ce = (cs + g.chunk_entries < p.E) ? cs + g.chunk_entries : p.E;
-  const int t = (int)(ce - cs);
-  const int64_t *ip = p.indptr + b * p.bstride;
-  if (lane == 0) g.head_row[chunk_id] = -1;
-  if (EXTRAS && p.skip_outside && (ce <= ip[0] || cs >= ip[p.N])) return;  // warp-uniform
-
-  const int piece = g.chunk_entries >> (5 - g.l_log2);
-  const int ps = (sub * piece < t) ? sub * piece : t;
-  const int pe = ((sub + 1) * piece < t) ? (sub + 1) * piece : t;
-  const int my_n = pe - ps;
-
-  // ---- first row of the chunk, then of every piece ---------------------------------------------------------------
-  const int64_t r_first = (w > 0) ? first_row_ending_after(ip, p.N, cs, lane) : 0;
-  int64_t my_first = r_first;
-  {
-    // rows r >= r_first with ends[r] <= cs + ps belong to earlier pieces; count them 32 at a time
-    int before = 0;
-    for (int64_t r0 = r_first; r0 < p.N; r0 += 32) {
-      const int64_t r = r0 + lane;
-      const int64_t end = (r < p.N) ? __ldg(ip + r + 1) - cs : (int64_t)kRelInf;
-      for (int q = 1; q < eps; ++q) {
-        const int bound = (q * piece < t) ? q * piece : t;
-        const int c = __popc(__ballot_sync(kFullMask, end <= (int64_t)bound));
-        if (q == sub) before += c;
-      }
-      if (__any_sync(kFullMask, end > (int64_t)t)) break;  // the rows that follow end after the chunk
-    }
-    my_first += before;
-  }
-
-  const T *bsrc = src + (b * p.E) * p.K;
-  A *carry = static_cast<A *>(g.carry_val) + chunk_id * 2 * p.K;
-  int64_t *carry_arg = Acc::kPair ? g.carry_arg + chunk_id * 2 * p.K : nullptr;
-  extern __shared__ __align__(16) unsigned char s_walk_raw[];
-  auto s_ring = reinterpret_cast<Pack<T, VEC>(*)[32]>(s_walk_raw);             // [kWalkRing][32]
-  int(*s_id)[32] = reinterpret_cast<int(*)[32]>(s_walk_raw + sizeof(Pack<T, VEC>) * kWalkRing * 32);  // INDIRECT MIN/MAX
-
-  for (int64_t cb = 0; cb < Kv; cb += L) {
-    const int64_t c = cb + col;
-    const bool col_ok = c < Kv;
-
-    // ---- this group's window of row pointers: lane j holds pointer j of rows [win, win + L - 1] ------------------
-    int64_t win = my_first;
-    int rel = 0;
-    auto load_window = [&]() {
-      const int64_t r = win + col;
-      int64_t v = (r <= p.N) ? __ldg(ip + r) - cs : (int64_t)kRelInf;
-      rel = v < 0 ? kBefore : (v > kRelInf ? kRelInf : (int)v);
-      for (int off = 1; off < L; off <<= 1) {  // monotone inside the window, so that bad pointers stay harmless
-        const int o = __shfl_up_sync(gmask, rel, off, L);
-        if (col >= off && o > rel) rel = o;
-      }
-    };
-    load_window();
-    int cur = 0;
-    int cur_start = __shfl_sync(gmask, rel, gbase + 0);
-    int cur_end = __shfl_sync(gmask, rel, gbase + 1);
-    if (win >= p.N) { cur_start = kRelInf; cur_end = kRelInf; }
-
-    Acc acc, head;
-    acc.init(kRelInf);
-    head.init(kRelInf);
-    int64_t head_row = -1;   // the row that began before this piece and ended inside it
-    int head_len = 0;
-    bool head_from_before_chunk = false;
-
-    // closes the open row (it ends at or before the position the walk has reached)
-    auto close_row = [&]() {
-      const int64_t row = win + cur;
-      if (cur_start < ps) {
-        // began before this piece (in an earlier piece, or before the chunk): only the scan after the walk knows
-        // what the earlier pieces hold of it
-        head = acc;
-        head_row = row;
-        head_len = cur_end - cur_start;
-        head_from_before_chunk = cur_start == kBefore;
-      } else {
-        const int64_t grow = b * p.N + row;
-        if (col_ok && !store_wide_routed<T, REDUCE, VEC, EXTRAS, int>(p, acc, grow, c * VEC)) {
-          write_row<T, REDUCE, VEC, int>(acc, row_address<T, REDUCE, EXTRAS>(p, grow, c * VEC),
-                                         kArg ? p.arg_out + grow * p.K + c * VEC : nullptr,
-                                         (int64_t)(cur_end - cur_start), p.mode, p.E, INDIRECT ? 0 : cs, kRelInf);
-        }
-        if (col == 0 && cb == 0 && p.count_out != nullptr) {
-          const int len = cur_end - cur_start;
-          static_cast<T *>(p.count_out)[grow] = from_acc<T>((A)(len > 0 ? len : 1));
-        }
-      }
-      acc.init(kRelInf);
-      ++cur;
-      if (cur == L - 1) {
-        win += L - 1;
-        cur = 0;
-        load_window();
-      }
-      cur_start = cur_end;
-      cur_end = __shfl_sync(gmask, rel, gbase + cur + 1);
-      if (win + cur >= p.N) { cur_start = kRelInf; cur_end = kRelInf; }  // past the last row: nothing more closes
-    };
-
-    // ---- the ring: every lane copies the packs of its own group's entries, kWalkRing entries ahead ----------------
-    const int row_elems = (int)p.K;
-    const T *next_ptr = bsrc + (cs + ps) * p.K + c * VEC;
-    const T *perm_col = bsrc + c * VEC;
-    // INDIRECT: lane j of the group holds the source entry of position (window start + j); two windows are kept
-    int pw0 = 0, pw1 = 0;
-    auto load_perm_window = [&](int first) -> int {
-      const int q = first + col;
-      int v = (q < my_n) ? p.perm[cs + ps + q] : 0;
-      const int last = (int)p.E - 1;
-      return v < 0 ? 0 : (v > last ? last : v);
-    };
-    if (INDIRECT) { pw0 = load_perm_window(0); pw1 = load_perm_window(L); }
-    int next_step = 0;
-    auto issue = [&](int into) {
-      if (INDIRECT) {
-        if (next_step > 0 && (next_step & (L - 1)) == 0) { pw0 = pw1; pw1 = load_perm_window(next_step + L); }
-        const int id = __shfl_sync(kFullMask, pw0, gbase + (next_step & (L - 1)));
-        if (col_ok && next_step < my_n) {
-          async_copy_pack<T, VEC>(&s_ring[into][lane], perm_col + (int64_t)id * row_elems);
-          if (kArg) s_id[into][lane] = id;
-        }
-      } else {
-        if (col_ok && next_step < my_n) async_copy_pack<T, VEC>(&s_ring[into][lane], next_ptr);
-        next_ptr += p.K;
-      }
-      async_commit();
-      ++next_step;
-    };
-#pragma unroll
-    for (int j = 0; j < kWalkRing; ++j) issue(j);
-
-    int slot = 0;
-    for (int step = 0; step < piece; ++step) {   // warp-uniform trip count
-      async_wait_all_but<kWalkRing - 1>();
-      const int e = ps + step;
-      if (step < my_n) {
-        while (cur_end <= e) close_row();
-        const Pack<T, VEC> v = s_ring[slot][lane];
-        const int id = (INDIRECT && kArg) ? s_id[slot][lane] : e;
-        if (e >= cur_start) acc.template update<INDIRECT>(v, id, kRelInf);
-      }
-      issue(slot);
-      slot = (slot + 1 == kWalkRing) ? 0 : slot + 1;
-    }
-    async_wait_all_but<0>();
-    while (cur_end <= pe) close_row();   // rows that end exactly at the piece's end, empty ones included
-
-    // ---- settle the rows that run over piece borders ---------------------------------------------------------------
-    // tail: the row still open at the end of this piece (acc holds what this piece saw of it)
-    const bool tail_open = (win + cur < p.N) && cur_start < pe;
-    const bool tail_fresh = tail_open && cur_start >= ps;   // it began inside this piece
-    Acc carry_in;
-    carry_in.init(kRelInf);
-    for (int q = 1; q < eps; ++q) {   // warp-uniform: group q takes over from group q - 1
-      A oval[VEC];
-      int oarg[Acc::kPair ? VEC : 1];
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        oval[i] = __shfl_up_sync(kFullMask, acc.val[i], L);
-        if (Acc::kPair) oarg[i] = __shfl_up_sync(kFullMask, acc.arg[i], L);
-      }
-      const int prev_open = __shfl_up_sync(kFullMask, (int)tail_open, L);
-      if (sub == q && prev_open) {
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-          carry_in.val[i] = oval[i];
-          if (Acc::kPair) carry_in.arg[i] = oarg[i];
-        }
-        if (tail_open && !tail_fresh) {   // the same row runs on through this whole piece: earlier pieces first
-          Acc merged = carry_in;
-          merged.merge(acc.val, acc.arg);
-          acc = merged;
-        }
-      }
-    }
-    if (head_row >= 0) {
-      Acc total = carry_in;   // the earlier pieces' share (identity if the row began before the chunk in piece 0)
-      total.merge(head.val, head.arg);
-      if (head_from_before_chunk) {
-        // the row began in an earlier chunk: leave this chunk's share for the fix-up kernel
-        if (col_ok) {
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) {
-            carry[c * VEC + i] = total.val[i];
-            if (kArg) carry_arg[c * VEC + i] = total.arg[i] == kRelInf ? p.E : (INDIRECT ? 0 : cs) + total.arg[i];
-            if (Acc::kLseAcc) carry_arg[c * VEC + i] = total.arg[i];
-          }
-        }
-        if (col == 0 && cb == 0) g.head_row[chunk_id] = head_row;
-      } else {
-        const int64_t grow = b * p.N + head_row;
-        if (col_ok && !store_wide_routed<T, REDUCE, VEC, EXTRAS, int>(p, total, grow, c * VEC)) {
-          write_row<T, REDUCE, VEC, int>(total, row_address<T, REDUCE, EXTRAS>(p, grow, c * VEC),
-                                         kArg ? p.arg_out + grow * p.K + c * VEC : nullptr, (int64_t)head_len, p.mode, p.E,
-                                         INDIRECT ? 0 : cs, kRelInf);
-        }
-        if (col == 0 && cb == 0 && p.count_out != nullptr)
-          static_cast<T *>(p.count_out)[grow] = from_acc<T>((A)(head_len > 0 ? head_len : 1));
-      }
-    }
-    // the row still open at the chunk's end runs on into the next chunk: store what this chunk holds of it
-    if (sub == eps - 1 && tail_open && col_ok) {
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        carry[p.K + c * VEC + i] = acc.val[i];
-        if (kArg) carry_arg[p.K + c * VEC + i] = acc.arg[i] == kRelInf ? p.E : (INDIRECT ? 0 : cs) + acc.arg[i];
-        if (Acc::kLseAcc) carry_arg[p.K + c * VEC + i] = acc.arg[i];
-      }
-    }
-  }
-}
-
-// First row whose end (indptr[r + 1]) lies after `pos`, by a cooperative 32-ary search of one warp; N if none.
-__device__ __forceinline__ int64_t first_row_ending_after(const int64_t *ip, int64_t N, int64_t pos, int lane) {
-  int64_t lo = 0, hi = N;  // answer in [lo, hi]; hi == N means "no such row"
-  while (hi - lo > 32) {
-    const int64_t step = (hi - lo + 31) / 32;
-    int64_t probe = lo + (lane + 1) * step - 1;
-    if (probe > hi - 1) probe = hi - 1;
-    const unsigned gt = __ballot_sync(kFullMask, ip[probe + 1] > pos);
-    if (gt == 0) { lo = hi; break; }
-    const int f = __ffs((int)gt) - 1;
-    const int64_t new_hi = lo + (int64_t)(f + 1) * step - 1;
-    lo = lo + (int64_t)f * step;
-    hi = new_hi < hi - 1 ? new_hi : hi - 1;  // ends[hi] > pos is known: the answer is <= hi
-    if (hi < lo) hi = lo;
-  }
-  if (lo >= N) return N;
-  const bool in = lo + lane <= hi && lo + lane < N;
-  const unsigned gt = __ballot_sync(kFullMask, in && ip[lo + lane + 1] > pos);
-  return gt ? lo + (__ffs((int)gt) - 1) : hi;
 }
 
 // K == 1 (a 1-D source; wider entries only through the tuning hook, where it loses): the streaming kernel would
@@ -1060,22 +513,26 @@ inline int choose_kernel(const CsrParams &p, int64_t packs_per_entry, bool wide_
   return p.E / rows < 6 ? kWalk : kStream;   // sums over rows of a few entries
 }
 
+template <typename T> constexpr int dtype_code() {
+  if (std::is_same<T, float>::value) return TSB_F32;
+  if (std::is_same<T, double>::value) return TSB_F64;
+  if (std::is_same<T, __half>::value) return TSB_F16;
+  if (std::is_same<T, __nv_bfloat16>::value) return TSB_BF16;
+  if (std::is_same<T, int32_t>::value) return TSB_I32;
+  if (std::is_same<T, uint8_t>::value) return TSB_U8;
+  if (std::is_same<T, int8_t>::value) return TSB_I8;
+  if (std::is_same<T, int16_t>::value) return TSB_I16;
+  return TSB_I64;
+}
+
 template <typename T, int REDUCE, int VEC, int MODE>
 void launch_chunks(const CsrParams &p, const CsrGeom &g, unsigned total_chunks, bool walk, cudaStream_t stream) {
   constexpr bool kWide = VEC > full_vec<T>();
   if constexpr (kWide) {
-    if constexpr (walk_wide_built<T, REDUCE, MODE>()) {
-      const size_t smem = sizeof(Pack<T, VEC>) * kWalkRing * 32;
-      csr_walk_kernel<T, REDUCE, VEC, MODE><<<total_chunks, 32, smem, stream>>>(p, g);
-    }
+    launch_csr_walk(p, &g, total_chunks, dtype_code<T>(), REDUCE, true, MODE, stream);   // built: see choose_kernel
   } else {
     if constexpr (VEC > 1) {   // (scalar packs always stream)
-      if (walk) {
-        constexpr bool kIds = MODE >= 1 && (REDUCE == kMin || REDUCE == kMax);
-        const size_t smem = sizeof(Pack<T, VEC>) * kWalkRing * 32 + (kIds ? sizeof(int) * kWalkRing * 32 : 0);
-        csr_walk_kernel<T, REDUCE, VEC, MODE><<<total_chunks, 32, smem, stream>>>(p, g);
-        return;
-      }
+      if (walk && launch_csr_walk(p, &g, total_chunks, dtype_code<T>(), REDUCE, false, MODE, stream)) return;
     }
     csr_stream_kernel<T, REDUCE, VEC, MODE><<<total_chunks, 32, 0, stream>>>(p, g);
   }
@@ -1178,12 +635,7 @@ int launch_typed(const CsrParams &p, cudaStream_t stream) {
 size_t csr_reduce_workspace_bytes(int64_t B, int64_t E, int64_t K, int64_t N, int dtype, int reduce) {
   (void)N;
   if (B <= 0 || K <= 0 || E < 0) return 256;
-  size_t elem = 4, acc = 4;
-  switch (dtype) {
-    case TSB_F64: case TSB_I64: elem = 8; acc = 8; break;
-    case TSB_F16: case TSB_BF16: elem = 2; acc = 4; break;
-    default: break;
-  }
+  const size_t elem = dtype_elem_bytes(dtype), acc = dtype_acc_bytes(dtype);
   const int c = chunk_entries_for(K, elem, E);
   int64_t chunks = (E + c - 1) / c;
   if (chunks < 1) chunks = 1;

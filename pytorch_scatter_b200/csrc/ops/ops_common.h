@@ -29,6 +29,9 @@ inline int dtype_enum(const torch::Tensor &t) {
     case at::ScalarType::BFloat16: return TSB_BF16;
     case at::ScalarType::Int: return TSB_I32;
     case at::ScalarType::Long: return TSB_I64;
+    case at::ScalarType::Byte: return TSB_U8;
+    case at::ScalarType::Char: return TSB_I8;
+    case at::ScalarType::Short: return TSB_I16;
     default: TORCH_CHECK(false, "torch_scatter (B200 build): unsupported dtype ", t.scalar_type());
   }
 }

@@ -6,7 +6,8 @@ import torch
 
 ROOT = osp.dirname(osp.dirname(osp.abspath(__file__)))
 LIB_PATH = osp.join(ROOT, 'pytorch_scatter_b200', 'libtsb200.so')
-DTYPE = {torch.float32: 0, torch.float64: 1, torch.float16: 2, torch.bfloat16: 3, torch.int32: 4, torch.int64: 5}
+DTYPE = {torch.float32: 0, torch.float64: 1, torch.float16: 2, torch.bfloat16: 3, torch.int32: 4, torch.int64: 5,
+         torch.uint8: 6, torch.int8: 7, torch.int16: 8}
 REDUCE = {'sum': 0, 'mean': 1, 'min': 2, 'max': 3, 'mul': 4, 'lse': 5}
 _lib = None
 

@@ -276,6 +276,31 @@ def random_cases(ts):
                 if dtype == torch.float:
                     rec['grad'] = grads_of(call, src)
                 cases.append(rec)
+
+    # ---- the narrow integer types upstream dispatches too (uint8 / int8 / int16), small values and short rows so that
+    # no sum or count leaves the type.  A generator of its own keeps every case above unchanged.
+    gen3 = torch.Generator().manual_seed(20240621)
+    for dtype in (torch.uint8, torch.int8, torch.int16):
+        # uint8 never 0: it is MAX's identity there, and upstream's arg for a row whose maximum equals the identity is
+        # whatever its loop last held
+        lo, hi = (1, 5) if dtype == torch.uint8 else (-3, 4)
+        for (rows, total, feat) in [(7, 40, ()), (6, 50, (5,)), (9, 64, (16,))]:
+            lens = rand_rows(gen3, rows, total)
+            indptr = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)])
+            index = torch.repeat_interleave(torch.arange(rows), lens)
+            src = torch.randint(lo, hi, (total,) + feat, generator=gen3).to(dtype)
+            for reduce in ['sum', 'mean', 'min', 'max']:
+                add('segment_csr', reduce, {'src': src, 'indptr': indptr}, getattr(ts, f'segment_{reduce}_csr'), src, indptr)
+                add('segment_coo', reduce, {'src': src, 'index': index, 'dim_size': rows},
+                    getattr(ts, f'segment_{reduce}_coo'), src, index, None, rows)
+            table = torch.randint(lo, hi, (rows,) + feat, generator=gen3).to(dtype)
+            add('gather_csr', None, {'src': table, 'indptr': indptr}, ts.gather_csr, table, indptr)
+            add('gather_coo', None, {'src': table, 'index': index}, ts.gather_coo, table, index)
+            shuffled = index[torch.randperm(total, generator=gen3)]
+            for reduce in ['sum', 'mul', 'mean', 'min', 'max']:
+                s = src if reduce != 'mul' else src.clamp(-1, 1)
+                add('scatter', reduce, {'src': s, 'index': shuffled, 'dim': 0, 'dim_size': rows},
+                    getattr(ts, 'scatter_' + reduce), s, shuffled, 0, None, rows)
     return cases
 
 

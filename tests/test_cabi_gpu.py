@@ -16,12 +16,22 @@ from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
-DTYPES = [torch.float32, torch.float64, torch.float16, torch.bfloat16, torch.int32, torch.int64]
+DTYPES = [torch.float32, torch.float64, torch.float16, torch.bfloat16, torch.int32, torch.int64,
+          torch.uint8, torch.int8, torch.int16]
+
+
+NARROW = (torch.uint8, torch.int8, torch.int16)
 
 
 def rand_src(gen, shape, dtype):
     if dtype.is_floating_point:
         return torch.randn(shape, generator=gen, dtype=torch.float32).to(dtype)
+    if dtype == torch.uint8:
+        # never 0: it is MAX's identity in this type, and a row whose maximum equals the identity keeps whatever arg
+        # upstream's loop last held (csrc/cpu/segment_csr_cpu.cpp:60: the arg scratch is not reset per row)
+        return torch.randint(1, 5, shape, generator=gen).to(dtype)
+    if dtype == torch.int8:     # small enough that no row sum leaves the type (a 5,000-entry row is not for int8)
+        return torch.randint(-1, 2, shape, generator=gen).to(dtype)
     return torch.randint(-9, 10, shape, generator=gen).to(dtype)
 
 
@@ -84,6 +94,8 @@ def test_segment_csr_and_coo(chunk, kind, K):
     for dtype in dtypes:
         src = rand_src(gen, (1, E, K), dtype)
         for reduce in ('sum', 'mean', 'min', 'max'):
+            if reduce == 'mean' and dtype in NARROW and int(lens.max()) > 100:
+                continue   # a count beyond the narrow type: upstream divides by the wrapped count
             want, want_arg = oracle.segment_csr(src, indptr, reduce)
             got, got_arg = cabi.segment_csr(src.cuda(), indptr.cuda(), reduce)
             got2, got_extra = cabi.segment_coo(src.cuda(), index.cuda(), rows, reduce)
@@ -277,6 +289,8 @@ def test_scatter_rows(scatter_slices, K):
             for reduce in ('sum', 'mean', 'min', 'max'):
                 if order == 'ascending' and dtype not in (torch.float32, torch.int64, torch.bfloat16):
                     continue
+                if reduce == 'mean' and dtype in NARROW:
+                    continue   # the hot target's count leaves the narrow type: upstream divides by the wrapped count
                 want, want_arg = oracle.scatter(src, ix, N, reduce)
                 got, got_arg, _ = cabi.scatter(src.cuda(), ix.cuda(), N, reduce, (0, 1, 0))
                 what = f'scatter {reduce} {dtype} K={K} {order}'

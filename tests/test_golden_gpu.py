@@ -7,7 +7,7 @@ from helpers import assert_close, load_golden
 
 pytestmark = pytest.mark.gpu
 
-DTYPES = [torch.half, torch.bfloat16, torch.float, torch.double, torch.int, torch.long]
+DTYPES = [torch.half, torch.bfloat16, torch.float, torch.double, torch.int, torch.long, torch.uint8, torch.int8, torch.int16]
 
 
 def tens(x, dtype, device='cuda'):

@@ -6,7 +6,7 @@ import torch
 from helpers import (assert_close, load_golden, oracle_gather_coo, oracle_gather_csr, oracle_scatter,
                      oracle_segment_coo, oracle_segment_csr)
 
-DTYPES = [torch.half, torch.bfloat16, torch.float, torch.double, torch.int, torch.long]
+DTYPES = [torch.half, torch.bfloat16, torch.float, torch.double, torch.int, torch.long, torch.uint8, torch.int8, torch.int16]
 
 
 def tens(x, dtype):
