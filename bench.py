@@ -31,6 +31,10 @@ FEAT = 64
 SEED = 20240602
 METRIC = 'segment_csr+scatter sum effective HBM bandwidth (F=64, fp32, power-law CSR)'
 UNIT = 'GB/s'
+# Per-operator timings (--suite, --comparator, --profile-op) start from an idle GPU after a synchronize; without a lead the
+# event pair would also span the host's own path to the first launch (tens of microseconds).  A spin kernel of this many
+# cycles (about 1 ms) keeps the GPU busy while the host enqueues the operator; the start event follows it on the stream.
+HOST_LEAD_CYCLES = 2_000_000
 
 
 def row_lengths(rows, seed, force_long=8, mean=16.0):
@@ -598,9 +602,9 @@ def run_ours(args):
                     'scatter_sum': {'ms': sc_ms, 'GB/s': sc_gbs, 'frac_of_peak': sc_gbs / peak,
                                     'elements_per_s': nnz_all[big] * FEAT / (sc_ms * 1e-3)},
                     'collective': f'inside scatter_sum ({exchange["kind"]})' if world > 1 else None},
-            'roofline': {'bound': 'hbm', 'kernel': 'csr_stream_kernel<float,sum,VEC=4> (+ csr_fixup_kernel), segment_csr',
+            'roofline': {'bound': 'hbm', 'kernel': 'csr_walk_kernel<float,sum,VEC=8> (+ csr_fixup_kernel), segment_csr',
                          'achieved': csr_gbs, 'peak': peak, 'unit': 'GB/s', 'frac': csr_gbs / peak,
-                         'traffic': traffic_of('csr_stream_kernel_contiguous', nnz_all[big]),
+                         'traffic': traffic_of('csr_kernel_contiguous', nnz_all[big]),
                          'peak_source': peak_src, 'algorithmic_bytes_per_launch': b0_csr},
             'roofline_scatter': {'bound': 'hbm', 'kernel': 'scatter(sum): bucket_hist/scan/partition/finalize + '
                                                            'csr_stream_kernel<float,sum,VEC=4,perm> + csr_fixup_kernel'
@@ -706,10 +710,18 @@ def run_profile_op(args):
         fn = lambda: ts.scatter_sum(src, idx, 0, None, N)  # noqa: E731
     else:
         raise ValueError(op)
-    for _ in range(args.warmup + args.steps):
+    for _ in range(args.warmup):
         fn()
     torch.cuda.synchronize()
-    print(json.dumps({'profile_op': op, 'rows': args.rows, 'entries': entries, 'calls': args.warmup + args.steps}))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda._sleep(HOST_LEAD_CYCLES)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    print(json.dumps({'profile_op': op, 'rows': args.rows, 'entries': entries, 'calls': args.warmup + args.steps,
+                      'ms_per_call': e0.elapsed_time(e1) / max(1, args.steps)}))
 
 
 def run_comparator(args):
@@ -738,6 +750,7 @@ def run_comparator(args):
         times = []
         for _ in range(args.steps):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(HOST_LEAD_CYCLES)  # the host enqueues the operator while the GPU is still busy
             e0.record()
             fn()
             e1.record()
@@ -798,6 +811,7 @@ def run_suite(args):
             if small:
                 l2_flush.zero_()  # working set below ~250 MB: flush L2 between iterations
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(HOST_LEAD_CYCLES)  # the host enqueues the operator while the GPU is still busy
             e0.record()
             fn()
             e1.record()

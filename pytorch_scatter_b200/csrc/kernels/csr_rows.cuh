@@ -17,6 +17,7 @@ namespace {
 constexpr int kMinCtasPerSm = 24;
 constexpr int kRingDepth = 16;
 constexpr int kWindowRows = 31;          // lane j holds row pointer j of the window, so rows+1 <= 32
+constexpr int kEmptyRun = 31;            // a warp closes at least this many rows without entries in a row before it searches for the run's end
 constexpr int kRelInf = 0x3fffffff;      // "never ends inside this chunk"
 constexpr int64_t kChunkBytes = 128 * 1024;
 constexpr int64_t kFlatTileBytes = 32 * 1024;  // K == 1: a chunk is staged whole in shared memory (csr_flat_kernel)
@@ -35,6 +36,9 @@ struct CsrGeom {
   void *carry_val;
   int64_t *carry_arg;
   int64_t *head_row;
+  // the fix-up kernel writes the rows without entries that follow kEmptyRun or more such rows (the streaming and the
+  // walking kernel stop closing a run there; the staged kernel hands rows to lane groups anyway and writes its own)
+  bool fill_empty = false;
 };
 
 // Chunk length: a power of two holding about kChunkBytes of source, shortened (down to one full
@@ -288,6 +292,36 @@ __device__ __forceinline__ int64_t first_row_ending_after(const int64_t *ip, int
   if (lo >= N) return N;
   const bool in = lo + lane <= hi && lo + lane < N;
   const unsigned gt = __ballot_sync(kFullMask, in && ip[lo + lane + 1] > pos);
+  return gt ? lo + (__ffs((int)gt) - 1) : hi;
+}
+
+// The same, not inlined, for call sites that run once per long run of empty rows inside issue-bound loops.
+__device__ __noinline__ int64_t first_row_ending_after_cold(const int64_t *ip, int64_t N, int64_t pos, int lane) {
+  return first_row_ending_after(ip, N, pos, lane);
+}
+
+// The same search by one group of L lanes (`gmask`: the group's lanes, `gbase`: its first lane, `col`: the lane inside
+// the group), over rows [from, N): every group of a warp may be in a search of its own.
+// Not inlined: it runs once per long run of empty rows, and the row-closing code it is called from is inlined twice
+// into kernels that are bound by instruction issue.
+__device__ __noinline__ int64_t first_row_ending_after_group(const int64_t *ip, int64_t from, int64_t N, int64_t pos, int col,
+                                                             int L, unsigned gmask, int gbase) {
+  int64_t lo = from < N ? from : N, hi = N;
+  while (hi - lo > L) {
+    const int64_t step = (hi - lo + L - 1) / L;
+    int64_t probe = lo + (col + 1) * step - 1;
+    if (probe > hi - 1) probe = hi - 1;
+    const unsigned gt = (__ballot_sync(gmask, ip[probe + 1] > pos) & gmask) >> gbase;
+    if (gt == 0) { lo = hi; break; }
+    const int f = __ffs((int)gt) - 1;
+    const int64_t new_hi = lo + (int64_t)(f + 1) * step - 1;
+    lo = lo + (int64_t)f * step;
+    hi = new_hi < hi - 1 ? new_hi : hi - 1;
+    if (hi < lo) hi = lo;
+  }
+  if (lo >= N) return N;
+  const bool in = lo + col <= hi && lo + col < N;
+  const unsigned gt = (__ballot_sync(gmask, in && ip[lo + col + 1] > pos) & gmask) >> gbase;
   return gt ? lo + (__ffs((int)gt) - 1) : hi;
 }
 

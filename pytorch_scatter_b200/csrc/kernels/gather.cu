@@ -210,16 +210,8 @@ __global__ void __launch_bounds__(kThreads) gather_coo_kernel(GatherCooParams p)
         for (int u = 0; u < kSteps; ++u) {
           const int m = i + u * eps + sub;  // entry within the batch handled by this lane group
           r[u] = __shfl_sync(kFullMask, (long long)srow[q], m & 31);
-          if (m >= 32 || !col_ok) {
-            r[u] = -1;
-          } else if (r[u] < 0 && ent0 + m < M) {
-            // an index outside [0, N): the entry has no source row; it reads as zero rather than as whatever the
-            // (possibly uninitialised) output held
-            Pack<T, VEC> zero;
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) zero.v[k] = from_acc<T>((acc_t<T>)0);
-            st_stream<T, VEC>(out + (ent0 + m) * p.K + c * VEC, zero);
-          }
+          if (m >= 32 || !col_ok) r[u] = -1;
+          else if (r[u] < 0) r[u] = ent0 + m < M ? -2 : -1;  // -2: an index outside [0, N)
           if (r[u] >= 0) {
             if constexpr (APPLY) {
               v[u] = ld_float_row<VEC>(table + r[u] * p.K + c * VEC);
@@ -254,6 +246,13 @@ __global__ void __launch_bounds__(kThreads) gather_coo_kernel(GatherCooParams p)
               }
               st_stream<T, VEC>(out + at, v[u]);
             }
+          } else if (r[u] == -2) {
+            // the entry has no source row: it reads as zero rather than as whatever the (possibly uninitialised)
+            // output held
+            Pack<T, VEC> zero;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) zero.v[k] = from_acc<T>((acc_t<T>)0);
+            st_stream<T, VEC>(out + (ent0 + i + u * eps + sub) * p.K + c * VEC, zero);
           }
         }
       }

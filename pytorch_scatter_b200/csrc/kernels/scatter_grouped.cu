@@ -137,7 +137,7 @@ group_place_kernel(const int64_t *__restrict__ index, int64_t E, const int32_t *
 //                               shared memory and written coalesced
 // Traffic: the index twice, the pairs written once and read twice (mostly from L2), permutation and
 // row pointers once.
-constexpr int kPartThreads = 1024;
+constexpr int kPartThreads = 1024;   // a tile of the partition kernel is 16 entries per thread: 512 threads (twice the tiles) took twice as long
 constexpr int kFinalThreads = 512;
 constexpr int kMaxBuckets = 4096;
 constexpr int kMaxBucketRows = 16384;
@@ -166,27 +166,27 @@ bucket_hist_kernel(const int64_t *__restrict__ index, int64_t E, int64_t N, int 
     if (s_hist[b] != 0) atomicAdd(hist + b, s_hist[b]);
 }
 
-// start[b] = entries in the buckets before b, start[P] = all valid entries; cursor[b] = 0
-__global__ void __launch_bounds__(kThreads)
-bucket_scan_kernel(const int32_t *__restrict__ hist, int P, int32_t *__restrict__ start, int32_t *__restrict__ cursor) {
-  constexpr int kItems = kMaxBuckets / kThreads;
-  int c[kItems];
+// start[q] = entries in the Q buckets before q, start[Q] = all valid entries; cursor[q] = 0.  One CTA: thread t owns a
+// run of consecutive buckets.
+constexpr int kScanThreads = 1024;
+__global__ void __launch_bounds__(kScanThreads)
+bucket_scan_kernel(const int32_t *__restrict__ hist, int Q, int32_t *__restrict__ start, int32_t *__restrict__ cursor) {
+  const int per = (Q + kScanThreads - 1) / kScanThreads;
+  const int q0 = threadIdx.x * per;
   int64_t v = 0;
-#pragma unroll
-  for (int i = 0; i < kItems; ++i) {
-    const int b = threadIdx.x * kItems + i;
-    c[i] = b < P ? hist[b] : 0;
-    v += c[i];
-  }
+  for (int i = 0; i < per; ++i)
+    if (q0 + i < Q) v += hist[q0 + i];
   int64_t total;
-  int64_t run = block_exclusive_scan(v, &total);
-#pragma unroll
-  for (int i = 0; i < kItems; ++i) {
-    const int b = threadIdx.x * kItems + i;
-    if (b < P) { start[b] = (int32_t)run; cursor[b] = 0; }
-    run += c[i];
+  int64_t run = block_exclusive_scan<kScanThreads>(v, &total);
+  for (int i = 0; i < per; ++i) {
+    const int q = q0 + i;
+    if (q < Q) {
+      start[q] = (int32_t)run;
+      cursor[q] = 0;
+      run += hist[q];
+    }
   }
-  if (threadIdx.x == 0) start[P] = (int32_t)total;
+  if (threadIdx.x == 0) start[Q] = (int32_t)total;
 }
 
 template <int kPartItems>  // entries per thread
@@ -203,17 +203,20 @@ bucket_partition_kernel(const int64_t *__restrict__ index, int64_t E, int64_t N,
   constexpr int kPartTile = kPartThreads * kPartItems;
   const int64_t first = (int64_t)blockIdx.x * kPartTile;
   int row[kPartItems], rank[kPartItems];
+  constexpr int kBatch = kPartItems < 8 ? kPartItems : 8;  // independent loads in flight, then their updates
 #pragma unroll
-  for (int j = 0; j < kPartItems; ++j) {
-    const int64_t e = first + (int64_t)j * kPartThreads + threadIdx.x;
-    row[j] = -1;
-    rank[j] = 0;
-    if (e < E) {
-      const int64_t t = __ldcs(index + e);
-      if (t >= 0 && t < N) {
-        row[j] = (int)t;
-        rank[j] = atomicAdd(&s_cnt[(int)(t >> shift)], 1);
-      }
+  for (int j0 = 0; j0 < kPartItems; j0 += kBatch) {
+    int64_t t[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int64_t e = first + (int64_t)(j0 + j) * kPartThreads + threadIdx.x;
+      t[j] = e < E ? __ldcs(index + e) : -1;
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const bool ok = t[j] >= 0 && t[j] < N;
+      row[j0 + j] = ok ? (int)t[j] : -1;
+      rank[j0 + j] = ok ? atomicAdd(&s_cnt[(int)(t[j] >> shift)], 1) : 0;
     }
   }
   __syncthreads();
@@ -234,6 +237,8 @@ bucket_partition_kernel(const int64_t *__restrict__ index, int64_t E, int64_t N,
       const int b = threadIdx.x * kItems + i;
       if (b < P) {
         s_off[b] = run;
+        // (handing a bucket's slots out through 8 counters instead of one, to shorten the queue of a thousand tiles on
+        // every counter, measured no faster: this kernel 104 vs 102 us, the histogram and the scan 18 us slower)
         if (c[i] != 0) s_dst[b] = start[b] + atomicAdd(cursor + b, c[i]);
       }
       run += c[i];
@@ -271,7 +276,18 @@ bucket_finalize_kernel(const int2 *__restrict__ pairs, const int32_t *__restrict
   const int64_t row0 = (int64_t)b << shift;
   for (int j = threadIdx.x; j < R; j += kFinalThreads) s_rows[j] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += kFinalThreads) atomicAdd(&s_rows[pairs[lo + i].y - (int)row0], 1);
+  constexpr int kBatch = 8;  // independent loads in flight, then their updates
+  for (int i0 = 0; i0 < n; i0 += kBatch * kFinalThreads) {
+    int y[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int i = i0 + j * kFinalThreads + threadIdx.x;
+      y[j] = i < n ? pairs[lo + i].y : -1;
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j)
+      if (y[j] >= 0) atomicAdd(&s_rows[y[j] - (int)row0], 1);
+  }
   __syncthreads();
   {  // exclusive scan over the R rows: thread t owns rows [t * per, t * per + per)
     const int per = (R + kFinalThreads - 1) / kFinalThreads;
@@ -297,11 +313,20 @@ bucket_finalize_kernel(const int2 *__restrict__ pairs, const int32_t *__restrict
   }
   __syncthreads();
   const bool staged = n <= stage_entries;
-  for (int i = threadIdx.x; i < n; i += kFinalThreads) {
-    const int2 pr = pairs[lo + i];
-    const int slot = atomicAdd(&s_rows[pr.y - (int)row0], 1);
-    if (staged) s_perm[slot] = pr.x;
-    else perm[lo + slot] = pr.x;
+  for (int i0 = 0; i0 < n; i0 += kBatch * kFinalThreads) {
+    int2 pr[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const int i = i0 + j * kFinalThreads + threadIdx.x;
+      pr[j] = i < n ? pairs[lo + i] : make_int2(0, -1);
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (pr[j].y < 0) continue;
+      const int slot = atomicAdd(&s_rows[pr[j].y - (int)row0], 1);
+      if (staged) s_perm[slot] = pr[j].x;
+      else perm[lo + slot] = pr[j].x;
+    }
   }
   if (!staged) return;
   __syncthreads();
@@ -312,7 +337,7 @@ bucket_finalize_kernel(const int2 *__restrict__ pairs, const int32_t *__restrict
 // permutation fits the shared-memory stage.  shift < 0: the shapes do not fit (too many rows for
 // kMaxBuckets buckets of kMaxBucketRows rows) and the global-atomic kernels are used.
 struct BucketGeom { int shift, P; };
-constexpr int kBucketEntries = 12288;  // entries a bucket should hold at least (measured: 8k-16k equal, 32k slower)
+constexpr int kBucketEntries = 12288;  // entries a bucket should hold at least (measured, whole scatter: 3k 1.059 ms, 6k 1.034, 12k 1.026, 24k 1.110)
 BucketGeom bucket_geom(int64_t E, int64_t N) {
   const int64_t want = ((int64_t)kBucketEntries * N) / (E > 0 ? E : 1);  // rows holding that many entries
   int shift = 6;
@@ -330,9 +355,8 @@ int allow_bucket_smem() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TSB_ERR_LAUNCH;
   if (done[dev]) return TSB_OK;
   const int part = (3 * kMaxBuckets + 1) * (int)sizeof(int);
-  const int pair = kPartThreads * (int)sizeof(int2);
   const int fin = kFinalSmemInts * (int)sizeof(int);
-  if (cudaFuncSetAttribute(bucket_partition_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, part + 16 * pair) != cudaSuccess ||
+  if (cudaFuncSetAttribute(bucket_partition_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, part + 16 * kPartThreads * (int)sizeof(int2)) != cudaSuccess ||
       cudaFuncSetAttribute(bucket_finalize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fin) != cudaSuccess)
     return TSB_ERR_LAUNCH;
   done[dev] = true;
@@ -416,14 +440,18 @@ int scatter_group(const int64_t *index, int64_t E, int64_t N, int64_t *rowptr, i
     const int P = geom.P, R = 1 << geom.shift;
     const int64_t hist_blocks = (E + kThreads * 64 - 1) / (kThreads * 64);
     constexpr int part_items = 16;
-    const int part_tile = kPartThreads * part_items;
+    const int part_tile = kPartThreads * part_items;   // the histogram kernel's tiles are the same 16384 entries
     const int64_t part_blocks = (E + part_tile - 1) / part_tile;
     if (cudaMemsetAsync(hist, 0, (size_t)P * sizeof(int32_t), stream) != cudaSuccess) return TSB_ERR_LAUNCH;
     bucket_hist_kernel<<<(unsigned)hist_blocks, kThreads, (size_t)P * sizeof(int), stream>>>(index, E, N, geom.shift, P, hist);
-    bucket_scan_kernel<<<1, kThreads, 0, stream>>>(hist, P, start, cursor);
+    bucket_scan_kernel<<<1, kScanThreads, 0, stream>>>(hist, P, start, cursor);
     const size_t part_smem = (size_t)(3 * P + (P & 1)) * sizeof(int) + (size_t)part_tile * sizeof(int2);
     bucket_partition_kernel<part_items><<<(unsigned)part_blocks, kPartThreads, part_smem, stream>>>(index, E, N, geom.shift, P, start, cursor, pairs);
-    int stage = 24576;
+    // staged permutation slots per bucket: one and a half times the average bucket, so that small buckets leave room for
+    // more CTAs per SM (the kernel is a chain of short dependent phases: residency is what hides them)
+    int stage = (int)(((E / P) * 3 / 2 + 1023) / 1024) * 1024;
+    if (stage < 4096) stage = 4096;
+    if (stage > 24576) stage = 24576;
     if (stage > kStageEntries) stage = kStageEntries;
     if (stage > kFinalSmemInts - R) stage = kFinalSmemInts - R;
     const size_t fin_smem = (size_t)(R + stage) * sizeof(int);

@@ -61,6 +61,8 @@ __global__ void __launch_bounds__(32, stream_ctas_per_sm<T, REDUCE, VEC>()) csr_
     // Routed rows: chunks are scheduled roughly in order, so without a rotation every rank would store to owner 0
     // first, then to owner 1, ... and world-1 senders would share one GPU's NVLink ingress at any time.  Rank r
     // starts with the chunks that hold the rows of owner r+1: at any moment the ranks target distinct owners.
+    // (Striding through the chunks instead, so that every rank stores to all owners all the time, measured no
+    // faster on 4 GPUs.)
     int64_t first_row = (int64_t)((p.route_rank + 1) % p.route_world) * p.route_rows;
     if (first_row > p.N) first_row = p.N;
     chunk_id = (chunk_id + clamp64(p.indptr[first_row], 0, p.E) / g.chunk_entries) % g.chunks;  // single batch
@@ -137,6 +139,7 @@ __global__ void __launch_bounds__(32, stream_ctas_per_sm<T, REDUCE, VEC>()) csr_
     if (r_win >= p.N) { cur_start = kRelInf; cur_end = kRelInf; }
     Acc acc;
     acc.init(kRelInf);
+    int empty_windows = 0;   // windows in a row without any entry
 
     // Closes every row that ends at or before `step_end`; `v` is this lane's entry `e` of the step.
     // `id` is what MIN/MAX record for the entry: its position, or with a permutation its source entry.
@@ -179,6 +182,22 @@ __global__ void __launch_bounds__(32, stream_ctas_per_sm<T, REDUCE, VEC>()) csr_
           r_win += kWindowRows;
           cur = 0;
           load_window();
+          // Runs of rows without entries: closed one by one like any other row, a gap of thousands of rows would keep
+          // this warp busy for longer than the rest of the launch takes.  When a second window in a row holds no entry at
+          // all (every pointer at the position the last row ended), the warp searches for the next row that has one
+          // and leaves the rows in between, each preceded by kEmptyRun or more empty rows, to the fix-up kernel.
+          if (__all_sync(kFullMask, rel == cur_end)) {
+            if (++empty_windows > 1) {
+              empty_windows = 0;
+              const int64_t r_next = first_row_ending_after_cold(ip, p.N, cs + cur_end, lane);  // the rows before it end here
+              if (r_next > r_win) {
+                r_win = r_next;
+                load_window();
+              }
+            }
+          } else {
+            empty_windows = 0;
+          }
         }
         cur_start = cur_end;
         cur_end = __shfl_sync(kFullMask, rel, cur + 1);
@@ -403,7 +422,8 @@ __global__ void __launch_bounds__(kFlatThreads) csr_flat_kernel(CsrParams p, Csr
 
 // Fix-up kernel: one warp per chunk.  If the chunk closed a row that began in an earlier chunk,
 // fold the TAIL partials of the chunks the row ran through and this chunk's HEAD partial, in a
-// fixed order, and write the row.
+// fixed order, and write the row.  With CsrGeom::fill_empty the first warps also write the rows the reduction kernels
+// leave out: rows without entries deep inside a long run of such rows.
 template <typename T, int REDUCE, int VEC, bool EXTRAS>
 __global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeom g) {
   using A = acc_t<T>;
@@ -415,7 +435,42 @@ __global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeo
   const int sub = lane >> g.l_log2;
   const int eps = 32 >> g.l_log2;
   const int64_t Kv = p.K / VEC;
-  const int64_t chunk_id = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  const int64_t warp_id = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+
+  // Rows without entries that follow at least kEmptyRun such rows: the reduction kernels stop closing a run there and
+  // search for its end.  The first (rows / 32) warps look at 32 rows each: row n is such a row iff the pointers of rows
+  // n - kEmptyRun and n + 1 are equal.
+  if (g.fill_empty && warp_id * 32 < p.B * p.N) {
+    const int64_t gr = warp_id * 32 + lane;
+    bool todo_lane = false;
+    if (gr < p.B * p.N) {
+      const int64_t b = p.B == 1 ? 0 : gr / p.N;
+      const int64_t n = gr - b * p.N;
+      if (n >= kEmptyRun) {
+        const int64_t *ip = p.indptr + b * p.bstride + n;
+        todo_lane = clamp64(ip[1], 0, p.E) == clamp64(ip[-kEmptyRun], 0, p.E);
+      }
+    }
+    const unsigned todo = __ballot_sync(kFullMask, todo_lane);
+    if (todo != 0) {
+      Acc idn;
+      idn.init(p.E);
+      for (int j = sub; j < 32; j += eps) {   // a lane group per row
+        if (!((todo >> j) & 1u)) continue;
+        const int64_t grow = warp_id * 32 + j;
+        for (int64_t cb = 0; cb < Kv; cb += L) {
+          const int64_t c = cb + col;
+          if (c < Kv && !store_wide_routed<T, REDUCE, VEC, EXTRAS, int64_t>(p, idn, grow, c * VEC))
+            write_row<T, REDUCE, VEC, int64_t>(idn, row_address<T, REDUCE, EXTRAS>(p, grow, c * VEC),
+                                               kArg ? p.arg_out + grow * p.K + c * VEC : nullptr, (int64_t)0, p.mode, p.E,
+                                               0, p.E);
+        }
+        if (col == 0 && p.count_out != nullptr) static_cast<T *>(p.count_out)[grow] = from_acc<T>((A)1);
+      }
+    }
+  }
+
+  const int64_t chunk_id = warp_id;
   if (chunk_id >= p.B * g.chunks) return;
   const int64_t row = g.head_row[chunk_id];
   if (row < 0 || row >= p.N) return;
@@ -551,12 +606,17 @@ int launch_vec(const CsrParams &p, CsrGeom g_in, cudaStream_t stream) {
   const int64_t total_chunks = p.B * g.chunks;
   if (total_chunks > 2147483647LL) return TSB_ERR_TOO_LARGE;
   const bool extras = p.skip_outside || p.route_world > 0;
-  const int64_t blocks = (total_chunks + (kThreads / 32) - 1) / (kThreads / 32);
+  // the fix-up kernel: a warp per chunk, and enough warps that none looks at more than 32 rows for rows without entries
+  g.fill_empty = gf.fill_empty = true;
+  const int64_t row_warps = (p.B * p.N + 31) / 32;
+  const int64_t fix_warps = total_chunks > row_warps ? total_chunks : row_warps;
+  const int64_t blocks = (fix_warps + (kThreads / 32) - 1) / (kThreads / 32);
+  if (blocks > 2147483647LL) return TSB_ERR_TOO_LARGE;
   const bool walk = VEC > full_vec<T>() || choose_kernel<T, REDUCE>(p, p.K / VEC, false) == kWalk;
   if constexpr (REDUCE == kMul) {  // the product exists for scatter only: through the permutation, whole problem
     if (p.perm == nullptr || extras) return TSB_ERR_REDUCE;
     launch_chunks<T, REDUCE, VEC, 1>(p, g, (unsigned)total_chunks, walk, stream);
-    if (g.chunks > 1) csr_fixup_kernel<T, REDUCE, FIX, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, gf);
+    csr_fixup_kernel<T, REDUCE, FIX, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, gf);
     return launch_status();
   } else if (p.perm != nullptr || extras) {
     if constexpr (REDUCE == kLse) {
@@ -565,14 +625,12 @@ int launch_vec(const CsrParams &p, CsrGeom g_in, cudaStream_t stream) {
       if (p.perm == nullptr && p.E > 0) return TSB_ERR_ARG;  // the sharded-scatter features come with a permutation
       if (extras) launch_chunks<T, REDUCE, VEC, 2>(p, g, (unsigned)total_chunks, walk, stream);
       else launch_chunks<T, REDUCE, VEC, 1>(p, g, (unsigned)total_chunks, walk, stream);
-      if (g.chunks > 1) {  // a single chunk per batch cannot split a row
-        if (extras) csr_fixup_kernel<T, REDUCE, FIX, true><<<(unsigned)blocks, kThreads, 0, stream>>>(p, gf);
-        else csr_fixup_kernel<T, REDUCE, FIX, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, gf);
-      }
+      if (extras) csr_fixup_kernel<T, REDUCE, FIX, true><<<(unsigned)blocks, kThreads, 0, stream>>>(p, gf);
+      else csr_fixup_kernel<T, REDUCE, FIX, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, gf);
     }
   } else {
     launch_chunks<T, REDUCE, VEC, 0>(p, g, (unsigned)total_chunks, walk, stream);
-    if (g.chunks > 1) csr_fixup_kernel<T, REDUCE, FIX, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, gf);
+    csr_fixup_kernel<T, REDUCE, FIX, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, gf);
   }
   return launch_status();
 }

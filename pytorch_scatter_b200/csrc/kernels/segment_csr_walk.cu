@@ -73,7 +73,10 @@ __global__ void __launch_bounds__(32, walk_ctas_per_sm<T, REDUCE, VEC>()) csr_wa
   {
     // rows r >= r_first with ends[r] <= cs + ps belong to earlier pieces; count them 32 at a time
     int before = 0;
-    for (int64_t r0 = r_first; r0 < p.N; r0 += 32) {
+    bool counted = false;
+    for (int it = 0; it < 4; ++it) {   // up to 128 rows by counting; chunks with more (runs of empty rows) search instead
+      const int64_t r0 = r_first + 32 * it;
+      if (r0 >= p.N) { counted = true; break; }
       const int64_t r = r0 + lane;
       const int64_t end = (r < p.N) ? __ldg(ip + r + 1) - cs : (int64_t)kRelInf;
       for (int q = 1; q < eps; ++q) {
@@ -81,9 +84,17 @@ __global__ void __launch_bounds__(32, walk_ctas_per_sm<T, REDUCE, VEC>()) csr_wa
         const int c = __popc(__ballot_sync(kFullMask, end <= (int64_t)bound));
         if (q == sub) before += c;
       }
-      if (__any_sync(kFullMask, end > (int64_t)t)) break;  // the rows that follow end after the chunk
+      if (__any_sync(kFullMask, end > (int64_t)t)) { counted = true; break; }  // the rows that follow end after the chunk
     }
-    my_first += before;
+    if (counted) {
+      my_first += before;
+    } else {
+      for (int q = 1; q < eps; ++q) {   // warp-uniform: one cooperative search per piece border
+        const int bound = (q * piece < t) ? q * piece : t;
+        const int64_t r = first_row_ending_after(ip, p.N, cs + bound, lane);
+        if (q == sub) my_first = r > r_first ? r : r_first;
+      }
+    }
   }
 
   const T *bsrc = src + (b * p.E) * p.K;
@@ -118,6 +129,7 @@ __global__ void __launch_bounds__(32, walk_ctas_per_sm<T, REDUCE, VEC>()) csr_wa
     Acc acc, head;
     acc.init(kRelInf);
     head.init(kRelInf);
+    int empty_windows = 0;   // windows in a row without any entry
     int64_t head_row = -1;   // the row that began before this piece and ended inside it
     int head_len = 0;
     bool head_from_before_chunk = false;
@@ -150,6 +162,20 @@ __global__ void __launch_bounds__(32, walk_ctas_per_sm<T, REDUCE, VEC>()) csr_wa
         win += L - 1;
         cur = 0;
         load_window();
+        // a long run of rows without entries (see the streaming kernel): once enough windows in a row held no entry at
+        // all, search for the run's end; the fix-up kernel writes the rows in between
+        if (__all_sync(gmask, rel == cur_end)) {
+          if (++empty_windows * (L - 1) > kEmptyRun + L - 2) {   // kEmptyRun or more such rows are closed already
+            empty_windows = 0;
+            const int64_t r_next = first_row_ending_after_group(ip, win, p.N, cs + cur_end, col, L, gmask, gbase);
+            if (r_next > win) {
+              win = r_next;
+              load_window();
+            }
+          }
+        } else {
+          empty_windows = 0;
+        }
       }
       cur_start = cur_end;
       cur_end = __shfl_sync(gmask, rel, gbase + cur + 1);

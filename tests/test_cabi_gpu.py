@@ -47,6 +47,11 @@ def row_lengths(gen, rows, kind):
         lens = torch.randint(1, 40, (rows,), generator=gen)
         lens[:40] = 0
         lens[-70:] = 0
+    elif kind == 'gaps':     # runs of empty rows: shorter than, equal to and many times a 31-row window, also at both ends
+        lens = torch.randint(1, 12, (rows,), generator=gen)
+        for first, count in ((0, 33), (50, 5), (70, 31), (110, 62), (180, 100)):
+            lens[first:first + count] = 0
+        lens[-45:] = 0
     else:
         raise ValueError(kind)
     return lens
@@ -81,7 +86,7 @@ def chunk(request):
             os.environ[k] = v
 
 
-@pytest.mark.parametrize('kind', ['lognormal', 'uniform', 'giant', 'empty_ends'])
+@pytest.mark.parametrize('kind', ['lognormal', 'uniform', 'giant', 'empty_ends', 'gaps'])
 @pytest.mark.parametrize('K', [1, 2, 3, 4, 16, 33, 64, 130])
 def test_segment_csr_and_coo(chunk, kind, K):
     gen = torch.Generator().manual_seed(1000 + K)
@@ -138,6 +143,52 @@ def test_segment_csr_batched(chunk):
                     assert torch.equal(got_arg.cpu(), want_arg)
 
 
+def test_segment_csr_long_runs_of_empty_rows(chunk):
+    """Thousands of consecutive rows without entries (node-id ranges without edges) are written as identity rows by all
+    lanes side by side and skipped with a search, not closed one by one: results as for any other row structure, with
+    and without seeds in the output."""
+    gen = torch.Generator().manual_seed(31)
+    rows = 20000
+    lens = torch.randint(0, 6, (rows,), generator=gen)
+    lens[:1500] = 0
+    lens[4000:13007] = 0
+    lens[13100:13131] = 0
+    lens[-2600:] = 0
+    indptr = torch.cat([torch.zeros(1, dtype=torch.long), lens.cumsum(0)]).view(1, -1)
+    index = torch.repeat_interleave(torch.arange(rows), lens).view(1, -1)
+    E = int(indptr[0, -1])
+    for K, dtype in ((64, torch.float32), (16, torch.float32), (64, torch.bfloat16), (4, torch.int64), (1, torch.float32)):
+        src = rand_src(gen, (1, E, K), dtype)
+        for reduce in ('sum', 'mean', 'max'):
+            want, want_arg = oracle.segment_csr(src, indptr, reduce)
+            got, got_arg = cabi.segment_csr(src.cuda(), indptr.cuda(), reduce)
+            what = f'gaps csr {reduce} {dtype} K={K}'
+            assert_close(got, want, what=what)
+            if want_arg is not None:
+                assert torch.equal(got_arg.cpu(), want_arg), what + ' arg'
+            want, want_extra = oracle.segment_coo(src, index, rows, reduce)
+            got, got_extra = cabi.segment_coo(src.cuda(), index.cuda(), rows, reduce)
+            assert_close(got, want, what=what.replace('csr', 'coo'))
+            if reduce == 'max':
+                assert torch.equal(got_extra.cpu(), want_extra), what + ' coo arg'
+            elif reduce == 'mean':
+                assert_close(got_extra, want_extra, what=what + ' coo count')
+        seeds = rand_src(gen, (1, rows, K), dtype)
+        index0 = index.clone()   # upstream seeds the first run from row 0 of `out`: let the first run be row 0's
+        index0[0, 0] = 0
+        for reduce in ('sum', 'max'):
+            if reduce == 'max':   # seeds no entry ties with or loses to: where a seed wins, upstream's arg is a stale
+                seeds = seeds - 100 if dtype != torch.uint8 else seeds * 0   # value of an earlier run, ours is E
+            want, want_extra = oracle.segment_coo(src, index0, rows, reduce, out=seeds.clone())
+            got, got_extra = cabi.segment_coo(src.cuda(), index0.cuda(), rows, reduce, out=seeds.clone().cuda())
+            assert_close(got, want, what=f'gaps coo seeded {reduce} {dtype} K={K}')
+            if reduce == 'max':
+                bad = (got_extra.cpu() != want_extra).nonzero()
+                assert bad.numel() == 0, (f'gaps coo seeded {reduce} {dtype} K={K} arg: {bad.size(0)} differ, first at '
+                                          f'{bad[0].tolist()}: got {int(got_extra.cpu()[tuple(bad[0])])}, '
+                                          f'want {int(want_extra[tuple(bad[0])])}, row length {int(lens[bad[0][1]])}')
+
+
 def test_segment_csr_deterministic(chunk):
     gen = torch.Generator().manual_seed(11)
     lens = row_lengths(gen, 2000, 'lognormal')
@@ -148,7 +199,7 @@ def test_segment_csr_deterministic(chunk):
     assert torch.equal(a, b)
 
 
-@pytest.mark.parametrize('kind', ['lognormal', 'giant', 'empty_ends'])
+@pytest.mark.parametrize('kind', ['lognormal', 'giant', 'empty_ends', 'gaps'])
 @pytest.mark.parametrize('K', [1, 3, 4, 64])
 def test_log_sum_exp_rows(chunk, kind, K):
     """TSB_LSE (the reduction behind the fused softmax composites) against float64 torch.logsumexp per row."""
