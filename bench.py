@@ -222,7 +222,7 @@ def sharded_workload(world, rank, dev):
             'nnz': e_hi - e_lo, 'nnz_all': nnz_all, 'rows_all': [int(cuts[r + 1] - cuts[r]) for r in range(world)]}
 
 
-def check_results(ts, w, world, rank, dev, scatter_step):
+def check_results(ts, w, world, rank, dev, scatter_step, interleaved=False):
     """After the timed region: both operators once more, compared with float64 results computed by ATen on the device
     (`index_add_`).  segment_csr: this rank's rows.  scatter: this rank's block of target rows against the same block
     of an NCCL reduce-scatter of the ranks' float64 partials.  Tolerance: |error| <= 1e-5 x the sum of |terms| behind
@@ -245,7 +245,7 @@ def check_results(ts, w, world, rank, dev, scatter_step):
         dist.reduce_scatter_tensor(mass_b, mass)
         want, mass = want_b, mass_b
     got = scatter_step(src, w['shuffled'])
-    if world > 1 and got.size(0) != per:
+    if world > 1 and interleaved:
         # the NCCL per-slice variant interleaves ownership: compare the rows this rank really holds
         from pytorch_scatter_b200.dist import overlapped_layout, owned_rows
         passes, sub = overlapped_layout(ROWS, world, FEAT * 4)
@@ -389,12 +389,19 @@ def run_c5(ts, world, rank, dev, steps):
         return {'ms': ms[name], 'GB/s': gbs, 'frac_of_peak_per_gpu': gbs / world / peak,
                 'elements_per_s': E * F / (ms[name] * 1e-3)}
 
+    # what bounds the sharded scatter: every rank holds a partial of every node row (fp32 on the wire) and stores
+    # (world - 1) / world of them into its peers; 770 GB/s is the peer-copy rate measured on this pool, per direction
+    nvlink = None
+    if world > 1 and routed:
+        wire = nodes * F * 4 * (world - 1) / world
+        nvlink = {'bytes_out_per_rank': int(wire), 'ms_at_770_GBps': wire / 770e9 * 1e3,
+                  'frac': (wire / 770e9 * 1e3) / ms['scatter_sum']}
     return {'workload': f'{nodes} nodes / {E} edges (log-normal in-degree, mean 20, clip 20000), bf16 messages [{E} x {F}], '
                         'one global problem at every GPU count (strong scaling)', 'n_gpus': world, 'steps': steps,
             'shard_entries': nnz_all, 'nnz_imbalance_max_over_mean': max(nnz_all) / (E / world),
             'exchange': ('peer stores from the reduction kernel' if routed else 'NCCL reduce-scatter per slice') if world > 1 else None,
             'segment_csr_sum': entry('segment_csr_sum', b_csr), 'segment_csr_mean': entry('segment_csr_mean', b_csr),
-            'scatter_sum': entry('scatter_sum', b_sc),
+            'scatter_sum': entry('scatter_sum', b_sc), 'scatter_nvlink_bound': nvlink,
             'check': {'segment_csr_sum': float(ratios[0]), 'segment_csr_mean': float(ratios[1]), 'scatter_sum': float(ratios[2]),
                       'what': 'worst |error| / (1e-2 |result| + 1e-2) over 20,000 rows per rank (csr) and 50,000 sampled '
                               'target rows (scatter), against float64 index_add_', 'ok': bool((ratios <= 1.0).all())}}
@@ -538,7 +545,8 @@ def run_ours(args):
     del in_bufs
 
     # ---- what was timed is also checked (untimed)
-    csr_ratio, sc_ratio, ok = check_results(ts, w, world, rank, dev, scatter_step)
+    csr_ratio, sc_ratio, ok = check_results(ts, w, world, rank, dev, scatter_step,
+                                            interleaved=world > 1 and not (exchange['kind'] or '').startswith('peer'))
 
     # ---- the GNN-scale configuration (bf16 F=128, 10 M nodes / 200 M edges) at this GPU count, untimed by the metric
     del src, indptr, shuffled, out_csr
@@ -617,7 +625,7 @@ def run_ours(args):
             'check': {'csr_max_err_over_bound': csr_ratio, 'scatter_max_err_over_bound': sc_ratio,
                       'bound': '1e-5 x sum|terms| per output, against float64 index_add_ (N>1: reduce-scatter of the '
                                'float64 partials)', 'ok': ok},
-            # per step, segment_csr: csr_stream_kernel + csr_fixup_kernel.  scatter on one GPU (output larger
+            # per step, segment_csr: csr_walk_kernel + csr_fixup_kernel.  scatter on one GPU (output larger
             # than L2: the grouped path): bucket_hist, bucket_scan, bucket_partition, bucket_finalize, then
             # csr_stream_kernel + csr_fixup_kernel through the permutation.  Several GPUs with the routed exchange:
             # the same plus sum_slabs_kernel; with the NCCL variant: the grouping once plus stream + fix-up per slice.
