@@ -470,6 +470,8 @@ __global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeo
     }
   }
 
+  // (One thread per chunk looking for such rows and the warps sharing out the hits, to launch fewer CTAs, was slower:
+  // nearly every chunk of a short-row problem closes a row begun earlier, and eight warps then took 256 folds in turn.)
   const int64_t chunk_id = warp_id;
   if (chunk_id >= p.B * g.chunks) return;
   const int64_t row = g.head_row[chunk_id];
@@ -489,14 +491,33 @@ __global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeo
     Acc acc;
     acc.init(p.E);
     if (col_ok) {
-      for (int64_t cc = c1 + sub; cc < w; cc += eps) {  // TAIL partials of the chunks run through
+      // TAIL partials of the chunks run through, kFold loads in flight (a 20,000-entry row runs through 150 chunks:
+      // one load per trip made this loop, and with it the kernel, a chain of 80 L2 latencies), merged in chunk order
+      constexpr int kFold = 4;
+      int64_t cc = c1 + sub;
+      for (; cc + (kFold - 1) * eps < w; cc += kFold * eps) {
+        A oval[kFold][VEC];
+        int64_t oarg[kFold][Acc::kPair ? VEC : 1];
+#pragma unroll
+        for (int f = 0; f < kFold; ++f) {
+          const int64_t at = ((b * g.chunks + cc + f * eps) * 2 + 1) * p.K + c * VEC;
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) {
+            oval[f][i] = __ldg(carry + at + i);
+            if (Acc::kPair) oarg[f][i] = __ldg(g.carry_arg + at + i);
+          }
+        }
+#pragma unroll
+        for (int f = 0; f < kFold; ++f) acc.merge(oval[f], oarg[f]);
+      }
+      for (; cc < w; cc += eps) {
         const int64_t at = ((b * g.chunks + cc) * 2 + 1) * p.K + c * VEC;
         A oval[VEC];
         int64_t oarg[Acc::kPair ? VEC : 1];
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
-          oval[i] = carry[at + i];
-          if (Acc::kPair) oarg[i] = g.carry_arg[at + i];
+          oval[i] = __ldg(carry + at + i);
+          if (Acc::kPair) oarg[i] = __ldg(g.carry_arg + at + i);
         }
         acc.merge(oval, oarg);
       }
@@ -521,6 +542,14 @@ __global__ void __launch_bounds__(kThreads) csr_fixup_kernel(CsrParams p, CsrGeo
   if (lane == 0 && p.count_out != nullptr) {
     static_cast<T *>(p.count_out)[grow] = from_acc<T>((A)(re - rs > 0 ? re - rs : 1));
   }
+}
+
+// CTAs of the fix-up kernel: a warp per chunk, and enough warps that none looks at more than 32 rows for rows without
+// entries.
+inline int64_t fixup_blocks(int64_t total_chunks, int64_t total_rows) {
+  const int64_t row_warps = (total_rows + 31) / 32;
+  const int64_t warps = total_chunks > row_warps ? total_chunks : row_warps;
+  return (warps + (kThreads / 32) - 1) / (kThreads / 32);
 }
 
 size_t carry_bytes(int64_t total_chunks, int64_t K, size_t acc_size, bool with_arg, size_t *arg_off, size_t *row_off) {
@@ -606,11 +635,8 @@ int launch_vec(const CsrParams &p, CsrGeom g_in, cudaStream_t stream) {
   const int64_t total_chunks = p.B * g.chunks;
   if (total_chunks > 2147483647LL) return TSB_ERR_TOO_LARGE;
   const bool extras = p.skip_outside || p.route_world > 0;
-  // the fix-up kernel: a warp per chunk, and enough warps that none looks at more than 32 rows for rows without entries
   g.fill_empty = gf.fill_empty = true;
-  const int64_t row_warps = (p.B * p.N + 31) / 32;
-  const int64_t fix_warps = total_chunks > row_warps ? total_chunks : row_warps;
-  const int64_t blocks = (fix_warps + (kThreads / 32) - 1) / (kThreads / 32);
+  const int64_t blocks = fixup_blocks(total_chunks, p.B * p.N);
   if (blocks > 2147483647LL) return TSB_ERR_TOO_LARGE;
   const bool walk = VEC > full_vec<T>() || choose_kernel<T, REDUCE>(p, p.K / VEC, false) == kWalk;
   if constexpr (REDUCE == kMul) {  // the product exists for scatter only: through the permutation, whole problem
@@ -663,7 +689,7 @@ int launch_typed(const CsrParams &p, cudaStream_t stream) {
     if (Kv <= 32) {
       g.l_log2 = ilog2_ceil(Kv);
       const size_t smem = (size_t)g.chunk_entries * (size_t)p.K * sizeof(T);
-      const int64_t blocks = (total_chunks + (kThreads / 32) - 1) / (kThreads / 32);
+      const int64_t blocks = fixup_blocks(total_chunks, 0);   // the staged kernel writes its own rows without entries
       if (vec) {
         csr_flat_kernel<T, REDUCE, kFull><<<(unsigned)total_chunks, kFlatThreads, smem, stream>>>(p, g);
         if (g.chunks > 1) csr_fixup_kernel<T, REDUCE, kFull, false><<<(unsigned)blocks, kThreads, 0, stream>>>(p, g);
