@@ -583,6 +583,10 @@ __global__ void __launch_bounds__(kThreads, 3) scatter_rows_binned_kernel(Scatte
 
   for (int i = tid; i < kBinBins; i += kThreads) s_cnt[i] = 0;
   __syncthreads();
+  // The bin is a multiplicative hash of the target, salted with the tile: two hot targets that share a bin (their
+  // entries then alternate inside it and every switch costs an update) do so in one tile out of kBinBins, not in all.
+  const unsigned salt = (unsigned)blockIdx.x * 0x9e3779b9u;
+  auto bin_of = [](int row, unsigned salt) -> unsigned { return (((unsigned)row ^ salt) * 2654435761u) >> 20; };
   // 1. targets of this thread's entries (coalesced loads, all in flight), rank inside the bin
   int row[kBinItems], rank[kBinItems];
 #pragma unroll
@@ -598,7 +602,7 @@ __global__ void __launch_bounds__(kThreads, 3) scatter_rows_binned_kernel(Scatte
 #pragma unroll
   for (int j = 0; j < kBinItems; ++j) {
     rank[j] = 0;
-    if (row[j] >= 0) rank[j] = atomicAdd(&s_cnt[((unsigned)row[j] * 2654435761u) >> 20], 1);
+    if (row[j] >= 0) rank[j] = atomicAdd(&s_cnt[bin_of(row[j], salt)], 1);
   }
   __syncthreads();
   // 2. exclusive scan of the bin counts (kBinBins / kThreads consecutive bins per thread)
@@ -628,7 +632,7 @@ __global__ void __launch_bounds__(kThreads, 3) scatter_rows_binned_kernel(Scatte
   for (int w = 0; w < kWarps; ++w) n += s_warp_sum[w];
 #pragma unroll
   for (int j = 0; j < kBinItems; ++j)
-    if (row[j] >= 0) s_pair[s_cnt[((unsigned)row[j] * 2654435761u) >> 20] + rank[j]] = make_int2(row[j], j * kThreads + tid);
+    if (row[j] >= 0) s_pair[s_cnt[bin_of(row[j], salt)] + rank[j]] = make_int2(row[j], j * kThreads + tid);
   __syncthreads();  // the list is complete and the bin counters are dead: their space becomes the ring
   if (n == 0) return;
 
