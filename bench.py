@@ -466,6 +466,7 @@ def run_ours(args):
         sampler.start()
     stream = torch.cuda.current_stream()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
+    host_t0 = time.perf_counter()
     ev[0].record(stream)
     for i in range(args.steps):
         # CSR rows are independent: each rank reduces its own row range, no collective.
@@ -473,10 +474,51 @@ def run_ours(args):
         ev[2 * i + 1].record(stream)
         scatter_step(src, shuffled, record=True)
         ev[2 * i + 2].record(stream)
+    host_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps   # what the host needs to enqueue a step
     sync_all()
-    clocks = sampler.stop() if rank == 0 else None
 
     total_ms = ev[0].elapsed_time(ev[-1])
+    launch = 'eager (one operator call after the other from Python)'
+    # Several ranks wait for one another in every step (the exchange's barrier), so a rank whose host falls behind with
+    # its launches holds up all of them.  The step is therefore also captured in a CUDA graph (two steps: the exchange
+    # alternates between two staging buffers) and replayed; if every rank could capture it, the replays are what
+    # `value` reports, and the per-operator and per-phase times stay those of the eager loop above.
+    graph = None
+    if args.graph == 'on' or (args.graph == 'auto' and world > 1 and (exchange['kind'] or '').startswith('peer')):
+        captured = 1
+        try:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for _ in range(2):
+                    ts.segment_csr(src, indptr, out=out_csr, reduce='sum')
+                    scatter_step(src, shuffled)
+        except Exception as exc:  # noqa: BLE001  (whatever refuses to be captured: time the eager loop instead)
+            print(f'[bench] rank {rank}: CUDA graph capture failed, eager timing stands: {type(exc).__name__}: {exc}',
+                  file=sys.stderr, flush=True)
+            graph, captured = None, 0
+        if world > 1:
+            flag = torch.tensor([captured], device=dev, dtype=torch.int32)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            captured = int(flag.item())
+        if not captured:
+            graph = None
+    if graph is not None:
+        for _ in range(2):
+            graph.replay()
+        sync_all()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record(stream)
+        for _ in range(args.steps // 2):
+            graph.replay()
+        if args.steps % 2:   # exactly K steps: the odd one out runs eagerly
+            ts.segment_csr(src, indptr, out=out_csr, reduce='sum')
+            scatter_step(src, shuffled)
+        g1.record(stream)
+        sync_all()
+        total_ms = g0.elapsed_time(g1)
+        launch = 'CUDA graph of two steps, replayed (per-operator and per-phase times: eager loop)'
+    clocks = sampler.stop() if rank == 0 else None
     csr_ms = sum(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(args.steps)) / args.steps
     sc_ms = sum(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps)) / args.steps
     n_ph = len(ROUTED_PHASES)
@@ -555,7 +597,7 @@ def run_ours(args):
     c5 = None if args.no_c5 else run_c5(ts, world, rank, dev, max(3, min(args.steps, 10)))
 
     # ---- max (and mean) over ranks
-    times = torch.tensor([total_ms, csr_ms, sc_ms, e2e_ms] + phase_ms, device=dev, dtype=torch.float64)
+    times = torch.tensor([total_ms, csr_ms, sc_ms, e2e_ms] + phase_ms + [host_ms], device=dev, dtype=torch.float64)
     if world > 1:
         gathered = [torch.empty_like(times) for _ in range(world)]
         dist.all_gather(gathered, times)
@@ -630,6 +672,8 @@ def run_ours(args):
             # csr_stream_kernel + csr_fixup_kernel through the permutation.  Several GPUs with the routed exchange:
             # the same plus sum_slabs_kernel; with the NCCL variant: the grouping once plus stream + fix-up per slice.
             'gpu_launches': ((2 + 6) if world == 1 else (2 + 6 + 1) if routed else (2 + 4 + 2 * scatter_passes)) * args.steps,
+            'launch': launch,
+            'host_enqueue_ms_per_step': {'max': float(allt[:, -1].max()), 'per_rank': [round(float(x), 3) for x in allt[:, -1].tolist()]},
             'clocks': clocks,
         }
         if routed:
@@ -960,6 +1004,8 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--ref-fraction', type=int, default=4, help='reference arm runs on 1/this of the rows')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--graph', default='auto', choices=['auto', 'on', 'off'],
+                    help="replay the step from a CUDA graph for the timed value: 'auto' = with more than one GPU")
     ap.add_argument('--exchange', default='auto', choices=['auto', 'nccl'],
                     help='N > 1: auto = peer stores from the reduction kernel when symmetric memory is available; nccl = '
                          'the per-slice NCCL reduce-scatter variant')

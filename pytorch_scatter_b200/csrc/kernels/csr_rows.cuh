@@ -333,4 +333,9 @@ __device__ __noinline__ int64_t first_row_ending_after_group(const int64_t *ip, 
 bool launch_csr_walk(const CsrParams &p, const void *geom, unsigned total_chunks, int dtype, int reduce, bool wide, int mode,
                      cudaStream_t stream);
 
+// Launches csr_rows_kernel (segment_csr_rows.cu): a lane group per row, for problems whose rows hold only a few
+// entries.  `vec`: 16-byte packs (K a multiple of the pack, aligned pointers); mode as above.  Returns false if that
+// combination is not built.
+bool launch_csr_short_rows(const CsrParams &p, int dtype, int reduce, bool vec, int mode, cudaStream_t stream);
+
 }  // namespace tsb

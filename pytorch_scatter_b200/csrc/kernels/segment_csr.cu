@@ -597,6 +597,18 @@ inline int choose_kernel(const CsrParams &p, int64_t packs_per_entry, bool wide_
   return p.E / rows < 6 ? kWalk : kStream;   // sums over rows of a few entries
 }
 
+// The row-parallel kernel (segment_csr_rows.cu) is chosen for rows of fewer than 4 entries on average AND entries of at
+// most 64 bytes.  Measured (ms, row-parallel / walking / streaming): 4 M rows of ~2 entries, fp32 F=16: sum 0.291 / 0.496
+// / 0.593, max 0.450 / 0.628 / 1.364.  With wider entries it loses, because a CTA then holds few rows and every row is
+// a chain of three dependent loads (row pointers, permutation, source) with nothing else of that lane group in flight:
+// fp32 F=64, ~2 entries: sum 1.088 / 0.701 / 0.616; bf16 F=128, 25 M entries into 10 M rows through a permutation (an
+// edge shard of a power-law graph): sum 11.06 / 2.89 / 2.90.  TSB_CSR_KERNEL=rows (test hook) dictates it.
+inline bool short_rows_preferred(const CsrParams &p, size_t elem) {
+  if (const char *v = std::getenv("TSB_CSR_KERNEL")) return *v == 'r';
+  const int64_t rows = p.B * p.N > 0 ? p.B * p.N : 1;
+  return p.B * p.E < 4 * rows && p.K * (int64_t)elem <= 64;
+}
+
 template <typename T> constexpr int dtype_code() {
   if (std::is_same<T, float>::value) return TSB_F32;
   if (std::is_same<T, double>::value) return TSB_F64;
@@ -703,6 +715,14 @@ int launch_typed(const CsrParams &p, cudaStream_t stream) {
   }
   bool vec_ok = (p.K % kFull == 0) && aligned16(p.src) && aligned16(p.out);
   for (int q = 0; q < p.route_world; ++q) vec_ok = vec_ok && aligned16(p.route_base[q]);
+  if constexpr (REDUCE != kLse) {
+    // rows of only a few entries: a lane group per row instead of chunks (segment_csr_rows.cu)
+    const bool extras = p.skip_outside || p.route_world > 0;
+    if (short_rows_preferred(p, sizeof(T)) && (!extras || p.perm != nullptr || p.E == 0)) {
+      const int mode = extras ? 2 : (p.perm != nullptr ? 1 : 0);
+      if (launch_csr_short_rows(p, dtype_code<T>(), REDUCE, vec_ok, mode, stream)) return launch_status();
+    }
+  }
   if (vec_ok) {
     // two packs (32 bytes) per lane: every row of src / out must start on a 32-byte boundary
     const bool wide = (p.K % (2 * kFull) == 0) && p.K / (2 * kFull) >= 4 && aligned32(p.src) && aligned32(p.out);

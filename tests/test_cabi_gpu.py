@@ -57,13 +57,15 @@ def row_lengths(gen, rows, kind):
     return lens
 
 
-@pytest.fixture(params=[None, 32, 64, 'staged', 'walk', 'walk-32', 'stream', 'stream-32'],
-                ids=['chunk-default', 'chunk-32', 'chunk-64', 'staged-rows', 'walk', 'walk-chunk-32', 'stream', 'stream-chunk-32'])
+@pytest.fixture(params=[None, 32, 64, 'staged', 'walk', 'walk-32', 'stream', 'stream-32', 'rows'],
+                ids=['chunk-default', 'chunk-32', 'chunk-64', 'staged-rows', 'walk', 'walk-chunk-32', 'stream', 'stream-chunk-32',
+                     'row-parallel'])
 def chunk(request):
     """Chunk lengths of the row-pointer reduction (short chunks make rows straddle many chunk borders), the kernel
     that stages chunks in shared memory (the default for K == 1 only) forced for every entry of up to 64 bytes, and
     each of the two chunk kernels (lane groups walking pieces / the warp streaming steps) dictated where the library
-    would pick by shape."""
+    would pick by shape, and the row-parallel kernel (a lane group per row, long rows by the whole CTA) that it picks
+    for rows of a few entries."""
     names = ('TSB_CSR_CHUNK_ENTRIES', 'TSB_CSR_FORCE_FLAT', 'TSB_CSR_KERNEL')
     old = {k: os.environ.get(k) for k in names}
     for k in names:
@@ -286,7 +288,8 @@ def test_gathers(K):
 
 
 @pytest.fixture(params=['one-pass', 'sliced', 'replicated', 'runs', 'runs-sliced', 'direct', 'grouped', 'grouped-chunk32',
-                        'grouped-atomic', 'grouped-walk', 'grouped-walk-chunk32', 'grouped-stream', 'cached', 'cached-replicated'])
+                        'grouped-atomic', 'grouped-walk', 'grouped-walk-chunk32', 'grouped-stream', 'grouped-rows', 'cached',
+                        'cached-replicated'])
 def scatter_slices(request):
     """Forces the variants the launcher normally picks by size or by probing the index: sliced multi-pass
     accumulation (outputs larger than L2), accumulation into several copies of the output (small,
@@ -311,6 +314,8 @@ def scatter_slices(request):
         os.environ['TSB_CSR_CHUNK_ENTRIES'] = '32'
     if 'walk' in request.param or 'stream' in request.param:   # which chunk kernel reduces the grouped rows
         os.environ['TSB_CSR_KERNEL'] = 'walk' if 'walk' in request.param else 'stream'
+    if request.param == 'grouped-rows':    # ... or the row-parallel kernel (a lane group per row)
+        os.environ['TSB_CSR_KERNEL'] = 'rows'
     if request.param.startswith('cached'):  # fp32 sums through the shared-memory row cache (skewed indices)
         os.environ['TSB_SCATTER_CACHED'] = '1'
         os.environ['TSB_SCATTER_CLUSTERED'] = '0'
@@ -577,7 +582,19 @@ def test_scatter_group_and_permuted_row_slices(sort, chunk):
             os.environ['TSB_SCATTER_GROUPED_SORT'] = old
 
 
-def test_routed_rows_two_ranks_emulated():
+@pytest.fixture(params=[None, 'rows'], ids=['kernel-by-shape', 'row-parallel'])
+def routed_kernel(request):
+    old = os.environ.get('TSB_CSR_KERNEL')
+    os.environ.pop('TSB_CSR_KERNEL', None)
+    if request.param is not None:
+        os.environ['TSB_CSR_KERNEL'] = request.param
+    yield request.param
+    os.environ.pop('TSB_CSR_KERNEL', None)
+    if old is not None:
+        os.environ['TSB_CSR_KERNEL'] = old
+
+
+def test_routed_rows_two_ranks_emulated(routed_kernel):
     """The sharded scatter's fused exchange on one GPU: two "ranks" (two edge shards, run one after the other) store
     their finished rows into the owners' staging buffers; adding each owner's slabs must give the full scatter."""
     import pytorch_scatter_b200  # noqa: F401  (registers the operators)
