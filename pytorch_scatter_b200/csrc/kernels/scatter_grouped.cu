@@ -138,7 +138,7 @@ group_place_kernel(const int64_t *__restrict__ index, int64_t E, const int32_t *
 // Traffic: the index twice, the pairs written once and read twice (mostly from L2), permutation and
 // row pointers once.
 constexpr int kPartThreads = 1024;   // a tile of the partition kernel is 16 entries per thread: 512 threads (twice the tiles) took twice as long
-constexpr int kFinalThreads = 512;
+constexpr int kFinalThreads = 512;   // (1024 threads, full occupancy: 90.6 us against 93)
 constexpr int kMaxBuckets = 4096;
 constexpr int kMaxBucketRows = 16384;
 constexpr int kStageEntries = 49152;  // most permutation slots kernel C stages in shared memory (192 KiB)

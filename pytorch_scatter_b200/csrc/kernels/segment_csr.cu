@@ -34,6 +34,7 @@ namespace {
 // 16-bit MIN/MAX carry eight fp32 values and eight arg indices per lane: under the 80-register cap they spill, so
 // those variants trade resident warps for registers (16 CTAs = 128 KiB in flight per SM still covers the latency).
 template <typename T, int REDUCE, int VEC> constexpr int stream_ctas_per_sm() {
+  if (sizeof(T) == 2 && VEC > 1 && REDUCE == kMean) return 20;   // the row count and its reciprocal on top of a sum's registers
   return (sizeof(T) == 2 && VEC > 1 && (REDUCE == kMin || REDUCE == kMax)) ? 16 : kMinCtasPerSm;
 }
 
