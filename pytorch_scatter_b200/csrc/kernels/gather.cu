@@ -173,9 +173,11 @@ __global__ void __launch_bounds__(kThreads) gather_coo_kernel(GatherCooParams p)
   const T *__restrict__ count = static_cast<const T *>(p.count);
   const T *__restrict__ xs = static_cast<const T *>(p.x);  // APPLY: second operand at the entry's own position
   constexpr int kWarps = kThreads / 32;
-  // entries a lane group has in flight.  The apply modes on 16-bit data hold an fp32 table row (eight values) beside
-  // every 16-byte pack: with four steps they need 115 registers (two CTAs per SM), with two steps three CTAs fit.
-  constexpr int kSteps = (APPLY && sizeof(T) == 2) ? 2 : 4;
+  // entries a lane group has in flight.  The apply modes hold an fp32 table row beside every 16-byte pack (eight
+  // values on 16-bit data): with four steps the bf16 kernel needs 115 registers and two CTAs fit an SM, with two steps
+  // 64.  Measured, scatter_softmax at F=64 (ms; 1 / 2 / 4 / 8 steps): fp32 2.80 / 2.66 / 2.77 / 3.56; bf16 2.61 -> 2.01
+  // from four steps to two.
+  constexpr int kSteps = APPLY ? 2 : 4;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int L = 1 << p.l_log2;
   const int col = lane & (L - 1);
