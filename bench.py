@@ -517,10 +517,42 @@ def run_ours(args):
         g1.record(stream)
         sync_all()
         total_ms = g0.elapsed_time(g1)
-        launch = 'CUDA graph of two steps, replayed (per-operator and per-phase times: eager loop)'
-    clocks = sampler.stop() if rank == 0 else None
+        launch = 'CUDA graph of two steps, replayed (per-phase times: eager loop)'
     csr_ms = sum(ev[2 * i].elapsed_time(ev[2 * i + 1]) for i in range(args.steps)) / args.steps
     sc_ms = sum(ev[2 * i + 1].elapsed_time(ev[2 * i + 2]) for i in range(args.steps)) / args.steps
+    csr_eager_ms, sc_eager_ms = csr_ms, sc_ms
+    if graph is not None and args.steps >= 2:
+        # the two operators on their own, replayed the same way (a graph of two calls each), so that the per-operator
+        # times belong to the same kind of launch as `value`; if a capture fails here the eager times stand
+        def replayed(fn):
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2):
+                for _ in range(2):
+                    fn()
+            g2.replay()
+            sync_all()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(args.steps // 2):
+                g2.replay()
+            b.record(stream)
+            sync_all()
+            return a.elapsed_time(b) / (2 * (args.steps // 2))
+        ok_ops = 1
+        try:
+            csr_g = replayed(lambda: ts.segment_csr(src, indptr, out=out_csr, reduce='sum'))
+            sc_g = replayed(lambda: scatter_step(src, shuffled))
+        except Exception as exc:  # noqa: BLE001
+            print(f'[bench] rank {rank}: per-operator graphs failed, eager times stand: {type(exc).__name__}: {exc}',
+                  file=sys.stderr, flush=True)
+            ok_ops = 0
+        if world > 1:
+            flag = torch.tensor([ok_ops], device=dev, dtype=torch.int32)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            ok_ops = int(flag.item())
+        if ok_ops:
+            csr_ms, sc_ms = csr_g, sc_g
+    clocks = sampler.stop() if rank == 0 else None
     n_ph = len(ROUTED_PHASES)
     phase_ms = [0.0] * n_ph
     if timeline:
@@ -597,7 +629,8 @@ def run_ours(args):
     c5 = None if args.no_c5 else run_c5(ts, world, rank, dev, max(3, min(args.steps, 10)))
 
     # ---- max (and mean) over ranks
-    times = torch.tensor([total_ms, csr_ms, sc_ms, e2e_ms] + phase_ms + [host_ms], device=dev, dtype=torch.float64)
+    times = torch.tensor([total_ms, csr_ms, sc_ms, e2e_ms] + phase_ms + [csr_eager_ms, sc_eager_ms, host_ms], device=dev,
+                         dtype=torch.float64)
     if world > 1:
         gathered = [torch.empty_like(times) for _ in range(world)]
         dist.all_gather(gathered, times)
@@ -683,6 +716,7 @@ def run_ours(args):
                 for k, name in enumerate(ROUTED_PHASES)}
             line['ops']['per_rank_ms'] = {'segment_csr_sum': [round(float(x), 4) for x in allt[:, 1].tolist()],
                                           'scatter_sum': [round(float(x), 4) for x in allt[:, 2].tolist()]}
+            line['ops']['eager_ms'] = {'segment_csr_sum': float(allt[:, -3].max()), 'scatter_sum': float(allt[:, -2].max())}
         if c5 is not None:
             line['c5'] = c5
         if world == 1 and not args.no_cpu_baseline:
