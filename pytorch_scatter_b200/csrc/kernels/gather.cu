@@ -232,7 +232,6 @@ __global__ void __launch_bounds__(kThreads) gather_coo_kernel(GatherCooParams p)
             const int64_t at = (ent0 + i + u * eps + sub) * p.K + c * VEC;
             if constexpr (APPLY) {
               Pack<T, VEC> o;
-#pragma unroll
               FloatRow<VEC> w;
               if constexpr (SCALED) w = ld_float_row<VEC>(p.scale + r[u] * p.K + c * VEC);  // the table row's neighbour in time: L1/L2
 #pragma unroll
