@@ -1,6 +1,7 @@
-// Shared pieces of the row-pointer reduction's chunk kernels (segment_csr.cu: streaming, staged and fix-up kernels;
-// segment_csr_walk.cu: the walking kernel): chunk geometry, per-lane row accumulators, the row writer and the
-// cooperative row search.  Split over two translation units so that they compile side by side.
+// Shared pieces of the row-pointer reduction's kernels (segment_csr.cu: streaming, staged and fix-up kernels;
+// segment_csr_walk.cu: the walking kernel; segment_csr_rows.cu: the row-parallel kernel): chunk geometry, per-lane row
+// accumulators, the row writer and the cooperative row searches.  Split over translation units so that they compile
+// side by side.
 #pragma once
 
 #include <cstdlib>

@@ -17,8 +17,13 @@
 //   * a row that straddles chunk borders is never written by the stream: the chunk where it ends
 //     stores a HEAD partial, every chunk it runs out of stores a TAIL partial (workspace), and a
 //     small fix-up kernel folds TAIL[c1..c2-1] and HEAD[c2] in a fixed order and writes the row.
+//   * a run of rows without entries sits at one position of the stream and therefore in one chunk: after two
+//     windows without any entry the warp searches for the next row that has one, and the fix-up kernel writes the
+//     rows in between (every empty row that follows kEmptyRun or more empty rows), all of them in parallel.
 // A 20,000-entry row is thus spread over 40 warps, a million-entry row over 2,000.  Nothing is
 // atomic: results depend only on the shapes, never on scheduling.
+// Two more kernels reduce the same problems where they are faster: the walking kernel (segment_csr_walk.cu: lane groups
+// own pieces of a chunk) and the row-parallel kernel (segment_csr_rows.cu: a lane group per row, short narrow rows).
 //
 // Replaces segment_csr_kernel / segment_csr_broadcast_kernel of the upstream project
 // (csrc/cuda/segment_csr_cuda.cu:15-95), which walk each row with a single thread per feature.
